@@ -1,0 +1,188 @@
+/*
+ * piekv.h - C ABI of libpiekv.so, the B200 (sm_100a) paged KV-cache hot path.
+ *
+ * The reference (zyma98/pie) has no C FFI at this seam: its Python worker calls a
+ * module-level operator API (`ops.<name>`; the list of names a replacement must
+ * export is pie/src/flashinfer_metal/__init__.py:14-37).  Each entry point below
+ * names the reference call site it stands behind.  `pie_b200/ops.py` is the thin
+ * Python shim that keeps the reference's names and keyword arguments and forwards
+ * raw device pointers to these functions.
+ *
+ * Conventions
+ *   - every pointer named q/k/v/pool/out/indptr/... is a DEVICE pointer unless the
+ *     comment says "host";
+ *   - `stream` is a cudaStream_t passed as void*; every call is stream-ordered,
+ *     performs no device allocation and no synchronisation;
+ *   - strides are in ELEMENTS; the innermost (head_dim) axis is contiguous;
+ *   - `dtype` is one of PIEKV_F32 / PIEKV_F16 / PIEKV_BF16;
+ *   - return value: 0 ok; >0 invalid argument (checked on the host, nothing was
+ *     launched; text via piekv_last_error_string()); <0 is -(cudaError_t);
+ *   - `err` (nullable) is a device int32[4] "error word": a kernel that meets an
+ *     out-of-range index or gives up a bounded wait writes
+ *     {code, kernel id, index, value} there with an atomic compare-and-swap on
+ *     err[0] (first error wins) and skips the access.  Kernels never trap.
+ *   - KV pool layout (one layer): [num_pages, 2, page_size, num_kv_heads, head_dim],
+ *     "NHD", K at [:,0], V at [:,1]  (pie/src/pie_worker/model/llama3.py:959-979).
+ */
+#ifndef PIEKV_H_
+#define PIEKV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PIEKV_VERSION 100
+
+/* element types */
+#define PIEKV_F32 0
+#define PIEKV_F16 1
+#define PIEKV_BF16 2
+
+/* RoPE modes */
+#define PIEKV_ROPE_NONE 0    /* no rotation: pure append                                  */
+#define PIEKV_ROPE_PLAIN 1   /* f_i = theta^(-2i/D)                                       */
+#define PIEKV_ROPE_LLAMA31 2 /* plain + Llama-3.1 wavelength-dependent frequency scaling   */
+#define PIEKV_ROPE_TABLE 3   /* cos/sin read from a caller-supplied fp32 table            */
+
+/* device error-word codes (err[0]) */
+#define PIEKV_ERR_NONE 0
+#define PIEKV_ERR_BATCH_INDEX 1   /* batch_indices[i] outside [0,B)                         */
+#define PIEKV_ERR_PAGE_SLOT 2     /* position / page_size beyond the request's page list    */
+#define PIEKV_ERR_PAGE_ID 3       /* physical page id outside [0,num_pages)                 */
+#define PIEKV_ERR_LAST_PAGE_LEN 4 /* kv_last_page_len outside [1,page_size]                 */
+#define PIEKV_ERR_WAIT_TIMEOUT 5  /* a bounded on-chip wait ran out                         */
+#define PIEKV_ERR_TABLE_RANGE 6   /* RoPE table position outside [0,table_len)              */
+#define PIEKV_ERR_INDPTR 7        /* non-monotone indptr                                    */
+
+/* RoPE parameters.  Reference arguments: apply_llama31_rope_pos_ids_inplace(q, k,
+ * pos_ids, rope_scale, rope_theta, low_freq_factor, high_freq_factor, old_context_len)
+ * at pie/src/pie_worker/model/llama3.py:660-669; arithmetic restated in
+ * pie/src/flashinfer_metal/kernels/metal_rope.metal:58-106. */
+typedef struct piekv_rope_params {
+  int32_t mode;             /* PIEKV_ROPE_*                                               */
+  int32_t interleave;       /* 0: pairs (i, i+D/2)  (reference default); 1: pairs (2i,2i+1) */
+  float theta;              /* rope_theta                                                 */
+  float scale;              /* rope_scale / rope_factor (LLAMA31 only)                    */
+  float low_freq_factor;    /* LLAMA31 only                                               */
+  float high_freq_factor;   /* LLAMA31 only                                               */
+  float old_context_len;    /* LLAMA31 only                                               */
+  int32_t table_len;        /* rows of cos_sin_table (TABLE only)                         */
+  const float *cos_sin_table; /* device [table_len, D] fp32: cos in [:, :D/2], sin in [:, D/2:] */
+} piekv_rope_params;
+
+/* ---- library ------------------------------------------------------------------- */
+
+/* Version of this ABI (PIEKV_VERSION of the build). No reference counterpart. */
+int piekv_version(void);
+
+/* Text of the last >0 / <0 status returned on the calling thread. Reference: Python
+ * exceptions raised by the op library (pie/src/flashinfer_metal/ops.py:208-209). */
+const char *piekv_last_error_string(void);
+
+/* ---- metadata (device-resident) ------------------------------------------------- */
+
+/* seq_lens[b] = max(npages_b - 1, 0) * page_size + last_page_len[b]  (a request without pages
+ * keeps last_page_len, as in pie/src/pie_worker/batching.py:104-111).
+ * Replaces ops.get_seq_lens (call: llama3.py:745-749; restated ops.py:392-407). */
+int piekv_get_seq_lens(const int32_t *kv_indptr, const int32_t *kv_last_page_len, int32_t batch,
+                       int32_t page_size, int32_t *seq_lens_out, void *stream);
+
+/* For token i of request b: batch_indices[i] = b,
+ * positions[i] = seq_lens[b] - (indptr[b+1]-indptr[b]) + (i - indptr[b]).
+ * Replaces ops.get_batch_indices_positions (call: llama3.py:751-755; ops.py:410-436). */
+int piekv_get_batch_indices_positions(const int32_t *append_indptr, const int32_t *seq_lens,
+                                      int32_t batch, int32_t nnz, int32_t *batch_indices_out,
+                                      int32_t *positions_out, void *stream);
+
+/* Both of the above in one launch (seq_lens_out may be NULL). */
+int piekv_metadata(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                   const int32_t *kv_last_page_len, int32_t batch, int32_t nnz, int32_t page_size,
+                   int32_t *seq_lens_out, int32_t *batch_indices_out, int32_t *positions_out,
+                   void *stream);
+
+/* ---- RoPE and append ------------------------------------------------------------- */
+
+/* In-place rotary embedding of q [n,Hq,D] and k [n,Hkv,D] (either may be NULL).
+ * Replaces ops.apply_llama31_rope_pos_ids_inplace (llama3.py:660-669) and
+ * ops.apply_rope_pos_ids_inplace (qwen3.py:665-670). */
+int piekv_rope_inplace(void *q, void *k, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
+                       int64_t k_stride_h, const int32_t *pos_ids, int32_t nnz, int32_t num_qo_heads,
+                       int32_t num_kv_heads, int32_t head_dim, int32_t dtype,
+                       const piekv_rope_params *rope, int32_t *err, void *stream);
+
+/* Write k,v [n,Hkv,D] into the pool at page = kv_indices[kv_indptr[b] + pos/page_size],
+ * slot pos % page_size.  With rope->mode != NONE, k is rotated on the way (one
+ * rounding to the storage type) and, if q != NULL, q is rotated in place; with
+ * `rotate_k_in_place` != 0 the rotated k is also stored back over k (so the caller
+ * sees what the reference's two separate ops would leave behind).
+ * rope == NULL or mode NONE: exactly ops.append_paged_kv_cache (llama3.py:675-685;
+ * addressing restated in metal_append_paged_kv_cache.metal:45-105). */
+int piekv_rope_append(void *q, void *k, const void *v, int64_t q_stride_n, int64_t q_stride_h,
+                      int64_t k_stride_n, int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h,
+                      const int32_t *pos_ids, const int32_t *batch_indices, const int32_t *positions,
+                      void *pool, const int32_t *kv_indices, const int32_t *kv_indptr,
+                      const int32_t *kv_last_page_len, int32_t nnz, int32_t batch,
+                      int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
+                      int32_t num_pages, int32_t dtype, const piekv_rope_params *rope,
+                      int32_t rotate_k_in_place, int32_t *err, void *stream);
+
+/* ---- attention ------------------------------------------------------------------- */
+
+/* Bytes of scratch piekv_decode_run needs for `batch` requests (split-KV partials and
+ * per-request arrival counters).  The first `piekv_decode_counter_bytes(batch)` bytes hold
+ * the counters and must be zero before the first run; runs leave them zero.
+ * Reference: the 128 MiB workspace handed to the wrappers (llama3.py:230-232). */
+int64_t piekv_decode_workspace_bytes(int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
+                                     int32_t head_dim);
+int64_t piekv_decode_counter_bytes(int32_t batch);
+
+/* out[b,h,:] = softmax(q[b,h,:] . K_b^T * sm_scale) V_b over all cached tokens of request
+ * b, kv head = h / (Hq/Hkv).  `lse` (nullable) receives natural-log-sum-exp [batch,Hq] fp32.
+ * The work partition is computed on the device from kv_indptr, so there is no host plan
+ * step and the call can be captured in a CUDA graph whose index buffers change between
+ * replays.  Replaces BatchDecodeWithPagedKVCacheWrapper.plan/run
+ * (llama3.py:293-300,766-777,689). */
+int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                     void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                     const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                     int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                     int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
+                     int32_t *err, void *stream);
+
+/* Bytes of scratch piekv_prefill_run needs. */
+int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads,
+                                      int32_t head_dim);
+
+/* Packed variable-length attention over paged K/V: query token j of request b (rows
+ * qo_indptr[b]..qo_indptr[b+1]) attends to cached token t of that request when
+ *   (!causal || t <= kv_len_b - qo_len_b + j)  and
+ *   (custom_mask == NULL || custom_mask[off_b + j*kv_len_b + t] != 0),
+ * off_b = sum_{b'<b} qo_len_b' * kv_len_b'   (flat bool layout of
+ * pie/src/pie_worker/batching.py:113-135).
+ * Replaces BatchPrefillWithPagedKVCacheWrapper.plan/run (llama3.py:307-309,779-791,689). */
+int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                      void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
+                      const int32_t *kv_indices, const int32_t *kv_last_page_len,
+                      const uint8_t *custom_mask, int32_t causal, int32_t batch, int32_t nnz,
+                      int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
+                      int32_t page_size, int32_t num_pages, int32_t dtype, float sm_scale,
+                      void *workspace, int64_t workspace_bytes, int32_t *err, void *stream);
+
+/* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */
+
+/* For every pair j and every layer l: pool_l[dst[j], :, :valid_j] = pool_l[src[j], :, :valid_j]
+ * (valid_len == NULL copies whole pages).  `pools` is a HOST array of `num_layers` device
+ * pointers.  The reference never copies a page: Context::fork drops the partial last page
+ * and recomputes it (sdk/rust/inferlet/src/context.rs:147-225); this entry point is the
+ * copy-on-write that replaces that recomputation. */
+int piekv_copy_pages(void *const *pools, int32_t num_layers, const int32_t *src_pages,
+                     const int32_t *dst_pages, const int32_t *valid_len, int32_t count,
+                     int32_t page_size, int32_t num_kv_heads, int32_t head_dim, int32_t num_pages,
+                     int32_t dtype, int32_t *err, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PIEKV_H_ */

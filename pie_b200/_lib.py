@@ -1,0 +1,116 @@
+"""ctypes binding of libpiekv.so (the C ABI declared in include/piekv.h).
+
+The library is the only implementation: there is no Python or CPU fallback.  If the shared
+object is missing or a symbol is absent, import fails with an explicit error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libpiekv.so"
+
+PIEKV_F32, PIEKV_F16, PIEKV_BF16 = 0, 1, 2
+ROPE_NONE, ROPE_PLAIN, ROPE_LLAMA31, ROPE_TABLE = 0, 1, 2, 3
+
+ERR_NAMES = {
+    0: "ok",
+    1: "batch index out of range",
+    2: "position beyond the request's page list",
+    3: "physical page id out of range",
+    4: "kv_last_page_len out of range",
+    5: "bounded on-chip wait timed out",
+    6: "RoPE table position out of range",
+    7: "non-monotone indptr",
+}
+
+
+class RopeParams(C.Structure):
+    """Mirror of `piekv_rope_params`."""
+
+    _fields_ = [
+        ("mode", C.c_int32),
+        ("interleave", C.c_int32),
+        ("theta", C.c_float),
+        ("scale", C.c_float),
+        ("low_freq_factor", C.c_float),
+        ("high_freq_factor", C.c_float),
+        ("old_context_len", C.c_float),
+        ("table_len", C.c_int32),
+        ("cos_sin_table", C.c_void_p),
+    ]
+
+
+_p = C.c_void_p
+_i32 = C.c_int32
+_i64 = C.c_int64
+_f32 = C.c_float
+
+# name -> (restype, argtypes); must list every function declared in include/piekv.h
+SIGNATURES = {
+    "piekv_version": (C.c_int, []),
+    "piekv_last_error_string": (C.c_char_p, []),
+    "piekv_get_seq_lens": (C.c_int, [_p, _p, _i32, _i32, _p, _p]),
+    "piekv_get_batch_indices_positions": (C.c_int, [_p, _p, _i32, _i32, _p, _p, _p]),
+    "piekv_metadata": (C.c_int, [_p, _p, _p, _i32, _i32, _i32, _p, _p, _p, _p]),
+    "piekv_rope_inplace": (
+        C.c_int,
+        [_p, _p, _i64, _i64, _i64, _i64, _p, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _p, _p],
+    ),
+    "piekv_rope_append": (
+        C.c_int,
+        [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
+         _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _i32, _p, _p],
+    ),
+    "piekv_decode_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
+    "piekv_decode_counter_bytes": (_i64, [_i32]),
+    "piekv_decode_run": (
+        C.c_int,
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p],
+    ),
+    "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
+    "piekv_prefill_run": (
+        C.c_int,
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+         _f32, _p, _i64, _p, _p],
+    ),
+    "piekv_copy_pages": (
+        C.c_int,
+        [C.POINTER(C.c_void_p), _i32, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _p, _p],
+    ),
+}
+
+
+class PiekvError(RuntimeError):
+    """A libpiekv call returned a non-zero status."""
+
+
+def _load() -> C.CDLL:
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m pie_b200.build` "
+            "(nvcc, sm_100a). pie_b200 has no fallback implementation."
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:  # pragma: no cover
+            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it") from e
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+def check(status: int, what: str) -> None:
+    """Raise on a non-zero status, with the library's message."""
+    if status == 0:
+        return
+    msg = lib.piekv_last_error_string()
+    text = msg.decode("utf-8", "replace") if msg else ""
+    if status > 0:
+        raise ValueError(f"{what}: {text}")
+    raise PiekvError(f"{what}: {text} (status {status})")

@@ -1,0 +1,36 @@
+// Argument block shared by the attention kernels and their launchers.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace piekv {
+
+struct AttnArgs {
+  const void *q;  // [nnz, Hq, D], strides q_sn / q_sh (elements)
+  int64_t q_sn, q_sh;
+  const void *pool;            // [num_pages, 2, page_size, Hkv, D]
+  void *out;                   // [nnz, Hq, D] contiguous
+  float *lse;                  // nullable [nnz, Hq]
+  const int32_t *qo_indptr;    // nullable: decode (one row per request)
+  const int32_t *kv_indptr;    // [batch+1]
+  const int32_t *kv_indices;   // [kv_indptr[batch]]
+  const int32_t *kv_last_page_len;  // [batch]
+  const uint8_t *mask;         // nullable flat bool mask
+  int causal;
+  int batch, nnz, hq, hkv, dim, page_size, num_pages;
+  float sm_scale;
+  int32_t *err;
+};
+
+// any dtype / shape
+int launch_attn_generic(const AttnArgs &a, int dtype, cudaStream_t st);
+
+// tuned decode (16-bit, D=128, page 16): returns 0 on launch, >0 / <0 on error
+bool decode_tma_supported(const AttnArgs &a, int dtype);
+int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st);
+
+// tuned prefill (tcgen05): 16-bit, D=128, page 16
+bool prefill_tc_supported(const AttnArgs &a, int dtype);
+int launch_prefill_tc(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st);
+
+}  // namespace piekv

@@ -1,0 +1,530 @@
+// Paged decode attention for 16-bit K/V, head_dim 128, page_size 16 on sm_100a.
+//
+// Work partition (on the device, no host plan): the flat list of all requests' pages
+// (kv_indices[0 .. kv_indptr[B])) is cut into gridDim.x equal contiguous ranges, one per
+// CTA (one CTA per SM).  A CTA therefore streams the same number of pages whatever the
+// mix of context lengths; where a range crosses a request boundary the CTA closes one
+// "segment" and opens the next.  A request cut across CTAs is finished by whichever CTA
+// delivers its last segment (per-request arrival counter), which merges the partial
+// (max, sum, accumulator) triples from scratch memory.
+//
+// Data path: a producer warp gathers pages with TMA.  A page holds K [16, Hkv, 128] then
+// V [16, Hkv, 128]; one 5-D tensor-map box {64 d, 16 tokens, 2 d-halves, Hkv heads, K|V}
+// moves the whole page (Hkv * 8 KiB) and lands it in shared memory regrouped per head as
+// 128-byte-swizzled [token][64 d] tiles, which is the layout ldmatrix wants.  A stage is
+// always 64 KiB = 8 (page, head) tiles: 8/Hkv pages for Hkv heads.  Three stages keep
+// 128-192 KiB per SM in flight.
+//
+// Math: consumer warp w owns tile (page w / Hkv, head w % Hkv).  The GQA group's query
+// heads (<= 16) are the M rows of m16n8k16 tensor-core MMAs: S = Q K^T (16 x 16 tokens),
+// fp32 online softmax in the base-2 domain with quad shuffles, O += P V.
+#include <cuda.h>
+
+#include "attn.cuh"
+#include "common.cuh"
+
+namespace piekv {
+
+namespace {
+
+constexpr int kDim = 128;
+constexpr int kPage = 16;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kStages = 3;
+constexpr int kTileBytes = 8192;               // one (page, head): K 4 KiB + V 4 KiB
+constexpr int kStageBytes = 8 * kTileBytes;    // 64 KiB
+constexpr int kCounterBytes = 65536;           // head of the workspace: arrival counters
+constexpr int kMaxBatch = kCounterBytes / 4;
+
+struct DecodeParams {
+  AttnArgs a;
+  float *part_o;    // [slot][PG][Hq][128]
+  float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
+  int *counters;    // [batch], zero between launches
+};
+
+__device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap *tmap, int coord4, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(0), "r"(0), "r"(0), "r"(0), "r"(coord4), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32)); }
+
+// CTA that owns flat page g when T pages are cut into G ranges [c*T/G, (c+1)*T/G).
+__device__ __forceinline__ int cta_of_page(long long g, long long T, long long G) {
+  return (int)(((g + 1) * G - 1) / T);
+}
+
+// last request whose first page index is <= g, skipping empty requests after it
+__device__ __forceinline__ int request_of_page(const int32_t *indptr, int batch, int g) {
+  int lo = 0, hi = batch;  // first b with indptr[b+1] > g
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (indptr[mid + 1] > g)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  return lo;
+}
+
+template <typename T, int HKV>
+__global__ void __launch_bounds__(kThreads, 1)
+    decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, DecodeParams p) {
+  constexpr int PG = 8 / HKV;  // pages per stage
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kStages];
+  __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ int sh_abort;
+  __shared__ int sh_last;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t stage0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t *stage0_ptr = smem_raw + (stage0 - smem_u32(smem_raw));
+
+  const AttnArgs &a = p.a;
+  const int B = a.batch;
+  const int G = gridDim.x;
+  const int c = blockIdx.x;
+  const int total_pages = a.kv_indptr[B];
+  const int lo = (int)((long long)c * total_pages / G);
+  const int hi = (int)((long long)(c + 1) * total_pages / G);
+  const int group = a.hq / HKV;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kConsumerWarps);
+    }
+    sh_abort = 0;
+    sh_last = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ------------------------------------------------------------------ producer
+    int armed = 0;  // stages armed so far
+    if (lo < hi) {
+      int b = request_of_page(a.kv_indptr, B, lo);
+      int g = lo;
+      bool stop = false;
+      while (g < hi && !stop) {
+        while (b < B - 1 && a.kv_indptr[b + 1] <= g) ++b;
+        const int seg_end = min(hi, a.kv_indptr[b + 1]);
+        if (seg_end <= g) {  // non-monotone indptr: give up cleanly
+          if (lane == 0) report_error(a.err, PIEKV_ERR_INDPTR, KID_DECODE, b, g);
+          if (lane == 0) atomicExch(&sh_abort, 1);
+          break;
+        }
+        while (g < seg_end) {
+          const int npg = min(PG, seg_end - g);
+          // page ids first, so the load is in flight while we wait for the stage
+          int page = lane < npg ? __ldg(a.kv_indices + g + lane) : 0;
+          const int s = armed % kStages;
+          const uint32_t ph = (armed / kStages) & 1;
+          if (*(volatile int *)&sh_abort) {
+            stop = true;
+            break;
+          }
+          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+            if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 100 + s);
+            if (lane == 0) atomicExch(&sh_abort, 1);
+            stop = true;
+            break;
+          }
+          if (lane < npg && (page < 0 || page >= a.num_pages)) {
+            report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
+            page = a.num_pages;  // outside the tensor map: the box is zero-filled
+          }
+          if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(npg * HKV * kTileBytes));
+          __syncwarp();
+          if (lane < npg) {
+            tma_load_page(stage0 + s * kStageBytes + lane * (HKV * kTileBytes), &tmap, page * 2, &full_bar[s]);
+          }
+          g += npg;
+          ++armed;
+        }
+      }
+    }
+    // Drain: do not let the CTA retire while a bulk copy may still be landing.
+    __syncwarp();
+    if (lane == 0) {
+      const int first = armed > kStages ? armed - kStages : 0;
+      for (int it = first; it < armed; ++it) {
+        mbar_wait(&full_bar[it % kStages], (it / kStages) & 1, 200000000ull);
+      }
+    }
+    return;
+  }
+
+  // -------------------------------------------------------------------- consumers
+  const int tid = threadIdx.x;   // 0..255
+  const int pslot = warp / HKV;  // page slot within a stage
+  const int h = warp % HKV;      // kv head
+  const int quad = lane >> 2;    // MMA row (and row + 8)
+  const int qlane = lane & 3;
+  const float scale_log2 = a.sm_scale * 1.4426950408889634f;
+  T *out = reinterpret_cast<T *>(a.out);
+
+  // requests without any page: softmax over nothing -> zeros
+  for (int b = c; b < B; b += G) {
+    if (a.kv_indptr[b + 1] == a.kv_indptr[b]) {
+      for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32)
+        out[(size_t)b * a.hq * kDim + x] = Elem<T>::from_f32(0.f);
+      if (a.lse != nullptr)
+        for (int x = tid; x < a.hq; x += kConsumerWarps * 32) a.lse[(size_t)b * a.hq + x] = -INFINITY;
+    }
+  }
+  if (lo >= hi) return;
+
+  uint32_t qa[8][4];
+  float o[16][4];
+  int b = request_of_page(a.kv_indptr, B, lo);
+  int g = lo;
+  int it = 0;
+  bool aborted = false;
+
+  while (g < hi) {
+    // ================= open the segment of request b that starts at flat page g
+    while (b < B - 1 && a.kv_indptr[b + 1] <= g) ++b;
+    const int req_begin = a.kv_indptr[b];
+    const int req_end = a.kv_indptr[b + 1];
+    const int seg_end = min(hi, req_end);
+    if (seg_end <= g) break;  // non-monotone indptr (the producer reports it)
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    {
+      // query fragments of this head's group (rows beyond the group are zero)
+      const T *qb = reinterpret_cast<const T *>(a.q) + (size_t)b * a.q_sn + (size_t)(h * group) * a.q_sh;
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const int col = ks * 16 + qlane * 2;
+        const uint32_t *r0 = reinterpret_cast<const uint32_t *>(qb + (size_t)quad * a.q_sh + col);
+        const uint32_t *r1 = reinterpret_cast<const uint32_t *>(qb + (size_t)(quad + 8) * a.q_sh + col);
+        qa[ks][0] = quad < group ? __ldg(r0) : 0u;
+        qa[ks][1] = quad + 8 < group ? __ldg(r1) : 0u;
+        qa[ks][2] = quad < group ? __ldg(r0 + 4) : 0u;
+        qa[ks][3] = quad + 8 < group ? __ldg(r1 + 4) : 0u;
+      }
+    }
+    int last_len = a.kv_last_page_len[b];
+    if (last_len < 1 || last_len > kPage) {
+      if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
+      last_len = last_len < 1 ? 1 : kPage;
+    }
+
+    // ================= stream the segment's pages
+    while (g < seg_end) {
+      const int npg = min(PG, seg_end - g);
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1;
+      if (!aborted && *(volatile int *)&sh_abort) aborted = true;
+      if (!aborted && !mbar_wait(&full_bar[s], ph)) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
+        if (lane == 0) atomicExch(&sh_abort, 1);
+        aborted = true;
+      }
+      if (!aborted && pslot < npg) {
+        const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
+        const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
+        const uint32_t ktile = page_base + h * 4096;
+        const uint32_t vtile = page_base + HKV * 4096 + h * 4096;
+        if (valid < kPage) {
+          // rows past the end of the context may hold anything: zero the V rows so that
+          // 0 * garbage cannot produce NaN (their scores are masked to -inf below)
+          uint8_t *vptr = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + HKV * 4096 + h * 4096;
+          for (int x = lane; x < (kPage - valid) * 16; x += 32) {
+            const int row = valid + (x >> 4);
+            const int hf = (x >> 3) & 1;
+            const int ch = x & 7;
+            *reinterpret_cast<uint4 *>(vptr + hf * 2048 + row * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+        // ---- S = Q K^T : 16 rows x 16 tokens
+        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+          const int mi = lane >> 3, r = lane & 7;
+          const int t = (mi >> 1) * 8 + r;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const int hf = ks >> 2;
+            const int ch = (ks & 3) * 2 + (mi & 1);
+            uint32_t kb[4];
+            ldmatrix_x4(kb, ktile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
+            mma_16816<T>(sc[0], qa[ks], kb[0], kb[1]);
+            mma_16816<T>(sc[1], qa[ks], kb[2], kb[3]);
+          }
+        }
+        // ---- online softmax (base 2); rows quad and quad+8, tokens nt*8 + qlane*2 + {0,1}
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int tok = nt * 8 + qlane * 2 + e;
+            const bool ok = tok < valid;
+            sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
+            sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+            mx0 = fmaxf(mx0, sc[nt][e]);
+            mx1 = fmaxf(mx1, sc[nt][2 + e]);
+          }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float mu0 = mn0 == -INFINITY ? 0.f : mn0;
+        const float mu1 = mn1 == -INFINITY ? 0.f : mn1;
+        const float al0 = fast_exp2(m0 - mu0), al1 = fast_exp2(m1 - mu1);
+        m0 = mn0;
+        m1 = mn1;
+        float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            sc[nt][e] = fast_exp2(sc[nt][e] - mu0);
+            sc[nt][2 + e] = fast_exp2(sc[nt][2 + e] - mu1);
+            ps0 += sc[nt][e];
+            ps1 += sc[nt][2 + e];
+          }
+        }
+        l0 = l0 * al0 + ps0;
+        l1 = l1 * al1 + ps1;
+        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+          for (int nt = 0; nt < 16; ++nt) {
+            o[nt][0] *= al0;
+            o[nt][1] *= al0;
+            o[nt][2] *= al1;
+            o[nt][3] *= al1;
+          }
+        }
+        // ---- O += P V
+        uint32_t pa[4];
+        pa[0] = pack2<T>(sc[0][0], sc[0][1]);
+        pa[1] = pack2<T>(sc[0][2], sc[0][3]);
+        pa[2] = pack2<T>(sc[1][0], sc[1][1]);
+        pa[3] = pack2<T>(sc[1][2], sc[1][3]);
+        {
+          const int mi = lane >> 3, r = lane & 7;
+          const int t = (mi & 1) * 8 + r;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int hf = i >> 2;
+            const int ch = (i & 3) * 2 + (mi >> 1);
+            uint32_t vb[4];
+            ldmatrix_x4_trans(vb, vtile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
+            mma_16816<T>(o[2 * i], pa, vb[0], vb[1]);
+            mma_16816<T>(o[2 * i + 1], pa, vb[2], vb[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0 && !aborted) mbar_arrive(&empty_bar[s]);
+      g += npg;
+      ++it;
+    }
+
+    // ================= close the segment: publish the result or the partial
+    const int c_first = cta_of_page(req_begin, total_pages, G);
+    const int c_last = cta_of_page(req_end - 1, total_pages, G);
+    const int nseg = c_last - c_first + 1;
+    float ls0 = l0, ls1 = l1;  // quad-reduce the running sums
+    ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
+    ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
+    ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
+    ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
+    if (PG == 1 && nseg == 1) {
+      // the whole request lived in this CTA: normalise and store
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int row = quad + half * 8;
+        if (row < group) {
+          const int qh = h * group + row;
+          const float lsum = half ? ls1 : ls0;
+          const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+          uint32_t *orow = reinterpret_cast<uint32_t *>(out + ((size_t)b * a.hq + qh) * kDim);
+#pragma unroll
+          for (int nt = 0; nt < 16; ++nt)
+            orow[nt * 4 + qlane] = pack2<T>(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+          if (a.lse != nullptr && qlane == 0) {
+            const float mm = half ? m1 : m0;
+            a.lse[(size_t)b * a.hq + qh] = lsum > 0.f ? (mm + log2f(lsum)) * 0.6931471805599453f : -INFINITY;
+          }
+        }
+      }
+      continue;
+    }
+    const size_t pidx = (size_t)(c + b) * PG + pslot;
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = quad + half * 8;
+      if (row < group) {
+        const int qh = h * group + row;
+        float2 *orow = reinterpret_cast<float2 *>(p.part_o + (pidx * a.hq + qh) * kDim);
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) orow[nt * 4 + qlane] = make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
+        if (qlane == 0) p.part_ml[pidx * a.hq + qh] = make_float2(half ? m1 : m0, half ? ls1 : ls0);
+      }
+    }
+    __threadfence();
+    consumer_bar_sync();
+    if (tid == 0) {
+      const int old = atomicAdd(&p.counters[b], 1);
+      sh_last = (old == nseg - 1) ? 1 : 0;
+    }
+    consumer_bar_sync();
+    const bool last = sh_last != 0;
+    consumer_bar_sync();  // everyone has read sh_last before a later segment rewrites it
+    if (!last) continue;
+    __threadfence();
+    // merge every partial of request b: thread -> (query head tid/32 + 8k, 4 consecutive d)
+    const int d4 = (tid & 31) * 4;
+    for (int qh = tid >> 5; qh < a.hq; qh += kConsumerWarps) {
+      float M = -INFINITY, L = 0.f;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int cc = c_first; cc <= c_last; ++cc) {
+        for (int sub = 0; sub < PG; ++sub) {
+          const size_t idx = ((size_t)(cc + b) * PG + sub) * a.hq + qh;
+          const float2 ml = __ldcg(p.part_ml + idx);
+          if (!(ml.y > 0.f)) continue;  // that warp saw no page of the segment
+          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
+          const float Mn = fmaxf(M, ml.x);
+          const float w_old = fast_exp2(M - Mn);
+          const float w_new = fast_exp2(ml.x - Mn);
+          L = L * w_old + ml.y * w_new;
+          acc.x = acc.x * w_old + po.x * w_new;
+          acc.y = acc.y * w_old + po.y * w_new;
+          acc.z = acc.z * w_old + po.z * w_new;
+          acc.w = acc.w * w_old + po.w * w_new;
+          M = Mn;
+        }
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      uint2 pk;
+      pk.x = pack2<T>(acc.x * inv, acc.y * inv);
+      pk.y = pack2<T>(acc.z * inv, acc.w * inv);
+      *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
+      if (a.lse != nullptr && (tid & 31) == 0)
+        a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+    }
+    if (tid == 0) p.counters[b] = 0;  // leave the counter ready for the next launch
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void *sym = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+      qres != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = reinterpret_cast<EncodeTiledFn>(sym);
+  return fn;
+}
+
+// Pool [P, 2, 16, Hkv, 128] seen as {64 d, 16 tokens, 2 d-halves, Hkv, 2P (page, K|V)}.
+int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int hkv, int dtype) {
+  EncodeTiledFn enc = get_encode_fn();
+  PIEKV_REQUIRE(enc != nullptr, "decode: cuTensorMapEncodeTiled is not available from the driver");
+  const cuuint64_t row = (cuuint64_t)hkv * kDim * 2;  // bytes of one token row (all heads)
+  cuuint64_t gdim[5] = {64, (cuuint64_t)kPage, 2, (cuuint64_t)hkv, (cuuint64_t)num_pages * 2};
+  cuuint64_t gstr[4] = {row, 128, 256, (cuuint64_t)kPage * row};
+  cuuint32_t box[5] = {64, (cuuint32_t)kPage, 2, (cuuint32_t)hkv, 2};
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = enc(tm, dtype == PIEKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
+                   const_cast<void *>(pool), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PIEKV_REQUIRE(r == CUDA_SUCCESS, "decode: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return 0;
+}
+
+template <typename T, int HKV>
+int launch_t(const CUtensorMap &tm, const DecodeParams &p, cudaStream_t st) {
+  static bool configured = false;  // per (T, HKV) instantiation
+  const int smem = kStages * kStageBytes + 1024;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<T, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return cuda_status(e, "decode: cudaFuncSetAttribute");
+    configured = true;
+  }
+  decode_tma_kernel<T, HKV><<<sm_count(), kThreads, smem, st>>>(tm, p);
+  PIEKV_LAUNCH_CHECK("decode_tma_kernel");
+  return 0;
+}
+
+template <typename T>
+int launch_h(const CUtensorMap &tm, const DecodeParams &p, cudaStream_t st) {
+  switch (p.a.hkv) {
+    case 1:
+      return launch_t<T, 1>(tm, p, st);
+    case 2:
+      return launch_t<T, 2>(tm, p, st);
+    case 4:
+      return launch_t<T, 4>(tm, p, st);
+    case 8:
+      return launch_t<T, 8>(tm, p, st);
+  }
+  set_error("decode: unsupported num_kv_heads %d", p.a.hkv);
+  return 1;
+}
+
+}  // namespace
+
+bool decode_tma_supported(const AttnArgs &a, int dtype) {
+  if (dtype != PIEKV_BF16 && dtype != PIEKV_F16) return false;
+  if (a.dim != kDim || a.page_size != kPage) return false;
+  if (!(a.hkv == 1 || a.hkv == 2 || a.hkv == 4 || a.hkv == 8)) return false;
+  if (a.hq % a.hkv != 0 || a.hq / a.hkv > 16) return false;
+  if (a.batch > kMaxBatch) return false;
+  if ((reinterpret_cast<uintptr_t>(a.pool) & 15) || (reinterpret_cast<uintptr_t>(a.q) & 3) ||
+      (reinterpret_cast<uintptr_t>(a.out) & 15))
+    return false;
+  if ((a.q_sn & 1) || (a.q_sh & 1)) return false;
+  return true;
+}
+
+int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
+  const int pg = (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8) ? 8 / hkv : 1;
+  const int64_t slots = (int64_t)sm_count() + batch;
+  return kCounterBytes + slots * pg * hq * (kDim * 4 + 8) + 256;
+}
+
+int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st) {
+  if (a.batch == 0) return 0;
+  const int pg = 8 / a.hkv;
+  const int64_t slots = (int64_t)sm_count() + a.batch;
+  const int64_t need = decode_tma_workspace_bytes(a.batch, a.hq, a.hkv);
+  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "decode: workspace too small (%lld < %lld bytes)",
+                (long long)workspace_bytes, (long long)need);
+  PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
+  DecodeParams p;
+  p.a = a;
+  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+  p.counters = reinterpret_cast<int *>(ws);
+  p.part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
+  const int64_t ml_bytes = ((slots * pg * a.hq * 8 + 255) / 256) * 256;
+  p.part_o = reinterpret_cast<float *>(ws + kCounterBytes + ml_bytes);
+  CUtensorMap tm;
+  if (int rc = make_page_tensor_map(&tm, a.pool, a.num_pages, a.hkv, dtype)) return rc;
+  if (dtype == PIEKV_BF16) return launch_h<__nv_bfloat16>(tm, p, st);
+  return launch_h<__half>(tm, p, st);
+}
+
+}  // namespace piekv

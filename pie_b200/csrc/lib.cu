@@ -1,0 +1,40 @@
+// Library-level plumbing: version, per-thread error text, device property cache.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace piekv {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int cuda_status(cudaError_t e, const char *what) {
+  if (e == cudaSuccess) return 0;
+  set_error("%s: CUDA error %d (%s)", what, (int)e, cudaGetErrorString(e));
+  return -(int)e;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace piekv
+
+extern "C" int piekv_version(void) { return PIEKV_VERSION; }
+
+extern "C" const char *piekv_last_error_string(void) { return piekv::g_err; }

@@ -1,0 +1,549 @@
+"""Paged-KV operator API of the reference, backed by libpiekv.so.
+
+This module keeps the names and keyword arguments that Pie's Python worker uses at its
+single op seam (`from flashinfer import ...` / `flashinfer_metal as ops`,
+pie/src/pie_worker/model/llama3.py:18-21; exported names
+pie/src/flashinfer_metal/__init__.py:14-37), so `import pie_b200.ops as ops` is a drop-in
+for that path:
+
+    get_seq_lens, get_batch_indices_positions,
+    apply_rope_pos_ids_inplace, apply_llama31_rope_pos_ids_inplace,
+    append_paged_kv_cache,
+    BatchDecodeWithPagedKVCacheWrapper, BatchPrefillWithPagedKVCacheWrapper
+
+plus the fused / extended entry points this library adds (`rope_append_paged_kv_cache`,
+`copy_kv_pages`).  Every function forwards raw device pointers and the current CUDA stream
+to the C ABI; nothing here computes on the host and there is no fallback path.
+Error behaviour follows the reference facade: wrong device / dtype / shape raise
+`ValueError`, `run()` before `plan()` raises `RuntimeError("Must call plan() before run()")`
+(pie/src/flashinfer_metal/ops.py:186-190,208-209).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from dataclasses import dataclass
+from typing import Optional, Sequence, Tuple
+
+import torch
+
+from . import _lib
+from ._lib import RopeParams, check, lib
+
+__all__ = [
+    "BatchPrefillWithPagedKVCacheWrapper",
+    "BatchDecodeWithPagedKVCacheWrapper",
+    "apply_rope_pos_ids_inplace",
+    "apply_llama31_rope_pos_ids_inplace",
+    "append_paged_kv_cache",
+    "get_seq_lens",
+    "get_batch_indices_positions",
+    "rope_append_paged_kv_cache",
+    "copy_kv_pages",
+    "RopeConfig",
+    "device_error",
+    "COUNTER_BYTES",
+]
+
+COUNTER_BYTES = 65536  # head of every workspace: split-KV arrival counters, kept zero
+
+_DTYPES = {torch.float32: _lib.PIEKV_F32, torch.float16: _lib.PIEKV_F16, torch.bfloat16: _lib.PIEKV_BF16}
+
+
+# ---------------------------------------------------------------------------------------
+# helpers
+# ---------------------------------------------------------------------------------------
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise ValueError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be on a CUDA device, got {t.device}")
+
+
+def _require_i32(t: torch.Tensor, name: str) -> None:
+    _require_cuda(t, name)
+    if t.dtype != torch.int32:
+        raise ValueError(f"{name} must be int32, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+
+
+def _dtype_code(dt: torch.dtype, name: str) -> int:
+    try:
+        return _DTYPES[dt]
+    except KeyError:
+        raise ValueError(f"{name}: unsupported dtype {dt} (float32, float16, bfloat16)") from None
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _rows(t: torch.Tensor, name: str) -> Tuple[int, int]:
+    """(token stride, head stride) in elements of a [n, H, D] tensor whose last axis is contiguous."""
+    if t.dim() != 3:
+        raise ValueError(f"{name} must be [tokens, heads, head_dim], got shape {tuple(t.shape)}")
+    if t.shape[2] > 1 and t.stride(2) != 1:
+        raise ValueError(f"{name}: head_dim axis must be contiguous")
+    return t.stride(0), t.stride(1)
+
+
+_ERR_WORDS: dict = {}
+
+
+def _err_word(device: torch.device) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    w = _ERR_WORDS.get(key)
+    if w is None:
+        w = torch.zeros(4, dtype=torch.int32, device=device)
+        _ERR_WORDS[key] = w
+    return w
+
+
+def device_error(device=None, clear: bool = True) -> Optional[dict]:
+    """Read the device error word (synchronises).  None when no kernel reported a fault."""
+    device = torch.device(device if device is not None else "cuda")
+    w = _err_word(device)
+    vals = w.cpu().tolist()
+    if vals[0] == 0:
+        return None
+    if clear:
+        w.zero_()
+    return {
+        "code": vals[0],
+        "what": _lib.ERR_NAMES.get(vals[0], "unknown"),
+        "kernel": vals[1],
+        "index": vals[2],
+        "value": vals[3],
+    }
+
+
+def _check_pool(pool: torch.Tensor, name: str = "paged_kv_cache"):
+    if isinstance(pool, (tuple, list)):
+        raise ValueError(f"{name}: separate (k_cache, v_cache) tensors are not supported; pass the "
+                         "combined [pages, 2, page_size, kv_heads, head_dim] tensor")
+    _require_cuda(pool, name)
+    if pool.dim() != 5 or pool.shape[1] != 2:
+        raise ValueError(f"{name} must be [pages, 2, page_size, kv_heads, head_dim], got {tuple(pool.shape)}")
+    if not pool.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    return pool.shape[0], pool.shape[2], pool.shape[3], pool.shape[4]
+
+
+@dataclass
+class RopeConfig:
+    """Rotary-embedding parameters (defaults: the reference's Llama-3 model config,
+    pie/src/pie_worker/model/llama3.py:167-173).  `mode`: "none" | "plain" | "llama31" | "table"."""
+
+    mode: str = "llama31"
+    theta: float = 500000.0
+    scale: float = 8.0
+    low_freq_factor: float = 1.0
+    high_freq_factor: float = 4.0
+    old_context_len: float = 8192.0
+    interleave: bool = False
+    cos_sin_table: Optional[torch.Tensor] = None  # fp32 [positions, head_dim]: cos | sin
+
+    def to_c(self, head_dim: int) -> RopeParams:
+        modes = {"none": _lib.ROPE_NONE, "plain": _lib.ROPE_PLAIN, "llama31": _lib.ROPE_LLAMA31,
+                 "table": _lib.ROPE_TABLE}
+        if self.mode not in modes:
+            raise ValueError(f"unknown rope mode {self.mode!r}")
+        rp = RopeParams()
+        rp.mode = modes[self.mode]
+        rp.interleave = 1 if self.interleave else 0
+        rp.theta = float(self.theta)
+        rp.scale = float(self.scale)
+        rp.low_freq_factor = float(self.low_freq_factor)
+        rp.high_freq_factor = float(self.high_freq_factor)
+        rp.old_context_len = float(self.old_context_len)
+        rp.table_len = 0
+        rp.cos_sin_table = None
+        if self.mode == "table":
+            t = self.cos_sin_table
+            if t is None:
+                raise ValueError("rope mode 'table' needs cos_sin_table")
+            _require_cuda(t, "cos_sin_table")
+            if t.dtype != torch.float32 or t.dim() != 2 or t.shape[1] != head_dim or not t.is_contiguous():
+                raise ValueError("cos_sin_table must be contiguous float32 [positions, head_dim]")
+            rp.table_len = t.shape[0]
+            rp.cos_sin_table = t.data_ptr()
+        return rp
+
+
+# ---------------------------------------------------------------------------------------
+# metadata
+# ---------------------------------------------------------------------------------------
+def get_seq_lens(kv_page_indptr: torch.Tensor, kv_last_page_lens: torch.Tensor, page_size: int) -> torch.Tensor:
+    """Sequence length of every request from its page count and last-page fill.
+
+    Reference call: pie/src/pie_worker/model/llama3.py:745-749."""
+    _require_i32(kv_page_indptr, "kv_page_indptr")
+    _require_i32(kv_last_page_lens, "kv_last_page_lens")
+    batch = kv_page_indptr.shape[0] - 1
+    if kv_last_page_lens.shape[0] < batch:
+        raise ValueError("kv_last_page_lens shorter than the batch")
+    out = torch.empty(batch, dtype=torch.int32, device=kv_page_indptr.device)
+    check(lib.piekv_get_seq_lens(kv_page_indptr.data_ptr(), kv_last_page_lens.data_ptr(), batch, int(page_size),
+                                 out.data_ptr(), _stream(out.device)), "get_seq_lens")
+    return out
+
+
+def get_batch_indices_positions(append_indptr: torch.Tensor, seq_lens: torch.Tensor, nnz: int
+                                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Request index and KV slot of every appended token.
+
+    Reference call: pie/src/pie_worker/model/llama3.py:751-755."""
+    _require_i32(append_indptr, "append_indptr")
+    _require_i32(seq_lens, "seq_lens")
+    batch = append_indptr.shape[0] - 1
+    dev = append_indptr.device
+    bi = torch.empty(nnz, dtype=torch.int32, device=dev)
+    pos = torch.empty(nnz, dtype=torch.int32, device=dev)
+    check(lib.piekv_get_batch_indices_positions(append_indptr.data_ptr(), seq_lens.data_ptr(), batch, int(nnz),
+                                                bi.data_ptr(), pos.data_ptr(), _stream(dev)),
+          "get_batch_indices_positions")
+    return bi, pos
+
+
+# ---------------------------------------------------------------------------------------
+# RoPE / append
+# ---------------------------------------------------------------------------------------
+def _rope_inplace(q, k, pos_ids, cfg: RopeConfig, who: str) -> None:
+    _require_cuda(q, "q")
+    _require_cuda(k, "k")
+    _require_i32(pos_ids, "pos_ids")
+    if q.dtype != k.dtype:
+        raise ValueError(f"{who}: q and k dtypes differ ({q.dtype} vs {k.dtype})")
+    qs, ks = _rows(q, "q"), _rows(k, "k")
+    n, hq, d = q.shape
+    if k.shape[0] != n or k.shape[2] != d or pos_ids.shape[0] != n:
+        raise ValueError(f"{who}: q {tuple(q.shape)}, k {tuple(k.shape)}, pos_ids {tuple(pos_ids.shape)} disagree")
+    rp = cfg.to_c(d)
+    check(lib.piekv_rope_inplace(q.data_ptr(), k.data_ptr(), qs[0], qs[1], ks[0], ks[1], pos_ids.data_ptr(), n, hq,
+                                 k.shape[1], d, _dtype_code(q.dtype, who), C.byref(rp),
+                                 _err_word(q.device).data_ptr(), _stream(q.device)), who)
+
+
+def apply_rope_pos_ids_inplace(q: torch.Tensor, k: torch.Tensor, pos_ids: torch.Tensor,
+                               rotary_dim: Optional[int] = None, interleave: bool = False,
+                               rope_scale: float = 1.0, rope_theta: float = 10000.0) -> None:
+    """Plain rotary embedding in place (reference call: pie/src/pie_worker/model/qwen3.py:665-670)."""
+    if rotary_dim is not None and rotary_dim != q.shape[-1]:
+        raise ValueError("rotary_dim smaller than head_dim is not supported")
+    cfg = RopeConfig(mode="plain", theta=rope_theta, scale=rope_scale, interleave=interleave)
+    _rope_inplace(q, k, pos_ids, cfg, "apply_rope_pos_ids_inplace")
+
+
+def apply_llama31_rope_pos_ids_inplace(q: torch.Tensor, k: torch.Tensor, pos_ids: torch.Tensor,
+                                       rotary_dim: Optional[int] = None, interleave: bool = False,
+                                       rope_scale: float = 8.0, rope_theta: float = 500000.0,
+                                       low_freq_factor: float = 1.0, high_freq_factor: float = 4.0,
+                                       old_context_len: int = 8192) -> None:
+    """Llama-3.1 rotary embedding in place (reference call: pie/src/pie_worker/model/llama3.py:660-669)."""
+    if rotary_dim is not None and rotary_dim != q.shape[-1]:
+        raise ValueError("rotary_dim smaller than head_dim is not supported")
+    cfg = RopeConfig(mode="llama31", theta=rope_theta, scale=rope_scale, low_freq_factor=low_freq_factor,
+                     high_freq_factor=high_freq_factor, old_context_len=float(old_context_len),
+                     interleave=interleave)
+    _rope_inplace(q, k, pos_ids, cfg, "apply_llama31_rope_pos_ids_inplace")
+
+
+def _append(q, k, v, pos_ids, batch_indices, positions, pool, kv_indices, kv_indptr, kv_last_page_len,
+            cfg: Optional[RopeConfig], rotate_k_in_place: bool, who: str) -> None:
+    _require_cuda(k, "append_key")
+    _require_cuda(v, "append_value")
+    _require_i32(batch_indices, "batch_indices")
+    _require_i32(positions, "positions")
+    _require_i32(kv_indices, "kv_indices")
+    _require_i32(kv_indptr, "kv_indptr")
+    _require_i32(kv_last_page_len, "kv_last_page_len")
+    num_pages, page_size, hkv, d = _check_pool(pool)
+    ks, vs = _rows(k, "append_key"), _rows(v, "append_value")
+    n = k.shape[0]
+    if tuple(k.shape) != (n, hkv, d) or tuple(v.shape) != (n, hkv, d):
+        raise ValueError(f"{who}: key {tuple(k.shape)} / value {tuple(v.shape)} do not match the cache "
+                         f"[*, {hkv}, {d}]")
+    if k.dtype != pool.dtype or v.dtype != pool.dtype:
+        raise ValueError(f"{who}: key/value dtype {k.dtype}/{v.dtype} differs from the cache dtype {pool.dtype}")
+    if batch_indices.shape[0] < n or positions.shape[0] < n:
+        raise ValueError(f"{who}: batch_indices / positions shorter than the number of tokens")
+    batch = kv_indptr.shape[0] - 1
+    rp = None
+    q_ptr, qs, hq, pos_ptr = None, (0, 0), 0, None
+    if cfg is not None and cfg.mode != "none":
+        rp = cfg.to_c(d)
+        _require_i32(pos_ids, "pos_ids")
+        pos_ptr = pos_ids.data_ptr()
+        if q is not None:
+            _require_cuda(q, "q")
+            qs = _rows(q, "q")
+            if q.shape[0] != n or q.shape[2] != d or q.dtype != pool.dtype:
+                raise ValueError(f"{who}: q {tuple(q.shape)} {q.dtype} does not match key / cache")
+            q_ptr, hq = q.data_ptr(), q.shape[1]
+    check(lib.piekv_rope_append(q_ptr, k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1], vs[0], vs[1], pos_ptr,
+                                batch_indices.data_ptr(), positions.data_ptr(), pool.data_ptr(),
+                                kv_indices.data_ptr(), kv_indptr.data_ptr(), kv_last_page_len.data_ptr(), n, batch,
+                                hq, hkv, d, page_size, num_pages, _dtype_code(pool.dtype, who),
+                                C.byref(rp) if rp is not None else None, 1 if rotate_k_in_place else 0,
+                                _err_word(pool.device).data_ptr(), _stream(pool.device)), who)
+
+
+def append_paged_kv_cache(append_key: torch.Tensor, append_value: torch.Tensor, batch_indices: torch.Tensor,
+                          positions: torch.Tensor, paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor,
+                          kv_indptr: torch.Tensor, kv_last_page_len: torch.Tensor, kv_layout: str = "NHD") -> None:
+    """Scatter new K/V rows into their pages (reference call: pie/src/pie_worker/model/llama3.py:675-685)."""
+    if kv_layout != "NHD":
+        raise ValueError(f"kv_layout {kv_layout!r} is not supported (NHD only)")
+    _append(None, append_key, append_value, None, batch_indices, positions, paged_kv_cache, kv_indices, kv_indptr,
+            kv_last_page_len, None, False, "append_paged_kv_cache")
+
+
+def rope_append_paged_kv_cache(q: Optional[torch.Tensor], k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
+                               batch_indices: torch.Tensor, positions: torch.Tensor, paged_kv_cache: torch.Tensor,
+                               kv_indices: torch.Tensor, kv_indptr: torch.Tensor, kv_last_page_len: torch.Tensor,
+                               rope: RopeConfig, rotate_k_in_place: bool = False) -> None:
+    """RoPE (q in place, k on the way to the cache) fused with the append: one launch for the
+    reference's two ops at pie/src/pie_worker/model/llama3.py:660-685."""
+    _append(q, k, v, pos_ids, batch_indices, positions, paged_kv_cache, kv_indices, kv_indptr, kv_last_page_len,
+            rope, rotate_k_in_place, "rope_append_paged_kv_cache")
+
+
+def copy_kv_pages(kv_cache_at_layer: Sequence[torch.Tensor], src_pages: torch.Tensor, dst_pages: torch.Tensor,
+                  valid_len: Optional[torch.Tensor] = None) -> None:
+    """Copy the first `valid_len[j]` token rows (default: all) of page src[j] to page dst[j] in every
+    layer's pool: copy-on-write of a partially filled last page when a context forks.  The reference
+    drops and recomputes that page instead (sdk/rust/inferlet/src/context.rs:147-225)."""
+    if isinstance(kv_cache_at_layer, torch.Tensor):
+        kv_cache_at_layer = [kv_cache_at_layer]
+    if len(kv_cache_at_layer) == 0:
+        raise ValueError("copy_kv_pages: no layers")
+    _require_i32(src_pages, "src_pages")
+    _require_i32(dst_pages, "dst_pages")
+    if src_pages.shape != dst_pages.shape:
+        raise ValueError("copy_kv_pages: src_pages and dst_pages differ in length")
+    if valid_len is not None:
+        _require_i32(valid_len, "valid_len")
+        if valid_len.shape != src_pages.shape:
+            raise ValueError("copy_kv_pages: valid_len length differs from src_pages")
+    shape0 = None
+    for i, pool in enumerate(kv_cache_at_layer):
+        s = _check_pool(pool, f"kv_cache_at_layer[{i}]")
+        if shape0 is None:
+            shape0, dt0 = s, pool.dtype
+        elif s != shape0 or pool.dtype != dt0:
+            raise ValueError("copy_kv_pages: layers differ in shape or dtype")
+    num_pages, page_size, hkv, d = shape0
+    ptrs = (C.c_void_p * len(kv_cache_at_layer))(*[p.data_ptr() for p in kv_cache_at_layer])
+    dev = kv_cache_at_layer[0].device
+    check(lib.piekv_copy_pages(ptrs, len(kv_cache_at_layer), src_pages.data_ptr(), dst_pages.data_ptr(),
+                               valid_len.data_ptr() if valid_len is not None else None, src_pages.shape[0],
+                               page_size, hkv, d, num_pages, _dtype_code(dt0, "copy_kv_pages"),
+                               _err_word(dev).data_ptr(), _stream(dev)), "copy_kv_pages")
+
+
+# ---------------------------------------------------------------------------------------
+# attention wrappers
+# ---------------------------------------------------------------------------------------
+def _check_workspace(ws: torch.Tensor) -> None:
+    _require_cuda(ws, "workspace_buffer")
+    if ws.dtype != torch.uint8 or ws.dim() != 1 or not ws.is_contiguous():
+        raise ValueError("workspace_buffer must be a contiguous 1-D uint8 tensor")
+    if ws.numel() < COUNTER_BYTES:
+        raise ValueError(f"workspace_buffer must hold at least {COUNTER_BYTES} bytes")
+
+
+class BatchDecodeWithPagedKVCacheWrapper:
+    """One query token per request against its paged K/V.
+
+    Reference construction and use: pie/src/pie_worker/model/llama3.py:293-300 (CUDA-graph form
+    bound to static index buffers), 311-313, plan 766-777, run 689.  `plan()` only records the
+    index tensors: the work partition is computed on the device inside `run()`, so the same planned
+    wrapper can be replayed from a CUDA graph while the buffers' contents change."""
+
+    def __init__(self, float_workspace_buffer: torch.Tensor, kv_layout: str = "NHD", use_cuda_graph: bool = False,
+                 use_tensor_cores: bool = False, paged_kv_indptr_buffer: Optional[torch.Tensor] = None,
+                 paged_kv_indices_buffer: Optional[torch.Tensor] = None,
+                 paged_kv_last_page_len_buffer: Optional[torch.Tensor] = None, **_ignored) -> None:
+        if kv_layout != "NHD":
+            raise ValueError(f"kv_layout {kv_layout!r} is not supported (NHD only)")
+        _check_workspace(float_workspace_buffer)
+        self.workspace_buffer = float_workspace_buffer
+        self.kv_layout = kv_layout
+        self.use_cuda_graph = use_cuda_graph
+        self._fixed = None
+        if use_cuda_graph:
+            for name, t in (("paged_kv_indptr_buffer", paged_kv_indptr_buffer),
+                            ("paged_kv_indices_buffer", paged_kv_indices_buffer),
+                            ("paged_kv_last_page_len_buffer", paged_kv_last_page_len_buffer)):
+                if t is None:
+                    raise ValueError(f"{name} is required when use_cuda_graph=True")
+                _require_i32(t, name)
+            self._fixed = (paged_kv_indptr_buffer, paged_kv_indices_buffer, paged_kv_last_page_len_buffer)
+        # split-KV arrival counters live at the head of the workspace and must start at zero
+        float_workspace_buffer[:COUNTER_BYTES].zero_()
+        self._plan = None
+
+    def plan(self, indptr: torch.Tensor, indices: torch.Tensor, last_page_len: torch.Tensor, num_qo_heads: int,
+             num_kv_heads: int, head_dim: int, page_size: int, pos_encoding_mode: str = "NONE",
+             window_left: int = -1, logits_soft_cap: Optional[float] = None,
+             q_data_type: torch.dtype = torch.float16, kv_data_type: Optional[torch.dtype] = None,
+             data_type: Optional[torch.dtype] = None, sm_scale: Optional[float] = None, **_ignored) -> None:
+        _require_i32(indptr, "indptr")
+        _require_i32(indices, "indices")
+        _require_i32(last_page_len, "last_page_len")
+        if pos_encoding_mode != "NONE":
+            raise ValueError("pos_encoding_mode other than 'NONE' is not supported; apply RoPE before the append")
+        if window_left != -1 or (logits_soft_cap not in (None, 0.0)):
+            raise ValueError("window_left / logits_soft_cap are not supported")
+        if num_qo_heads % num_kv_heads != 0:
+            raise ValueError(f"num_qo_heads {num_qo_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if kv_data_type is not None and kv_data_type != q_data_type:
+            raise ValueError("kv_data_type must equal q_data_type")
+        batch = indptr.shape[0] - 1
+        if last_page_len.shape[0] < batch:
+            raise ValueError("last_page_len shorter than the batch")
+        if self._fixed is not None:
+            fi, fx, fl = self._fixed
+            if fi.shape[0] != batch + 1 or fl.shape[0] < batch:
+                raise ValueError("batch size differs from the buffers this CUDA-graph wrapper was bound to")
+            if fi.data_ptr() != indptr.data_ptr():
+                fi.copy_(indptr, non_blocking=True)
+            if fx.data_ptr() != indices.data_ptr():
+                if indices.shape[0] > fx.shape[0]:
+                    raise ValueError("indices longer than paged_kv_indices_buffer")
+                fx[: indices.shape[0]].copy_(indices, non_blocking=True)
+            if fl.data_ptr() != last_page_len.data_ptr():
+                fl[:batch].copy_(last_page_len[:batch], non_blocking=True)
+            indptr, indices, last_page_len = fi, fx, fl
+        need = lib.piekv_decode_workspace_bytes(batch, num_qo_heads, num_kv_heads, head_dim)
+        if self.workspace_buffer.numel() < need:
+            raise ValueError(f"workspace_buffer too small: {self.workspace_buffer.numel()} < {need} bytes")
+        self._plan = dict(indptr=indptr, indices=indices, last_page_len=last_page_len, batch=batch,
+                          hq=int(num_qo_heads), hkv=int(num_kv_heads), d=int(head_dim), page_size=int(page_size),
+                          dtype=q_data_type,
+                          sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim))
+
+    def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, out: Optional[torch.Tensor] = None,
+            return_lse: bool = False):
+        if self._plan is None:
+            raise RuntimeError("Must call plan() before run()")
+        pl = self._plan
+        _require_cuda(q, "q")
+        num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
+        qs = _rows(q, "q")
+        if tuple(q.shape) != (pl["batch"], pl["hq"], pl["d"]):
+            raise ValueError(f"q shape {tuple(q.shape)} differs from the plan "
+                             f"({pl['batch']}, {pl['hq']}, {pl['d']})")
+        if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
+            raise ValueError("paged_kv_cache shape differs from the plan")
+        if q.dtype != paged_kv_cache.dtype:
+            raise ValueError(f"q dtype {q.dtype} differs from the cache dtype {paged_kv_cache.dtype}")
+        if out is None:
+            out = torch.empty((pl["batch"], pl["hq"], pl["d"]), dtype=q.dtype, device=q.device)
+        elif tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+            raise ValueError("out must be a contiguous tensor shaped and typed like q")
+        lse = torch.empty((pl["batch"], pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
+        ws = self.workspace_buffer
+        check(lib.piekv_decode_run(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
+                                   lse.data_ptr() if lse is not None else None, pl["indptr"].data_ptr(),
+                                   pl["indices"].data_ptr(), pl["last_page_len"].data_ptr(), pl["batch"], pl["hq"],
+                                   pl["hkv"], pl["d"], pl["page_size"], num_pages,
+                                   _dtype_code(q.dtype, "decode run"), pl["sm_scale"], ws.data_ptr(), ws.numel(),
+                                   _err_word(q.device).data_ptr(), _stream(q.device)), "BatchDecode.run")
+        return (out, lse) if return_lse else out
+
+    forward = run
+
+
+class BatchPrefillWithPagedKVCacheWrapper:
+    """Packed variable-length (prefill / chunked / multi-token) attention over paged K/V.
+
+    Reference construction and use: pie/src/pie_worker/model/llama3.py:307-309, plan 779-791,
+    run 689.  `custom_mask` is the flat boolean mask of pie/src/pie_worker/batching.py:113-135:
+    for every query token a row of kv_len_b entries."""
+
+    def __init__(self, float_workspace_buffer: torch.Tensor, kv_layout: str = "NHD", **_ignored) -> None:
+        if kv_layout != "NHD":
+            raise ValueError(f"kv_layout {kv_layout!r} is not supported (NHD only)")
+        _check_workspace(float_workspace_buffer)
+        self.workspace_buffer = float_workspace_buffer
+        self.kv_layout = kv_layout
+        float_workspace_buffer[:COUNTER_BYTES].zero_()
+        self._plan = None
+
+    def plan(self, qo_indptr: torch.Tensor, paged_kv_indptr: torch.Tensor, paged_kv_indices: torch.Tensor,
+             paged_kv_last_page_len: torch.Tensor, num_qo_heads: int, num_kv_heads: int, head_dim_qk: int,
+             page_size: int, head_dim_vo: Optional[int] = None, custom_mask: Optional[torch.Tensor] = None,
+             packed_custom_mask: Optional[torch.Tensor] = None, causal: bool = False,
+             pos_encoding_mode: str = "NONE", window_left: int = -1, logits_soft_cap: Optional[float] = None,
+             sm_scale: Optional[float] = None, q_data_type: torch.dtype = torch.float16,
+             kv_data_type: Optional[torch.dtype] = None, **_ignored) -> None:
+        _require_i32(qo_indptr, "qo_indptr")
+        _require_i32(paged_kv_indptr, "paged_kv_indptr")
+        _require_i32(paged_kv_indices, "paged_kv_indices")
+        _require_i32(paged_kv_last_page_len, "paged_kv_last_page_len")
+        if pos_encoding_mode != "NONE":
+            raise ValueError("pos_encoding_mode other than 'NONE' is not supported; apply RoPE before the append")
+        if window_left != -1 or (logits_soft_cap not in (None, 0.0)):
+            raise ValueError("window_left / logits_soft_cap are not supported")
+        if packed_custom_mask is not None:
+            raise ValueError("packed_custom_mask is not supported; pass the boolean custom_mask")
+        if head_dim_vo is not None and head_dim_vo != head_dim_qk:
+            raise ValueError("head_dim_vo must equal head_dim_qk")
+        if num_qo_heads % num_kv_heads != 0:
+            raise ValueError(f"num_qo_heads {num_qo_heads} is not a multiple of num_kv_heads {num_kv_heads}")
+        if kv_data_type is not None and kv_data_type != q_data_type:
+            raise ValueError("kv_data_type must equal q_data_type")
+        if paged_kv_indptr.shape[0] != qo_indptr.shape[0]:
+            raise ValueError("qo_indptr and paged_kv_indptr describe different batch sizes")
+        mask = None
+        if custom_mask is not None:
+            _require_cuda(custom_mask, "custom_mask")
+            if custom_mask.dtype not in (torch.bool, torch.uint8) or not custom_mask.is_contiguous():
+                raise ValueError("custom_mask must be a contiguous bool (or uint8) tensor")
+            mask = custom_mask.view(torch.uint8) if custom_mask.dtype == torch.bool else custom_mask
+            causal = False  # the mask alone decides, as in the reference
+        batch = qo_indptr.shape[0] - 1
+        self._plan = dict(qo_indptr=qo_indptr, indptr=paged_kv_indptr, indices=paged_kv_indices,
+                          last_page_len=paged_kv_last_page_len, batch=batch, hq=int(num_qo_heads),
+                          hkv=int(num_kv_heads), d=int(head_dim_qk), page_size=int(page_size), mask=mask,
+                          causal=bool(causal), dtype=q_data_type,
+                          sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim_qk))
+
+    def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, out: Optional[torch.Tensor] = None,
+            return_lse: bool = False):
+        if self._plan is None:
+            raise RuntimeError("Must call plan() before run()")
+        pl = self._plan
+        _require_cuda(q, "q")
+        num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
+        qs = _rows(q, "q")
+        n = q.shape[0]
+        if tuple(q.shape[1:]) != (pl["hq"], pl["d"]):
+            raise ValueError(f"q shape {tuple(q.shape)} differs from the plan (*, {pl['hq']}, {pl['d']})")
+        if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
+            raise ValueError("paged_kv_cache shape differs from the plan")
+        if q.dtype != paged_kv_cache.dtype:
+            raise ValueError(f"q dtype {q.dtype} differs from the cache dtype {paged_kv_cache.dtype}")
+        if out is None:
+            out = torch.empty((n, pl["hq"], pl["d"]), dtype=q.dtype, device=q.device)
+        elif tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+            raise ValueError("out must be a contiguous tensor shaped and typed like q")
+        lse = torch.empty((n, pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
+        ws = self.workspace_buffer
+        need = lib.piekv_prefill_workspace_bytes(pl["batch"], n, pl["hq"], pl["d"])
+        if ws.numel() < need:
+            raise ValueError(f"workspace_buffer too small: {ws.numel()} < {need} bytes")
+        check(lib.piekv_prefill_run(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
+                                    lse.data_ptr() if lse is not None else None, pl["qo_indptr"].data_ptr(),
+                                    pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
+                                    pl["last_page_len"].data_ptr(),
+                                    pl["mask"].data_ptr() if pl["mask"] is not None else None,
+                                    1 if pl["causal"] else 0, pl["batch"], n, pl["hq"], pl["hkv"], pl["d"],
+                                    pl["page_size"], num_pages, _dtype_code(q.dtype, "prefill run"),
+                                    pl["sm_scale"], ws.data_ptr(), ws.numel(), _err_word(q.device).data_ptr(),
+                                    _stream(q.device)), "BatchPrefill.run")
+        return (out, lse) if return_lse else out
+
+    forward = run

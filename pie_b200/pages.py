@@ -1,0 +1,237 @@
+"""Host-side page bookkeeping: which physical page ids each request presents to the kernels.
+
+Semantics follow the reference:
+  * `IdPool`  - smallest-free-id allocator with tail compaction
+                (runtime/src/utils.rs:42-158).
+  * `PagePool` - reference counts on top of the id pool; a page returns to the pool when its last
+                owner lets go (sdk/rust/inferlet/src/forward.rs:28-55 `KvPage` drop ->
+                runtime/src/model/resource.rs:225-254 deallocate).  Recycled pages are NOT cleared.
+  * `KvPageList` - one context's page list and last-page fill: grow / shrink / fork / adopt
+                (sdk/javascript/src/kv-page-manager.ts, sdk/rust/inferlet/src/context.rs:147-225,356-399).
+                `fork()` is the reference behaviour (share full pages, drop the partial one and report
+                the tokens to recompute); `fork_cow()` is this library's extension: the partial page is
+                duplicated with `ops.copy_kv_pages` instead of being recomputed.
+  * `build_csr` - the kv_page_indices / kv_page_indptr / kv_last_page_lens arrays of a batch
+                (wire layout runtime/src/model/request.rs:332-409).
+"""
+from __future__ import annotations
+
+import heapq
+from typing import Iterable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+
+class PoolExhausted(RuntimeError):
+    """No free page id is left ("ID pool exhausted", runtime/src/utils.rs:86-93)."""
+
+
+class IdPool:
+    """Bounded pool that always hands out the smallest available id."""
+
+    TAIL_COMPACTION_THRESHOLD = 1000  # runtime/src/utils.rs:119,133
+
+    def __init__(self, max_capacity: int) -> None:
+        self._next = 0
+        self._free: set = set()
+        self._heap: List[int] = []
+        self._cap = int(max_capacity)
+
+    @property
+    def capacity(self) -> int:
+        return self._cap
+
+    def set_capacity(self, capacity: int) -> None:
+        if capacity < self._next:
+            raise ValueError("Cannot set capacity lower than the next ID")
+        self._cap = int(capacity)
+
+    def available(self) -> int:
+        return len(self._free) + (self._cap - self._next)
+
+    def acquire(self) -> int:
+        while self._heap:
+            i = heapq.heappop(self._heap)
+            if i in self._free:  # lazy deletion: ids removed by tail compaction stay in the heap
+                self._free.discard(i)
+                return i
+        if self._next < self._cap:
+            i = self._next
+            self._next += 1
+            return i
+        raise PoolExhausted("ID pool exhausted")
+
+    def acquire_many(self, count: int) -> List[int]:
+        if self.available() < count:
+            raise PoolExhausted("ID pool exhausted")
+        return [self.acquire() for _ in range(count)]
+
+    def release(self, i: int) -> None:
+        self.release_many([i])
+
+    def release_many(self, ids: Iterable[int]) -> None:
+        for i in ids:
+            if i >= self._next or i < 0:
+                raise ValueError("ID was never allocated")
+            if i not in self._free:
+                self._free.add(i)
+                heapq.heappush(self._heap, i)
+        if len(self._free) > self.TAIL_COMPACTION_THRESHOLD:
+            self._tail_compaction()
+
+    def _tail_compaction(self) -> None:
+        while self._next > 0 and (self._next - 1) in self._free:
+            self._free.discard(self._next - 1)
+            self._next -= 1
+        if len(self._heap) > 4 * (len(self._free) + 16):
+            self._heap = list(self._free)
+            heapq.heapify(self._heap)
+
+
+class PagePool:
+    """Reference-counted physical pages of one GPU's pool."""
+
+    def __init__(self, num_pages: int) -> None:
+        self.ids = IdPool(num_pages)
+        self.refs = np.zeros(num_pages, dtype=np.int32)
+
+    def alloc(self, count: int) -> List[int]:
+        pages = self.ids.acquire_many(count)
+        self.refs[pages] = 1
+        return pages
+
+    def ref(self, pages: Sequence[int]) -> None:
+        for p in pages:
+            if self.refs[p] <= 0:
+                raise ValueError(f"page {p} is not allocated")
+            self.refs[p] += 1
+
+    def release(self, pages: Sequence[int]) -> List[int]:
+        """Drop one reference per page; returns the pages that went back to the free list."""
+        freed = []
+        for p in pages:
+            if self.refs[p] <= 0:
+                raise ValueError(f"page {p} is not allocated")
+            self.refs[p] -= 1
+            if self.refs[p] == 0:
+                freed.append(p)
+        if freed:
+            self.ids.release_many(freed)
+        return freed
+
+    def available(self) -> int:
+        return self.ids.available()
+
+
+class KvPageList:
+    """Pages and last-page fill of one context."""
+
+    def __init__(self, pool: PagePool, page_size: int) -> None:
+        self.pool = pool
+        self.page_size = int(page_size)
+        self.pages: List[int] = []
+        self.last_page_len = 0
+
+    # -- kv-page-manager.ts:19-31
+    @property
+    def page_count(self) -> int:
+        return len(self.pages)
+
+    @property
+    def total_tokens(self) -> int:
+        if not self.pages:
+            return self.last_page_len
+        return (len(self.pages) - 1) * self.page_size + self.last_page_len
+
+    def _set_last(self, total: int) -> None:
+        r = total % self.page_size
+        self.last_page_len = self.page_size if (r == 0 and total > 0) else r
+
+    # -- kv-page-manager.ts:150-181 (adjust)
+    def grow(self, num_tokens: int) -> List[int]:
+        """Make room for `num_tokens` more tokens; returns the newly allocated pages."""
+        return self._adjust(num_tokens)
+
+    def shrink(self, num_tokens: int) -> None:
+        self._adjust(-num_tokens)
+
+    def _adjust(self, delta: int) -> List[int]:
+        if delta == 0:
+            return []
+        new_total = self.total_tokens + delta
+        if new_total < 0:
+            raise ValueError("Token count adjustment resulted in underflow")
+        required = -(-new_total // self.page_size)
+        new_pages: List[int] = []
+        if required > len(self.pages):
+            new_pages = self.pool.alloc(required - len(self.pages))
+            self.pages.extend(new_pages)
+        elif required < len(self.pages):
+            drop = self.pages[required:]
+            del self.pages[required:]
+            self.pool.release(drop)
+        self._set_last(new_total)
+        return new_pages
+
+    # -- kv-page-manager.ts:57-86 (fork shares FULL pages only)
+    def fork(self) -> Tuple["KvPageList", int]:
+        """Reference fork: the child shares every page but the last one; returns (child, number of
+        tokens of the dropped last page that the caller has to recompute)."""
+        kept = max(0, len(self.pages) - 1)
+        child = KvPageList(self.pool, self.page_size)
+        child.pages = self.pages[:kept]
+        child.last_page_len = self.page_size if kept > 0 else 0
+        self.pool.ref(child.pages)
+        return child, self.total_tokens - kept * self.page_size
+
+    def fork_cow(self) -> Tuple["KvPageList", Optional[Tuple[int, int, int]]]:
+        """Copy-on-write fork: full pages are shared, a partially filled last page is given a private
+        copy.  Returns (child, (src_page, dst_page, valid_len)) - the copy to run with
+        `ops.copy_kv_pages` - or (child, None) when the last page is full (it is then shared: nobody
+        writes into a full page again)."""
+        child = KvPageList(self.pool, self.page_size)
+        child.last_page_len = self.last_page_len
+        if not self.pages:
+            return child, None
+        if self.last_page_len == self.page_size:
+            child.pages = list(self.pages)
+            self.pool.ref(child.pages)
+            return child, None
+        shared = self.pages[:-1]
+        self.pool.ref(shared)
+        (fresh,) = self.pool.alloc(1)
+        child.pages = shared + [fresh]
+        return child, (self.pages[-1], fresh, self.last_page_len)
+
+    def release(self) -> List[int]:
+        freed = self.pool.release(self.pages)
+        self.pages = []
+        self.last_page_len = 0
+        return freed
+
+    def adopt(self, other: "KvPageList") -> None:
+        """Become a co-owner of `other`'s pages (beam-search winner, kv-page-manager.ts:103-112)."""
+        self.release()
+        self.pages = list(other.pages)
+        self.last_page_len = other.last_page_len
+        self.pool.ref(self.pages)
+
+    def remove_page_at(self, index: int) -> None:
+        """Drop one fully masked page (kv-page-manager.ts:127-140)."""
+        if index < 0 or index >= len(self.pages):
+            raise IndexError(f"Page index {index} out of bounds")
+        removed = self.pages.pop(index)
+        self.pool.release([removed])
+        self._set_last(self.total_tokens)
+
+
+def build_csr(contexts: Sequence[KvPageList]) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
+    """(kv_page_indices, kv_page_indptr, kv_last_page_lens) int32 of a batch of contexts."""
+    counts = np.fromiter((len(c.pages) for c in contexts), dtype=np.int64, count=len(contexts))
+    indptr = np.zeros(len(contexts) + 1, dtype=np.int32)
+    np.cumsum(counts, out=indptr[1:])
+    indices = np.empty(int(indptr[-1]), dtype=np.int32)
+    for c, s in zip(contexts, indptr[:-1]):
+        indices[s: s + len(c.pages)] = c.pages
+    last = np.fromiter((c.last_page_len for c in contexts), dtype=np.int32, count=len(contexts))
+    return indices, indptr, last
