@@ -89,11 +89,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   const AttnArgs &a = p.a;
   const int B = a.batch;
-  const int G = gridDim.x;
   const int c = blockIdx.x;
   const int total_pages = a.kv_indptr[B];
-  const int lo = (int)((long long)c * total_pages / G);
-  const int hi = (int)((long long)(c + 1) * total_pages / G);
+  // With fewer pages than CTAs only the first `total_pages` CTAs take part, so that every
+  // participating range is non-empty (the segment count of a request relies on that).
+  const int G = min((int)gridDim.x, max(total_pages, 1));
+  const int lo = c < G ? (int)((long long)c * total_pages / G) : 0;
+  const int hi = c < G ? (int)((long long)(c + 1) * total_pages / G) : 0;
   const int group = a.hq / HKV;
 
   if (threadIdx.x == 0) {
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   T *out = reinterpret_cast<T *>(a.out);
 
   // requests without any page: softmax over nothing -> zeros
-  for (int b = c; b < B; b += G) {
+  for (int b = c; b < B; b += gridDim.x) {
     if (a.kv_indptr[b + 1] == a.kv_indptr[b]) {
       for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32)
         out[(size_t)b * a.hq * kDim + x] = Elem<T>::from_f32(0.f);
