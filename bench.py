@@ -1,0 +1,481 @@
+#!/usr/bin/env python
+"""Benchmark of the paged-KV decode hot path (fused RoPE + K/V append + paged decode attention).
+
+Workload (`config.workload`): the Llama-3-8B-shaped decode layer - 32 query / 8 KV heads, head_dim 128,
+bf16, page_size 16, a pool of 32768 pages with a fragmented (seeded-permutation) page table, 64 requests
+with context lengths uniform in [512, 4096]; every step appends one token per request and attends over
+all of that request's pages.  Data are synthetic (seeded N(0,1)*0.5); no dataset is involved.
+
+A "step" is one pass of the path over the batch: metadata kernel -> RoPE + append kernel -> decode
+attention kernel.  Steps run back to back on one stream from a captured CUDA graph.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+N > 1 (launched by torch.distributed.run, one rank per GPU): requests are sharded across GPUs with
+independent page pools and no data-path collective - every rank runs its own 64-request batch
+(weak scaling); time is the max over ranks.
+
+Printed JSON line: metric = decode tokens/s (whole job), `value` with inputs resident in HBM, `e2e`
+through pie_b200.ops with pinned HOST buffers (H2D of the step's q/k/v + metadata and D2H of the
+attention output inside the timed region), `roofline` for the decode-attention kernel (algorithmic
+bytes / CUDA-event time against the measured HBM copy bandwidth), `cpu_baseline` = the CPU oracle on a
+bounded sample.  `--impl reference` times the CPU restatement of the reference path on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode_tokens_per_s"
+UNIT = "tokens/s"
+WORKLOAD = "llama3-8b-shaped decode layer: 32q/8kv heads, D128, bf16, page16, 32768-page pool, " \
+           "64 requests/GPU, ctx U[512,4096], +1 token/request/step"
+HORIZON = 512  # distinct consecutive steps of metadata; longer runs wrap around
+
+# DRAM bytes per decode-kernel launch measured once with ncu (dram__bytes_read.sum + dram__bytes_write.sum),
+# scaled to this workload; see profiles/.  None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    REASONS = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+        0x80: "hw_power_brake_slowdown",
+    }
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                try:
+                    phys = int(visible.split(",")[index])
+                except Exception:
+                    phys = index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": float(np.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------------------------
+def build_steps(rank: int, horizon: int, batch: int = 64, num_pages: int = 32768):
+    from pie_b200 import workloads as W
+
+    reqs = W.config2_requests(batch=batch, seed=1 + rank, num_pages=num_pages)
+    return W.decode_steps(reqs, horizon)
+
+
+def pack_meta(meta, tmax: int) -> np.ndarray:
+    """One int32 row per step: [kv_indptr (B+1) | last_len (B) | pos_ids (B) | qo_indptr (B+1) | indices (tmax)]."""
+    row = np.zeros(meta.batch * 4 + 2 + tmax, dtype=np.int32)
+    b = meta.batch
+    row[: b + 1] = meta.kv_indptr
+    row[b + 1: 2 * b + 1] = meta.kv_last_page_len
+    row[2 * b + 1: 3 * b + 1] = meta.pos_ids
+    row[3 * b + 1: 4 * b + 2] = meta.qo_indptr
+    row[4 * b + 2: 4 * b + 2 + len(meta.kv_indices)] = meta.kv_indices
+    return row
+
+
+def views(row: torch.Tensor, b: int):
+    return dict(indptr=row[: b + 1], last=row[b + 1: 2 * b + 1], pos=row[2 * b + 1: 3 * b + 1],
+                qo=row[3 * b + 1: 4 * b + 2], indices=row[4 * b + 2:])
+
+
+# ---------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch.distributed as dist
+
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+    from pie_b200._lib import lib, check
+    import ctypes as C
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    n_gpus = world
+
+    cfg = W.CONFIG2
+    if args.pages != cfg.num_pages:
+        import dataclasses
+        cfg = dataclasses.replace(cfg, num_pages=args.pages)
+    B, HQ, HKV, D = args.requests, cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    steps, warmup = args.steps, args.warmup
+    horizon = min(HORIZON, steps + warmup)
+    metas = build_steps(rank, horizon, B, cfg.num_pages)
+    tmax = max(len(m.kv_indices) for m in metas)
+    packed_host = torch.from_numpy(np.stack([pack_meta(m, tmax) for m in metas])).pin_memory()
+    packed = packed_host.to(dev)
+
+    pool = W.randn(cfg.pool_shape(), 100 + rank, cfg.dtype, cfg.value_scale, device=dev)
+    n_var = 8  # distinct q/k/v inputs cycled over the steps
+    qkv_host = W.randn((n_var, B, (HQ + 2 * HKV) * D), 200 + rank, cfg.dtype, cfg.value_scale).pin_memory()
+    qkv = qkv_host.to(dev)
+    out = torch.empty((B, HQ, D), dtype=cfg.dtype, device=dev)
+    seq_lens = torch.empty(B, dtype=torch.int32, device=dev)
+    bidx = torch.empty(B, dtype=torch.int32, device=dev)
+    kvpos = torch.empty(B, dtype=torch.int32, device=dev)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
+    err = torch.zeros(4, dtype=torch.int32, device=dev)
+    rope = ops.RopeConfig(mode=cfg.rope_mode, theta=cfg.rope_theta, scale=cfg.rope_scale).to_c(D)
+    sm_scale = 1.0 / math.sqrt(D)
+    stream = torch.cuda.Stream(dev)
+    launches = [0]
+    es = 2
+
+    def qkv_views(t):
+        q = t[:, : HQ * D].view(B, HQ, D)
+        k = t[:, HQ * D: (HQ + HKV) * D].view(B, HKV, D)
+        v = t[:, (HQ + HKV) * D:].view(B, HKV, D)
+        return q, k, v
+
+    def step_device(i: int, st: int):
+        """One step on device-resident inputs through the C ABI (3 launches)."""
+        mv = views(packed[i % horizon], B)
+        q, k, v = qkv_views(qkv[i % n_var])
+        check(lib.piekv_metadata(mv["qo"].data_ptr(), mv["indptr"].data_ptr(), mv["last"].data_ptr(), B, B, 16,
+                                 seq_lens.data_ptr(), bidx.data_ptr(), kvpos.data_ptr(), st), "metadata")
+        check(lib.piekv_rope_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), q.stride(1), k.stride(0),
+                                    k.stride(1), v.stride(0), v.stride(1), mv["pos"].data_ptr(), bidx.data_ptr(),
+                                    kvpos.data_ptr(), pool.data_ptr(), mv["indices"].data_ptr(),
+                                    mv["indptr"].data_ptr(), mv["last"].data_ptr(), B, B, HQ, HKV, D, 16,
+                                    cfg.num_pages, 2, C.byref(rope), 0, err.data_ptr(), st), "rope_append")
+        check(lib.piekv_decode_run(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out.data_ptr(), None,
+                                   mv["indptr"].data_ptr(), mv["indices"].data_ptr(), mv["last"].data_ptr(), B, HQ,
+                                   HKV, D, 16, cfg.num_pages, 2, sm_scale, ws.data_ptr(), ws.numel(),
+                                   err.data_ptr(), st), "decode_run")
+        launches[0] += 3
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # NOTE: q is rotated in place by the fused kernel; the 8 input variants therefore drift over the
+    # steps (rotations keep their norm), which does not change the work done.
+
+    # ---- value: device-resident, CUDA graph of exactly `steps` steps -------------------------------
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            step_device(i, stream.cuda_stream)
+    stream.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    launches[0] = 0
+    with torch.cuda.graph(graph, stream=stream):
+        for i in range(steps):
+            step_device(warmup + i, torch.cuda.current_stream(dev).cuda_stream)
+    timed_launches = launches[0]
+    with torch.cuda.stream(stream):
+        graph.replay()  # one untimed replay: graph upload + caches
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    with sampler:
+        barrier()
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    value = n_gpus * B * steps / (ms * 1e-3)
+    errw = err.cpu().tolist()
+
+    # ---- roofline: the decode-attention kernel alone ------------------------------------------------
+    reps = args.kernel_reps
+    mid = metas[(warmup + steps // 2) % horizon]
+    mv = views(packed[(warmup + steps // 2) % horizon], B)
+    q, _, _ = qkv_views(qkv[0])
+
+    def decode_only(st):
+        check(lib.piekv_decode_run(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out.data_ptr(), None,
+                                   mv["indptr"].data_ptr(), mv["indices"].data_ptr(), mv["last"].data_ptr(), B, HQ,
+                                   HKV, D, 16, cfg.num_pages, 2, sm_scale, ws.data_ptr(), ws.numel(),
+                                   err.data_ptr(), st), "decode_run")
+
+    with torch.cuda.stream(stream):
+        for _ in range(5):
+            decode_only(stream.cuda_stream)
+        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        k0.record(stream)
+        for _ in range(reps):
+            decode_only(stream.cuda_stream)
+        k1.record(stream)
+    stream.synchronize()
+    kern_ms = k0.elapsed_time(k1) / reps
+    tokens = int(mid.seq_lens.astype(np.int64).sum())
+    kern_bytes = tokens * 2 * HKV * D * es + B * 2 * HQ * D * es + 4 * (len(mid.kv_indices) + 2 * B + 1)
+    peak, peak_kind = load_peaks()
+    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+    step_bytes = W.decode_step_bytes(mid, cfg)
+
+    # ---- e2e: public Python API, host buffers, H2D + D2H inside the timed region ---------------------
+    e2e_steps = min(steps, 256)
+    out_host = torch.empty((B, HQ, D), dtype=cfg.dtype).pin_memory()
+    meta_dev = torch.empty(packed.shape[1], dtype=torch.int32, device=dev)
+    qkv_dev = torch.empty_like(qkv[0])
+    rope_cfg = ops.RopeConfig(mode=cfg.rope_mode, theta=cfg.rope_theta, scale=cfg.rope_scale)
+    wrapper = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+    h2d = packed_host[0].numel() * 4 + qkv_host[0].numel() * es
+    d2h = out_host.numel() * es
+
+    def step_e2e(i: int):
+        meta_dev.copy_(packed_host[i % horizon], non_blocking=True)
+        qkv_dev.copy_(qkv_host[i % n_var], non_blocking=True)
+        mv_ = views(meta_dev, B)
+        q_, k_, v_ = qkv_views(qkv_dev)
+        sl = ops.get_seq_lens(mv_["indptr"], mv_["last"], 16)
+        bi, kp = ops.get_batch_indices_positions(mv_["qo"], sl, B)
+        ops.rope_append_paged_kv_cache(q_, k_, v_, mv_["pos"], bi, kp, pool, mv_["indices"], mv_["indptr"],
+                                       mv_["last"], rope_cfg)
+        wrapper.plan(mv_["indptr"], mv_["indices"], mv_["last"], HQ, HKV, D, 16, pos_encoding_mode="NONE",
+                     q_data_type=cfg.dtype)
+        o = wrapper.run(q_, pool, out=out)
+        out_host.copy_(o, non_blocking=True)
+
+    for i in range(3):
+        step_e2e(i)
+    barrier()
+    c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    c0.record()
+    for i in range(e2e_steps):
+        step_e2e(warmup + i)
+    c1.record()
+    barrier()
+    e2e_ms = c0.elapsed_time(c1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = n_gpus * B * e2e_steps / (e2e_ms * 1e-3)
+
+    # ---- cpu baseline (rank 0, N=1 only): the CPU oracle on a bounded sample --------------------------
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(sample_steps=args.cpu_steps)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "requests_per_gpu": B, "global_requests": B * n_gpus, "pool_pages": cfg.num_pages,
+                       "parallelism": f"request-sharded x{n_gpus}, independent page pools, no collective",
+                       "l2": "inputs larger than L2 (0.6 GB of KV per step vs 126 MB); no flush",
+                       "launch": "CUDA graph of all timed steps, 3 kernels per step",
+                       "step_algorithmic_bytes": step_bytes},
+            "clocks": sampler.summary(),
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": timed_launches,
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "bytes_per_launch": kern_bytes,
+                         "us_per_launch": kern_ms * 1e3,
+                         "frac_of_nominal_8tbs": achieved / 8000.0,
+                         "step_frac": step_bytes / (ms / steps * 1e-3) / 1e9 / peak},
+            "device_error_word": errw,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU arms
+# ---------------------------------------------------------------------------------------------
+class CpuPath:
+    """The reference path on host cores: the CPU oracle in the reference's op order
+    (RoPE -> append -> decode attention, pie/src/pie_worker/model/llama3.py:654-689)."""
+
+    def __init__(self, num_pages: int = 32768, seed: int = 1):
+        from oracle import paged_kv_ref as R
+        from pie_b200 import workloads as W
+
+        self.R, self.W = R, W
+        self.cfg = W.CONFIG2
+        torch.set_num_threads(os.cpu_count() or 1)
+        self.cores = torch.get_num_threads()
+        reqs = W.config2_requests(seed=seed, num_pages=num_pages)
+        self.metas = W.decode_steps(reqs, 64)
+        cfg = self.cfg
+        g = torch.Generator().manual_seed(7)
+        self.pool = torch.empty(cfg.pool_shape(), dtype=cfg.dtype)
+        # filling 2 GiB with Gaussian noise on the CPU takes a while; uniform noise of the same scale is
+        # enough for timing (values do not change the work)
+        self.pool.view(torch.int16).random_(0x3C00, 0x3F80, generator=g)  # bf16 bit patterns in [2^-7, 1)
+        self.q = W.randn((64, cfg.num_qo_heads, cfg.head_dim), 1, cfg.dtype, 0.5)
+        self.k = W.randn((64, cfg.num_kv_heads, cfg.head_dim), 2, cfg.dtype, 0.5)
+        self.v = W.randn((64, cfg.num_kv_heads, cfg.head_dim), 3, cfg.dtype, 0.5)
+        self.inv = R.rope_inv_freq(cfg.head_dim, cfg.rope_theta, "llama31", cfg.rope_scale)
+
+    def step(self, i: int, nreq: int = 64) -> int:
+        """One decode step over the first `nreq` requests; returns tokens processed."""
+        R = self.R
+        m = self.metas[i % len(self.metas)]
+        c, s = R.rope_cos_sin(m.pos_ids[:nreq], self.inv)
+        q = R.apply_rope(self.q[:nreq], c, s)
+        k = R.apply_rope(self.k[:nreq], c, s)
+        ptr = m.kv_indptr[: nreq + 1]
+        seq = R.get_seq_lens(ptr, m.kv_last_page_len[:nreq], 16)
+        bi, pos = R.get_batch_indices_positions(m.qo_indptr[: nreq + 1], seq, nreq)
+        R.append_paged_kv_cache(k, self.v[:nreq], bi, pos, self.pool, m.kv_indices, ptr)
+        R.decode_attention(q, self.pool, ptr, m.kv_indices, m.kv_last_page_len[:nreq])
+        return nreq
+
+
+def cpu_baseline(sample_steps: int = 0, budget_s: float = 20.0):
+    path = CpuPath()
+    path.step(0)
+    t0 = time.perf_counter()
+    path.step(1)
+    one = time.perf_counter() - t0
+    n = sample_steps or max(1, min(64, int(budget_s / max(one, 1e-3))))
+    t0 = time.perf_counter()
+    tokens = 0
+    for i in range(n):
+        tokens += path.step(2 + i)
+    dt = time.perf_counter() - t0
+    return {"value": tokens / dt, "unit": UNIT, "cores": path.cores, "kind": "port",
+            "sample": f"{n} full decode steps of the workload (64 requests each) on the CPU oracle, "
+                      f"torch CPU with {path.cores} threads; {dt:.1f} s"}
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's path on the host cores.  The reference has no CPU (or in-repo
+    CUDA) implementation of this path, so the timed code is the CPU restatement under oracle/ ("port")."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    path = CpuPath()
+    steps, warmup = args.steps, args.warmup
+    path.step(0)
+    t0 = time.perf_counter()
+    path.step(1)
+    one = time.perf_counter() - t0
+    # bound the whole run to about two minutes: each step processes a sample of the 64 requests
+    budget = 120.0
+    nreq = 64
+    if one * (steps + warmup) > budget:
+        nreq = max(1, min(64, int(64 * budget / (one * (steps + warmup)))))
+    for i in range(min(warmup, 3)):
+        path.step(i, nreq)
+    t0 = time.perf_counter()
+    tokens = 0
+    for i in range(steps):
+        tokens += path.step(warmup + i, nreq)
+    dt = time.perf_counter() - t0
+    value = tokens / dt
+    sample = (f"each step = the first {nreq} of 64 requests of the workload's decode step "
+              f"(RoPE + append + paged decode attention) on the CPU oracle, {path.cores} torch threads")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "requests_per_gpu": 64, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": path.cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=1024)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-steps", type=int, default=0, help="CPU-baseline sample size in steps (0 = ~20 s)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
+    ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
+    ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
+    ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -34,10 +34,19 @@ def randn(shape, seed: int, dtype: torch.dtype, scale: float = 1.0, device="cpu"
     generator is used (fast for multi-GiB pools) and values are reproducible per device type only."""
     device = torch.device(device)
     g = torch.Generator(device=device).manual_seed(seed)
-    x = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
-    if scale != 1.0:
-        x.mul_(scale)
-    return x.to(dtype)
+    shape = tuple(shape)
+    out = torch.empty(shape, dtype=dtype, device=device)
+    if device.type == "cpu" or out.numel() <= (1 << 26) or len(shape) < 2:
+        x = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
+        out.copy_(x.mul_(scale) if scale != 1.0 else x)
+        return out
+    # big device tensors: generate in slabs so the fp32 staging buffer stays small
+    rows = max(1, (1 << 26) // max(1, out[0].numel()))
+    for s in range(0, shape[0], rows):
+        e = min(shape[0], s + rows)
+        x = torch.randn((e - s,) + shape[1:], generator=g, dtype=torch.float32, device=device)
+        out[s:e].copy_(x.mul_(scale) if scale != 1.0 else x)
+    return out
 
 
 def pages_needed(tokens: int, page_size: int = PAGE_SIZE) -> int:
