@@ -6,8 +6,9 @@ bf16, page_size 16, a pool of 32768 pages with a fragmented (seeded-permutation)
 with context lengths uniform in [512, 4096]; every step appends one token per request and attends over
 all of that request's pages.  Data are synthetic (seeded N(0,1)*0.5); no dataset is involved.
 
-A "step" is one pass of the path over the batch: metadata kernel -> RoPE + append kernel -> decode
-attention kernel.  Steps run back to back on one stream from a captured CUDA graph.
+A "step" is one pass of the path over the batch: RoPE of q and of the new k, append of k / v into the
+pages and decode attention, in ONE fused kernel launch.  Steps run back to back on one stream from a
+captured CUDA graph.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
@@ -201,29 +202,21 @@ def run_ours(args):
         return q, k, v
 
     def step_device(i: int, st: int):
-        """One step on device-resident inputs through the C ABI (3 launches)."""
+        """One step on device-resident inputs through the C ABI: a single fused launch."""
         mv = views(packed[i % horizon], B)
         q, k, v = qkv_views(qkv[i % n_var])
-        check(lib.piekv_metadata(mv["qo"].data_ptr(), mv["indptr"].data_ptr(), mv["last"].data_ptr(), B, B, 16,
-                                 seq_lens.data_ptr(), bidx.data_ptr(), kvpos.data_ptr(), st), "metadata")
-        check(lib.piekv_rope_append(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), q.stride(1), k.stride(0),
-                                    k.stride(1), v.stride(0), v.stride(1), mv["pos"].data_ptr(), bidx.data_ptr(),
-                                    kvpos.data_ptr(), pool.data_ptr(), mv["indices"].data_ptr(),
-                                    mv["indptr"].data_ptr(), mv["last"].data_ptr(), B, B, HQ, HKV, D, 16,
-                                    cfg.num_pages, 2, C.byref(rope), 0, err.data_ptr(), st), "rope_append")
-        check(lib.piekv_decode_run(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out.data_ptr(), None,
-                                   mv["indptr"].data_ptr(), mv["indices"].data_ptr(), mv["last"].data_ptr(), B, HQ,
-                                   HKV, D, 16, cfg.num_pages, 2, sm_scale, ws.data_ptr(), ws.numel(),
-                                   err.data_ptr(), st), "decode_run")
-        launches[0] += 3
+        check(lib.piekv_decode_step_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), q.stride(1),
+                                          k.stride(0), k.stride(1), v.stride(0), v.stride(1), mv["pos"].data_ptr(),
+                                          pool.data_ptr(), out.data_ptr(), None, mv["indptr"].data_ptr(),
+                                          mv["indices"].data_ptr(), mv["last"].data_ptr(), B, HQ, HKV, D, 16,
+                                          cfg.num_pages, 2, C.byref(rope), sm_scale, ws.data_ptr(), ws.numel(),
+                                          err.data_ptr(), st), "decode_step_fused")
+        launches[0] += 1
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
-
-    # NOTE: q is rotated in place by the fused kernel; the 8 input variants therefore drift over the
-    # steps (rotations keep their norm), which does not change the work done.
 
     # ---- value: device-resident, CUDA graph of exactly `steps` steps -------------------------------
     with torch.cuda.stream(stream):
@@ -299,13 +292,9 @@ def run_ours(args):
         qkv_dev.copy_(qkv_host[i % n_var], non_blocking=True)
         mv_ = views(meta_dev, B)
         q_, k_, v_ = qkv_views(qkv_dev)
-        sl = ops.get_seq_lens(mv_["indptr"], mv_["last"], 16)
-        bi, kp = ops.get_batch_indices_positions(mv_["qo"], sl, B)
-        ops.rope_append_paged_kv_cache(q_, k_, v_, mv_["pos"], bi, kp, pool, mv_["indices"], mv_["indptr"],
-                                       mv_["last"], rope_cfg)
         wrapper.plan(mv_["indptr"], mv_["indices"], mv_["last"], HQ, HKV, D, 16, pos_encoding_mode="NONE",
                      q_data_type=cfg.dtype)
-        o = wrapper.run(q_, pool, out=out)
+        o = wrapper.run_fused(q_, k_, v_, mv_["pos"], pool, rope_cfg, out=out)
         out_host.copy_(o, non_blocking=True)
 
     for i in range(3):
@@ -337,13 +326,13 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "requests_per_gpu": B, "global_requests": B * n_gpus, "pool_pages": cfg.num_pages,
                        "parallelism": f"request-sharded x{n_gpus}, independent page pools, no collective",
                        "l2": "inputs larger than L2 (0.6 GB of KV per step vs 126 MB); no flush",
-                       "launch": "CUDA graph of all timed steps, 3 kernels per step",
+                       "launch": "CUDA graph of all timed steps, one fused kernel per step",
                        "step_algorithmic_bytes": step_bytes},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps},
             "gpu_launches": timed_launches,
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only; the fused step adds RoPE + append to it)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
                          "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "bytes_per_launch": kern_bytes,
                          "us_per_launch": kern_ms * 1e3,

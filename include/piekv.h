@@ -151,6 +151,25 @@ int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, cons
                      int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
                      int32_t *err, void *stream);
 
+/* One decode step in a single launch: rotate q and the new token's k (RoPE at pos_ids[b]), write
+ * k,v into slot kv_last_page_len[b]-1 of request b's last page, and attend over all of the
+ * request's pages including the new token.  The page table must already include the new token
+ * (the reference grows the page list before the forward pass,
+ * sdk/rust/inferlet/src/context.rs:489).  q, k and v are read only: unlike the three separate
+ * ops, q and k are NOT rotated in place.  Replaces the op sequence
+ * get_seq_lens / get_batch_indices_positions / apply_llama31_rope_pos_ids_inplace /
+ * append_paged_kv_cache / BatchDecodeWithPagedKVCacheWrapper.run of one decode layer
+ * (llama3.py:745-755,660-689). */
+int piekv_decode_step_fused(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                            int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                            int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
+                            void *out, float *lse, const int32_t *kv_indptr,
+                            const int32_t *kv_indices, const int32_t *kv_last_page_len, int32_t batch,
+                            int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
+                            int32_t page_size, int32_t num_pages, int32_t dtype,
+                            const piekv_rope_params *rope, float sm_scale, void *workspace,
+                            int64_t workspace_bytes, int32_t *err, void *stream);
+
 /* Bytes of scratch piekv_prefill_run needs. */
 int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads,
                                       int32_t head_dim);

@@ -68,6 +68,11 @@ SIGNATURES = {
         C.c_int,
         [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p],
     ),
+    "piekv_decode_step_fused": (
+        C.c_int,
+        [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
+         _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
+    ),
     "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
     "piekv_prefill_run": (
         C.c_int,
@@ -88,7 +93,7 @@ class PiekvError(RuntimeError):
 def _load() -> C.CDLL:
     if not LIB_PATH.exists():
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m pie_b200.build` "
+            f"{LIB_PATH} is missing: build it with `python pie_b200/build.py` "
             "(nvcc, sm_100a). pie_b200 has no fallback implementation."
         )
     lib = C.CDLL(str(LIB_PATH))

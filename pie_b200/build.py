@@ -1,6 +1,6 @@
 """Build libpiekv.so (sm_100a) in-tree with nvcc.
 
-`python -m pie_b200.build` compiles every translation unit under pie_b200/csrc into
+`python pie_b200/build.py` compiles every translation unit under pie_b200/csrc into
 pie_b200/libpiekv.so.  nvcc cross-compiles without a GPU.  Objects are cached under
 pie_b200/csrc/build/ and rebuilt when a source or header is newer.
 """

@@ -1,11 +1,29 @@
 // C ABI of the attention entry points: argument checks and kernel selection.
 #include "attn.cuh"
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace piekv {
 int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv);
 int64_t prefill_tc_workspace_bytes(int batch, int nnz, int hq);
+bool decode_fused_tma_supported(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn,
+                                int64_t k_sh, int64_t v_sn, int64_t v_sh);
+int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn, int64_t k_sh,
+                            int64_t v_sn, int64_t v_sh, const int32_t *pos_ids, const RopeDev &rope, void *workspace,
+                            int64_t workspace_bytes, cudaStream_t st);
+int launch_decode_append_general(void *q_out, const void *q, const void *k, const void *v, int64_t q_sn, int64_t q_sh,
+                                 int64_t k_sn, int64_t k_sh, int64_t v_sn, int64_t v_sh, const int32_t *pos_ids,
+                                 int32_t *bi_scratch, int32_t *pos_scratch, void *pool, const int32_t *kv_indices,
+                                 const int32_t *kv_indptr, const int32_t *kv_last_page_len, int batch, int hq, int hkv,
+                                 int dim, int page_size, int num_pages, int dtype, const RopeDev &rp, int32_t *err,
+                                 cudaStream_t st);
 }  // namespace piekv
+
+static const int64_t kCounterBytes = 65536;
+// scratch of the fused step's general path: batch_indices, positions, rotated q (fp32-sized upper bound)
+static int64_t general_fused_bytes(int batch, int hq, int dim) {
+  return kCounterBytes + ((int64_t)batch * 8 + 255) / 256 * 256 + (int64_t)batch * hq * dim * 4 + 256;
+}
 
 using namespace piekv;
 
@@ -30,7 +48,9 @@ extern "C" int64_t piekv_decode_workspace_bytes(int32_t batch, int32_t num_qo_he
                                                 int32_t head_dim) {
   (void)head_dim;
   if (batch < 0 || num_qo_heads <= 0 || num_kv_heads <= 0) return 0;
-  return decode_tma_workspace_bytes(batch, num_qo_heads, num_kv_heads);
+  const int64_t a = decode_tma_workspace_bytes(batch, num_qo_heads, num_kv_heads);
+  const int64_t b = general_fused_bytes(batch, num_qo_heads, head_dim);
+  return a > b ? a : b;
 }
 
 extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
@@ -65,6 +85,69 @@ extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_str
   if (batch == 0) return 0;
   if (decode_tma_supported(a, dtype)) return launch_decode_tma(a, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
   return launch_attn_generic(a, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                       int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                       int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
+                                       void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                       const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                       int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                                       int32_t dtype, const piekv_rope_params *rope, float sm_scale, void *workspace,
+                                       int64_t workspace_bytes, int32_t *err, void *stream) {
+  AttnArgs a{};
+  a.q = q;
+  a.q_sn = q_stride_n;
+  a.q_sh = q_stride_h;
+  a.pool = pool;
+  a.out = out;
+  a.lse = lse;
+  a.kv_indptr = kv_indptr;
+  a.kv_indices = kv_indices;
+  a.kv_last_page_len = kv_last_page_len;
+  a.batch = batch;
+  a.nnz = batch;
+  a.hq = num_qo_heads;
+  a.hkv = num_kv_heads;
+  a.dim = head_dim;
+  a.page_size = page_size;
+  a.num_pages = num_pages;
+  a.sm_scale = sm_scale;
+  a.err = err;
+  if (int rc = check_common(a, dtype, "decode_step_fused")) return rc;
+  if (int rc = check_rope(rope, head_dim, "decode_step_fused")) return rc;
+  if (batch == 0) return 0;
+  PIEKV_REQUIRE(k && v, "decode_step_fused: null k / v");
+  const bool do_rope = rope && rope->mode != PIEKV_ROPE_NONE;
+  PIEKV_REQUIRE(!do_rope || pos_ids, "decode_step_fused: pos_ids required when rope is on");
+  RopeDev rp;
+  fill_inv_freq(rope, head_dim, &rp);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (decode_fused_tma_supported(a, dtype, k, v, k_stride_n, k_stride_h, v_stride_n, v_stride_h))
+    return launch_decode_fused_tma(a, dtype, k, v, k_stride_n, k_stride_h, v_stride_n, v_stride_h, pos_ids, rp,
+                                   workspace, workspace_bytes, st);
+  // general path: metadata -> RoPE + append (rotated q into scratch) -> general attention
+  const int64_t need = general_fused_bytes(batch, num_qo_heads, head_dim);
+  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need,
+                "decode_step_fused: workspace too small (%lld < %lld bytes)", (long long)workspace_bytes,
+                (long long)need);
+  PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0,
+                "decode_step_fused: workspace must be 256-byte aligned");
+  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace) + kCounterBytes;
+  int32_t *bi = reinterpret_cast<int32_t *>(ws);
+  int32_t *pos = bi + batch;
+  void *q_rot = ws + ((int64_t)batch * 8 + 255) / 256 * 256;
+  if (int rc = launch_decode_append_general(q_rot, q, k, v, q_stride_n, q_stride_h, k_stride_n, k_stride_h,
+                                            v_stride_n, v_stride_h, pos_ids, bi, pos, pool, kv_indices, kv_indptr,
+                                            kv_last_page_len, batch, num_qo_heads, num_kv_heads, head_dim, page_size,
+                                            num_pages, dtype, rp, err, st))
+    return rc;
+  if (do_rope) {
+    a.q = q_rot;
+    a.q_sn = (int64_t)num_qo_heads * head_dim;
+    a.q_sh = head_dim;
+  }
+  return launch_attn_generic(a, dtype, st);
 }
 
 extern "C" int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t head_dim) {

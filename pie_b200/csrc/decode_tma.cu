@@ -22,6 +22,7 @@
 
 #include "attn.cuh"
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace piekv {
 
@@ -43,6 +44,18 @@ struct DecodeParams {
   float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
   int *counters;    // [batch], zero between launches
 };
+
+// Extra inputs of the fused step (RoPE + append + attention in one launch): the new token's
+// un-rotated k / v rows and RoPE position per request.  q in AttnArgs is then un-rotated too.
+struct FusedArgs {
+  const void *k_new;  // [batch, Hkv, 128]
+  const void *v_new;  // [batch, Hkv, 128]
+  int64_t k_sn, k_sh, v_sn, v_sh;
+  const int32_t *pos_ids;  // [batch]
+  RopeDev rope;
+};
+
+constexpr int kSmemBatch = 1024;  // kv_indptr is staged in shared memory up to this batch size
 
 __device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap *tmap, int coord4, uint64_t *bar) {
   asm volatile(
@@ -72,15 +85,17 @@ __device__ __forceinline__ int request_of_page(const int32_t *indptr, int batch,
   return lo;
 }
 
-template <typename T, int HKV>
+template <typename T, int HKV, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
-    decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, DecodeParams p) {
+    decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ DecodeParams p,
+                      const __grid_constant__ FusedArgs f) {
   constexpr int PG = 8 / HKV;  // pages per stage
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
   __shared__ int sh_abort;
   __shared__ int sh_last;
+  __shared__ int32_t sh_indptr[kSmemBatch + 1];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -90,14 +105,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   const AttnArgs &a = p.a;
   const int B = a.batch;
   const int c = blockIdx.x;
-  const int total_pages = a.kv_indptr[B];
-  // With fewer pages than CTAs only the first `total_pages` CTAs take part, so that every
-  // participating range is non-empty (the segment count of a request relies on that).
-  const int G = min((int)gridDim.x, max(total_pages, 1));
-  const int lo = c < G ? (int)((long long)c * total_pages / G) : 0;
-  const int hi = c < G ? (int)((long long)(c + 1) * total_pages / G) : 0;
-  const int group = a.hq / HKV;
-
+  // one coalesced read of the page-table offsets instead of a chain of dependent searches in L2
+  const int32_t *ip = a.kv_indptr;
+  if (B <= kSmemBatch) {
+    for (int x = threadIdx.x; x <= B; x += kThreads) sh_indptr[x] = __ldg(a.kv_indptr + x);
+    ip = sh_indptr;
+  }
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -108,17 +121,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_fence_init();
   }
   __syncthreads();
+  const int total_pages = ip[B];
+  // With fewer pages than CTAs only the first `total_pages` CTAs take part, so that every
+  // participating range is non-empty (the segment count of a request relies on that).
+  const int G = min((int)gridDim.x, max(total_pages, 1));
+  const int lo = c < G ? (int)((long long)c * total_pages / G) : 0;
+  const int hi = c < G ? (int)((long long)(c + 1) * total_pages / G) : 0;
+  const int group = a.hq / HKV;
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------------------------ producer
     int armed = 0;  // stages armed so far
     if (lo < hi) {
-      int b = request_of_page(a.kv_indptr, B, lo);
+      int b = request_of_page(ip, B, lo);
       int g = lo;
       bool stop = false;
       while (g < hi && !stop) {
-        while (b < B - 1 && a.kv_indptr[b + 1] <= g) ++b;
-        const int seg_end = min(hi, a.kv_indptr[b + 1]);
+        while (b < B - 1 && ip[b + 1] <= g) ++b;
+        const int seg_end = min(hi, ip[b + 1]);
         if (seg_end <= g) {  // non-monotone indptr: give up cleanly
           if (lane == 0) report_error(a.err, PIEKV_ERR_INDPTR, KID_DECODE, b, g);
           if (lane == 0) atomicExch(&sh_abort, 1);
@@ -176,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   // requests without any page: softmax over nothing -> zeros
   for (int b = c; b < B; b += gridDim.x) {
-    if (a.kv_indptr[b + 1] == a.kv_indptr[b]) {
+    if (ip[b + 1] == ip[b]) {
       for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32)
         out[(size_t)b * a.hq * kDim + x] = Elem<T>::from_f32(0.f);
       if (a.lse != nullptr)
@@ -187,16 +207,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   uint32_t qa[8][4];
   float o[16][4];
-  int b = request_of_page(a.kv_indptr, B, lo);
+  int b = request_of_page(ip, B, lo);
   int g = lo;
   int it = 0;
   bool aborted = false;
 
   while (g < hi) {
     // ================= open the segment of request b that starts at flat page g
-    while (b < B - 1 && a.kv_indptr[b + 1] <= g) ++b;
-    const int req_begin = a.kv_indptr[b];
-    const int req_end = a.kv_indptr[b + 1];
+    while (b < B - 1 && ip[b + 1] <= g) ++b;
+    const int req_begin = ip[b];
+    const int req_end = ip[b + 1];
     const int seg_end = min(hi, req_end);
     if (seg_end <= g) break;  // non-monotone indptr (the producer reports it)
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
@@ -221,6 +241,62 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
       last_len = last_len < 1 ? 1 : kPage;
     }
+    int rope_pos = 0;
+    int last_phys = -1;  // physical id of the request's last page when this segment contains it
+    if (FUSED) {
+      rope_pos = f.pos_ids[b];
+      if (f.rope.mode == PIEKV_ROPE_TABLE && (rope_pos < 0 || rope_pos >= f.rope.table_len)) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
+        rope_pos = 0;
+      }
+      if (seg_end == req_end) last_phys = __ldg(a.kv_indices + req_end - 1);
+      // rotate the query fragments in registers (one rounding to T, as the in-place op does)
+      if (f.rope.mode != PIEKV_ROPE_NONE) {
+        if (!f.rope.interleave) {
+          // element d pairs with d + 64: fragments ks and ks + 4 of the same thread
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+            for (int hi8 = 0; hi8 < 2; ++hi8) {
+              const int i0 = ks * 16 + hi8 * 8 + qlane * 2;
+              float c0, s0, c1, s1;
+              rope_cos_sin1(f.rope, rope_pos, i0, 64, c0, s0);
+              rope_cos_sin1(f.rope, rope_pos, i0 + 1, 64, c1, s1);
+#pragma unroll
+              for (int rr = 0; rr < 2; ++rr) {
+                const int j = hi8 * 2 + rr;
+                const float2 x = unpack2<T>(qa[ks][j]);
+                const float2 y = unpack2<T>(qa[ks + 4][j]);
+                float xa, ya, xb, yb;
+                rope_rotate(x.x, y.x, c0, s0, xa, ya);
+                rope_rotate(x.y, y.y, c1, s1, xb, yb);
+                qa[ks][j] = pack2<T>(xa, xb);
+                qa[ks + 4][j] = pack2<T>(ya, yb);
+              }
+            }
+          }
+        } else {
+          // pairs (2i, 2i+1) sit in one register
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+            for (int hi8 = 0; hi8 < 2; ++hi8) {
+              const int pair = (ks * 16 + hi8 * 8 + qlane * 2) >> 1;
+              float c0, s0;
+              rope_cos_sin1(f.rope, rope_pos, pair, 64, c0, s0);
+#pragma unroll
+              for (int rr = 0; rr < 2; ++rr) {
+                const int j = hi8 * 2 + rr;
+                const float2 x = unpack2<T>(qa[ks][j]);
+                float xa, ya;
+                rope_rotate(x.x, x.y, c0, s0, xa, ya);
+                qa[ks][j] = pack2<T>(xa, ya);
+              }
+            }
+          }
+        }
+      }
+    }
 
     // ================= stream the segment's pages
     while (g < seg_end) {
@@ -238,6 +314,61 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
         const uint32_t ktile = page_base + h * 4096;
         const uint32_t vtile = page_base + HKV * 4096 + h * 4096;
+        if (FUSED && g + pslot == req_end - 1) {
+          // This warp owns (last page, head h): rotate the new token's k, copy its v, store both
+          // into the pool for later steps and patch them into the staged tile for this one.
+          const int row = last_len - 1;
+          uint8_t *kp = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + h * 4096;
+          uint8_t *vp = kp + HKV * 4096;
+          const T *ksrc = reinterpret_cast<const T *>(f.k_new) + (size_t)b * f.k_sn + (size_t)h * f.k_sh;
+          const T *vsrc = reinterpret_cast<const T *>(f.v_new) + (size_t)b * f.v_sn + (size_t)h * f.v_sh;
+          const bool page_ok = last_phys >= 0 && last_phys < a.num_pages;
+          T *pool = reinterpret_cast<T *>(const_cast<void *>(a.pool));
+          T *kdst = pool + ((size_t)last_phys * 2 * kPage + row) * (HKV * kDim) + h * kDim;
+          T *vdst = kdst + (size_t)kPage * HKV * kDim;
+          // smem byte offset of element d of `row` inside a [2][16][64] swizzled tile
+          auto tile_off = [&](int d) { return (d >> 6) * 2048 + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2; };
+          if (f.rope.mode == PIEKV_ROPE_NONE) {
+            const int d = lane * 4;
+            const uint2 kv = *reinterpret_cast<const uint2 *>(ksrc + d);
+            *reinterpret_cast<uint2 *>(kp + tile_off(d)) = kv;
+            if (page_ok) *reinterpret_cast<uint2 *>(kdst + d) = kv;
+          } else if (!f.rope.interleave) {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+              const int i = lane + 32 * rr;
+              float cc, ss, xo, yo;
+              rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
+              rope_rotate(Elem<T>::to_f32(ksrc[i]), Elem<T>::to_f32(ksrc[i + 64]), cc, ss, xo, yo);
+              const T xt = Elem<T>::from_f32(xo), yt = Elem<T>::from_f32(yo);
+              *reinterpret_cast<T *>(kp + tile_off(i)) = xt;
+              *reinterpret_cast<T *>(kp + tile_off(i + 64)) = yt;
+              if (page_ok) {
+                kdst[i] = xt;
+                kdst[i + 64] = yt;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int rr = 0; rr < 2; ++rr) {
+              const int i = lane + 32 * rr;  // pair (2i, 2i+1)
+              float cc, ss, xo, yo;
+              rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
+              rope_rotate(Elem<T>::to_f32(ksrc[2 * i]), Elem<T>::to_f32(ksrc[2 * i + 1]), cc, ss, xo, yo);
+              const uint32_t pk = pack2<T>(xo, yo);
+              *reinterpret_cast<uint32_t *>(kp + tile_off(2 * i)) = pk;
+              if (page_ok) *reinterpret_cast<uint32_t *>(kdst + 2 * i) = pk;
+            }
+          }
+          {
+            const int d = lane * 4;
+            const uint2 vv = *reinterpret_cast<const uint2 *>(vsrc + d);
+            *reinterpret_cast<uint2 *>(vp + tile_off(d)) = vv;
+            if (page_ok) *reinterpret_cast<uint2 *>(vdst + d) = vv;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
         if (valid < kPage) {
           // rows past the end of the context may hold anything: zero the V rows so that
           // 0 * garbage cannot produce NaN (their scores are masked to -inf below)
@@ -457,31 +588,32 @@ int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int h
   return 0;
 }
 
-template <typename T, int HKV>
-int launch_t(const CUtensorMap &tm, const DecodeParams &p, cudaStream_t st) {
-  static bool configured = false;  // per (T, HKV) instantiation
+template <typename T, int HKV, bool FUSED>
+int launch_t(const CUtensorMap &tm, const DecodeParams &p, const FusedArgs &f, cudaStream_t st) {
+  static bool configured = false;  // per instantiation
   const int smem = kStages * kStageBytes + 1024;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<T, HKV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<T, HKV, FUSED>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return cuda_status(e, "decode: cudaFuncSetAttribute");
     configured = true;
   }
-  decode_tma_kernel<T, HKV><<<sm_count(), kThreads, smem, st>>>(tm, p);
+  decode_tma_kernel<T, HKV, FUSED><<<sm_count(), kThreads, smem, st>>>(tm, p, f);
   PIEKV_LAUNCH_CHECK("decode_tma_kernel");
   return 0;
 }
 
-template <typename T>
-int launch_h(const CUtensorMap &tm, const DecodeParams &p, cudaStream_t st) {
+template <typename T, bool FUSED>
+int launch_h(const CUtensorMap &tm, const DecodeParams &p, const FusedArgs &f, cudaStream_t st) {
   switch (p.a.hkv) {
     case 1:
-      return launch_t<T, 1>(tm, p, st);
+      return launch_t<T, 1, FUSED>(tm, p, f, st);
     case 2:
-      return launch_t<T, 2>(tm, p, st);
+      return launch_t<T, 2, FUSED>(tm, p, f, st);
     case 4:
-      return launch_t<T, 4>(tm, p, st);
+      return launch_t<T, 4, FUSED>(tm, p, f, st);
     case 8:
-      return launch_t<T, 8>(tm, p, st);
+      return launch_t<T, 8, FUSED>(tm, p, f, st);
   }
   set_error("decode: unsupported num_kv_heads %d", p.a.hkv);
   return 1;
@@ -508,25 +640,59 @@ int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
   return kCounterBytes + slots * pg * hq * (kDim * 4 + 8) + 256;
 }
 
-int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st) {
-  if (a.batch == 0) return 0;
+static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, DecodeParams *p,
+                   CUtensorMap *tm) {
   const int pg = 8 / a.hkv;
   const int64_t slots = (int64_t)sm_count() + a.batch;
   const int64_t need = decode_tma_workspace_bytes(a.batch, a.hq, a.hkv);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "decode: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)need);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
-  DecodeParams p;
-  p.a = a;
+  p->a = a;
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
-  p.counters = reinterpret_cast<int *>(ws);
-  p.part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
+  p->counters = reinterpret_cast<int *>(ws);
+  p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
   const int64_t ml_bytes = ((slots * pg * a.hq * 8 + 255) / 256) * 256;
-  p.part_o = reinterpret_cast<float *>(ws + kCounterBytes + ml_bytes);
+  p->part_o = reinterpret_cast<float *>(ws + kCounterBytes + ml_bytes);
+  return make_page_tensor_map(tm, a.pool, a.num_pages, a.hkv, dtype);
+}
+
+int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st) {
+  if (a.batch == 0) return 0;
+  DecodeParams p;
   CUtensorMap tm;
-  if (int rc = make_page_tensor_map(&tm, a.pool, a.num_pages, a.hkv, dtype)) return rc;
-  if (dtype == PIEKV_BF16) return launch_h<__nv_bfloat16>(tm, p, st);
-  return launch_h<__half>(tm, p, st);
+  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
+  FusedArgs f{};
+  if (dtype == PIEKV_BF16) return launch_h<__nv_bfloat16, false>(tm, p, f, st);
+  return launch_h<__half, false>(tm, p, f, st);
+}
+
+bool decode_fused_tma_supported(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn,
+                                int64_t k_sh, int64_t v_sn, int64_t v_sh) {
+  if (!decode_tma_supported(a, dtype)) return false;
+  if ((reinterpret_cast<uintptr_t>(k) & 7) || (reinterpret_cast<uintptr_t>(v) & 7)) return false;
+  if ((k_sn & 3) || (k_sh & 3) || (v_sn & 3) || (v_sh & 3)) return false;
+  return true;
+}
+
+int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn, int64_t k_sh,
+                            int64_t v_sn, int64_t v_sh, const int32_t *pos_ids, const RopeDev &rope, void *workspace,
+                            int64_t workspace_bytes, cudaStream_t st) {
+  if (a.batch == 0) return 0;
+  DecodeParams p;
+  CUtensorMap tm;
+  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
+  FusedArgs f;
+  f.k_new = k;
+  f.v_new = v;
+  f.k_sn = k_sn;
+  f.k_sh = k_sh;
+  f.v_sn = v_sn;
+  f.v_sh = v_sh;
+  f.pos_ids = pos_ids;
+  f.rope = rope;
+  if (dtype == PIEKV_BF16) return launch_h<__nv_bfloat16, true>(tm, p, f, st);
+  return launch_h<__half, true>(tm, p, f, st);
 }
 
 }  // namespace piekv

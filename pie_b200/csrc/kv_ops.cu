@@ -4,6 +4,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "rope.cuh"
 
 namespace piekv {
 
@@ -25,6 +26,12 @@ __global__ void meta_kernel(const int32_t *__restrict__ qo_indptr, const int32_t
     seq_lens_out[tid] = (np > 0 ? (np - 1) * page_size : 0) + kv_last_page_len[tid];
   }
   if (batch_indices != nullptr && tid < nnz) {
+    if (qo_indptr == nullptr) {  // decode: token i belongs to request i
+      int np = kv_indptr[tid + 1] - kv_indptr[tid];
+      batch_indices[tid] = tid;
+      positions[tid] = (np > 0 ? (np - 1) * page_size : 0) + kv_last_page_len[tid] - 1;
+      return;
+    }
     // first b with qo_indptr[b+1] > tid
     int lo = 0, hi = batch;  // answer in [0, batch)
     while (lo < hi) {
@@ -51,16 +58,6 @@ __global__ void meta_kernel(const int32_t *__restrict__ qo_indptr, const int32_t
 // =====================================================================================
 // RoPE + append
 // =====================================================================================
-
-constexpr int kMaxHalfDim = 128;  // head_dim <= 256
-
-struct RopeDev {
-  int mode;
-  int interleave;
-  int table_len;
-  const float *table;           // [table_len, D]
-  float inv_freq[kMaxHalfDim];  // final per-pair frequency (plain or Llama-3.1 scaled), fp32
-};
 
 template <typename T, int VEC>
 struct alignas(sizeof(T) * VEC) Vec {
@@ -140,6 +137,7 @@ __device__ __forceinline__ void rotate_pair_interleaved(const T *src, T *dst0, T
 }
 
 struct AppendArgs {
+  void *q_out;    // nullable: rotated q goes here ([n, Hq, D] contiguous) instead of back into q
   void *q;        // nullable
   void *k;        // nullable (rope-only call may pass only q)
   const void *v;  // nullable (rope-only call)
@@ -215,7 +213,8 @@ __global__ void rope_append_kernel(AppendArgs a, RopeDev rp) {
         for (int h = threadIdx.y; h < n_rot_heads; h += blockDim.y) {
           if (h < q_heads) {
             T *row = reinterpret_cast<T *>(a.q) + (size_t)tok * a.q_sn + (size_t)h * a.q_sh;
-            rotate_chunk<T, VEC>(row, row, nullptr, ch, half, false, c, s);
+            T *dst = a.q_out ? reinterpret_cast<T *>(a.q_out) + ((size_t)tok * a.hq + h) * D : row;
+            rotate_chunk<T, VEC>(row, dst, nullptr, ch, half, false, c, s);
           } else {
             int hk = h - q_heads;
             T *row = reinterpret_cast<T *>(a.k) + (size_t)tok * a.k_sn + (size_t)hk * a.k_sh;
@@ -235,7 +234,8 @@ __global__ void rope_append_kernel(AppendArgs a, RopeDev rp) {
         for (int h = threadIdx.y; h < n_rot_heads; h += blockDim.y) {
           if (h < q_heads) {
             T *row = reinterpret_cast<T *>(a.q) + (size_t)tok * a.q_sn + (size_t)h * a.q_sh;
-            rotate_pair_interleaved<T>(row, row, nullptr, pr, c[0], s[0]);
+            T *dst = a.q_out ? reinterpret_cast<T *>(a.q_out) + ((size_t)tok * a.hq + h) * D : row;
+            rotate_pair_interleaved<T>(row, dst, nullptr, pr, c[0], s[0]);
           } else {
             int hk = h - q_heads;
             T *row = reinterpret_cast<T *>(a.k) + (size_t)tok * a.k_sn + (size_t)hk * a.k_sh;
@@ -269,7 +269,7 @@ __global__ void rope_append_kernel(AppendArgs a, RopeDev rp) {
 // Per-pair frequencies in double, rounded once to fp32.  Formula of
 // pie/src/flashinfer_metal/kernels/metal_rope.metal:66-89 with the low/high/old_context
 // parameters the reference passes at pie/src/pie_worker/model/llama3.py:660-669.
-static void fill_inv_freq(const piekv_rope_params *rope, int head_dim, RopeDev *out) {
+void fill_inv_freq(const piekv_rope_params *rope, int head_dim, RopeDev *out) {
   const int half = head_dim / 2;
   out->mode = rope ? rope->mode : PIEKV_ROPE_NONE;
   out->interleave = rope ? rope->interleave : 0;
@@ -307,6 +307,7 @@ static int launch_rope_append_t(const AppendArgs &a, const RopeDev &rp, cudaStre
   bool vec_ok = (a.dim % (2 * VEC) == 0);
   auto stride_ok = [&](int64_t s) { return (s * (int64_t)es) % 16 == 0; };
   if (a.q) vec_ok = vec_ok && aligned16(a.q) && stride_ok(a.q_sn) && stride_ok(a.q_sh);
+  if (a.q_out) vec_ok = vec_ok && aligned16(a.q_out);
   if (a.k) vec_ok = vec_ok && aligned16(a.k) && stride_ok(a.k_sn) && stride_ok(a.k_sh);
   if (a.v) vec_ok = vec_ok && aligned16(a.v) && stride_ok(a.v_sn) && stride_ok(a.v_sh);
   if (a.pool) vec_ok = vec_ok && aligned16(a.pool);
@@ -383,6 +384,45 @@ __global__ void copy_pages_kernel(PoolPtrs pools, const int32_t *__restrict__ sr
   }
 }
 
+int launch_decode_append_general(void *q_out, const void *q, const void *k, const void *v, int64_t q_sn, int64_t q_sh,
+                                 int64_t k_sn, int64_t k_sh, int64_t v_sn, int64_t v_sh, const int32_t *pos_ids,
+                                 int32_t *bi_scratch, int32_t *pos_scratch, void *pool, const int32_t *kv_indices,
+                                 const int32_t *kv_indptr, const int32_t *kv_last_page_len, int batch, int hq, int hkv,
+                                 int dim, int page_size, int num_pages, int dtype, const RopeDev &rp, int32_t *err,
+                                 cudaStream_t st) {
+  meta_kernel<<<(batch + 255) / 256, 256, 0, st>>>(nullptr, kv_indptr, kv_last_page_len, nullptr, batch, batch,
+                                                   page_size, nullptr, bi_scratch, pos_scratch);
+  PIEKV_LAUNCH_CHECK("meta_kernel");
+  AppendArgs a{};
+  const bool do_rope = rp.mode != PIEKV_ROPE_NONE;
+  a.q_out = do_rope ? q_out : nullptr;
+  a.q = do_rope ? const_cast<void *>(q) : nullptr;
+  a.k = const_cast<void *>(k);
+  a.v = v;
+  a.q_sn = q_sn;
+  a.q_sh = q_sh;
+  a.k_sn = k_sn;
+  a.k_sh = k_sh;
+  a.v_sn = v_sn;
+  a.v_sh = v_sh;
+  a.pos_ids = pos_ids;
+  a.batch_indices = bi_scratch;
+  a.positions = pos_scratch;
+  a.pool = pool;
+  a.kv_indices = kv_indices;
+  a.kv_indptr = kv_indptr;
+  a.nnz = batch;
+  a.batch = batch;
+  a.hq = hq;
+  a.hkv = hkv;
+  a.dim = dim;
+  a.page_size = page_size;
+  a.num_pages = num_pages;
+  a.rotate_k_in_place = 0;
+  a.err = err;
+  return launch_rope_append(a, rp, dtype, st);
+}
+
 }  // namespace piekv
 
 using namespace piekv;
@@ -431,7 +471,8 @@ extern "C" int piekv_metadata(const int32_t *qo_indptr, const int32_t *kv_indptr
   return 0;
 }
 
-static int check_rope(const piekv_rope_params *rope, int head_dim, const char *who) {
+namespace piekv {
+int check_rope(const piekv_rope_params *rope, int head_dim, const char *who) {
   PIEKV_REQUIRE(head_dim > 0 && head_dim % 2 == 0 && head_dim / 2 <= kMaxHalfDim, "%s: head_dim %d unsupported", who,
                 head_dim);
   if (!rope) return 0;
@@ -447,6 +488,7 @@ static int check_rope(const piekv_rope_params *rope, int head_dim, const char *w
                   "%s: bad llama31 rope parameters", who);
   return 0;
 }
+}  // namespace piekv
 
 extern "C" int piekv_rope_inplace(void *q, void *k, int64_t q_stride_n, int64_t q_stride_h, int64_t k_stride_n,
                                   int64_t k_stride_h, const int32_t *pos_ids, int32_t nnz, int32_t num_qo_heads,

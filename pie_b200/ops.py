@@ -455,6 +455,48 @@ class BatchDecodeWithPagedKVCacheWrapper:
 
     forward = run
 
+    def run_fused(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
+                  paged_kv_cache: torch.Tensor, rope: Optional["RopeConfig"] = None,
+                  out: Optional[torch.Tensor] = None, return_lse: bool = False):
+        """One decode step in a single launch: RoPE of q and of the new k at `pos_ids`, append of k / v
+        into the last slot of every request's last page, attention over all pages.  Equivalent to the
+        reference's per-layer sequence at pie/src/pie_worker/model/llama3.py:660-689, except that q and
+        k are read only (not rotated in place).  The planned page table must already include the new
+        token, as it does in the reference."""
+        if self._plan is None:
+            raise RuntimeError("Must call plan() before run()")
+        pl = self._plan
+        for t, name in ((q, "q"), (k, "k"), (v, "v")):
+            _require_cuda(t, name)
+        _require_i32(pos_ids, "pos_ids")
+        num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
+        qs, ks, vs = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+        b = pl["batch"]
+        if tuple(q.shape) != (b, pl["hq"], pl["d"]) or tuple(k.shape) != (b, pl["hkv"], pl["d"]) \
+                or tuple(v.shape) != tuple(k.shape) or pos_ids.shape[0] < b:
+            raise ValueError(f"q {tuple(q.shape)} / k {tuple(k.shape)} / v {tuple(v.shape)} differ from the plan")
+        if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
+            raise ValueError("paged_kv_cache shape differs from the plan")
+        if not (q.dtype == k.dtype == v.dtype == paged_kv_cache.dtype):
+            raise ValueError("q, k, v and the cache must share one dtype")
+        if out is None:
+            out = torch.empty((b, pl["hq"], pl["d"]), dtype=q.dtype, device=q.device)
+        elif tuple(out.shape) != tuple(q.shape) or out.dtype != q.dtype or not out.is_contiguous():
+            raise ValueError("out must be a contiguous tensor shaped and typed like q")
+        lse = torch.empty((b, pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
+        rp = (rope if rope is not None else RopeConfig()).to_c(d)
+        ws = self.workspace_buffer
+        check(lib.piekv_decode_step_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1],
+                                          vs[0], vs[1], pos_ids.data_ptr(), paged_kv_cache.data_ptr(),
+                                          out.data_ptr(), lse.data_ptr() if lse is not None else None,
+                                          pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
+                                          pl["last_page_len"].data_ptr(), b, pl["hq"], pl["hkv"], pl["d"],
+                                          pl["page_size"], num_pages, _dtype_code(q.dtype, "fused decode"),
+                                          C.byref(rp), pl["sm_scale"], ws.data_ptr(), ws.numel(),
+                                          _err_word(q.device).data_ptr(), _stream(q.device)),
+              "BatchDecode.run_fused")
+        return (out, lse) if return_lse else out
+
 
 class BatchPrefillWithPagedKVCacheWrapper:
     """Packed variable-length (prefill / chunked / multi-token) attention over paged K/V.

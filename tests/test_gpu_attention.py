@@ -256,3 +256,96 @@ def test_prefill_against_oracle(dtype, hq, hkv, d, reqs, mode):
     out = _run_prefill(sc, mask, causal=(mode == "causal"))
     assert ops.device_error("cuda") is None
     assert (out.cpu().float() - ref.float()).abs().max().item() <= TOL[dtype]
+
+
+FUSED_CASES = [
+    (torch.bfloat16, 32, 8, 128, [37, 64, 100, 5, 1, 16, 17, 4096, 512, 33], "table", False),
+    (torch.float16, 32, 8, 128, [300, 1, 2048], "table", False),
+    (torch.bfloat16, 64, 8, 128, [129, 2000, 15, 16], "table", False),
+    (torch.bfloat16, 32, 4, 128, [77, 1025, 16, 3, 1], "table", False),
+    (torch.bfloat16, 8, 1, 128, [700, 5, 64, 129, 1], "table", True),
+    (torch.bfloat16, 32, 8, 128, [511, 4096, 2049], "llama31", False),
+    (torch.bfloat16, 32, 8, 128, [45, 160], "none", False),
+    (torch.float32, 4, 2, 64, [38, 65, 101, 6], "table", False),      # config 1 through the general path
+    (torch.bfloat16, 12, 4, 64, [50, 7, 130], "plain", False),        # general path, on-the-fly RoPE
+]
+
+
+@pytest.mark.parametrize("dtype,hq,hkv,d,ctx,mode,interleave", FUSED_CASES)
+def test_fused_decode_step(dtype, hq, hkv, d, ctx, mode, interleave):
+    """RoPE + append + attention in one call == the oracle's three ops in the reference's order."""
+    sc = make_scenario(hq, hkv, d, dtype, [(c - 1, 1) for c in ctx], seed=hq + len(ctx), scale=0.5)
+    m = sc.meta
+    theta = 500000.0
+    table = None
+    if mode == "none":
+        q_ref, k_ref = sc.q, sc.k
+        cfg = ops.RopeConfig(mode="none")
+    else:
+        inv = R.rope_inv_freq(d, theta, "plain" if mode == "plain" else "llama31", 1.0 if mode == "plain" else 8.0)
+        if mode == "table":
+            table = R.make_cos_sin_table(4200, inv)
+            c, s = table[m.pos_ids, : d // 2], table[m.pos_ids, d // 2:]
+            cfg = ops.RopeConfig(mode="table", cos_sin_table=dev(table), interleave=interleave)
+        else:
+            c, s = R.rope_cos_sin(m.pos_ids, inv)
+            cfg = ops.RopeConfig(mode=mode, theta=theta, scale=1.0 if mode == "plain" else 8.0, interleave=interleave)
+        q_ref, k_ref = R.apply_rope(sc.q, c, s, interleave), R.apply_rope(sc.k, c, s, interleave)
+    ref_pool = sc.pool.clone()
+    seq = R.get_seq_lens(m.kv_indptr, m.kv_last_page_len, 16)
+    bi, pos = R.get_batch_indices_positions(m.qo_indptr, seq, sc.n)
+    R.append_paged_kv_cache(k_ref, sc.v, bi, pos, ref_pool, m.kv_indices, m.kv_indptr)
+    ref = R.decode_attention(q_ref, ref_pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len)
+
+    pool, q, k, v = sc.pool.cuda(), sc.q.cuda(), sc.k.cuda(), sc.v.cuda()
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(_workspace(), "NHD")
+    w.plan(dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), hq, hkv, d, 16, q_data_type=dtype)
+    out = w.run_fused(q, k, v, dev(m.pos_ids), pool, cfg)
+    assert ops.device_error("cuda") is None
+    assert torch.equal(q.cpu(), sc.q) and torch.equal(k.cpu(), sc.k)  # inputs are read only
+    if mode in ("table", "none"):
+        assert torch.equal(pool.cpu().view(torch.uint8), ref_pool.view(torch.uint8))  # bit-exact pages
+    else:
+        from tests.util import ulp_diff_bf16
+        assert ulp_diff_bf16(pool.cpu(), ref_pool) <= 1
+    assert (out.cpu().float() - ref.float()).abs().max().item() <= TOL[dtype]
+    # the separate ops on the same inputs give the same pages and (within rounding) the same output
+    pool2, q2, k2 = sc.pool.cuda(), sc.q.cuda(), sc.k.cuda()
+    if mode != "none":
+        ops._rope_inplace(q2, k2, dev(m.pos_ids), cfg, "rope")
+    ops.append_paged_kv_cache(k2, v, dev(bi), dev(pos), pool2, dev(m.kv_indices), dev(m.kv_indptr),
+                              dev(m.kv_last_page_len))
+    out2 = w.run(q2, pool2)
+    assert torch.equal(pool2, pool)
+    assert (out2.float() - out.float()).abs().max().item() <= (1e-5 if dtype == torch.float32 else 4e-3)
+
+
+def test_fused_decode_many_steps_match_separate_ops():
+    """Sixteen consecutive fused steps keep the pool identical to the separate-op sequence."""
+    from pie_b200 import workloads as W2
+    hq, hkv, d = 32, 8, 128
+    reqs = W2.PagedRequests(W2.seeded_perm(256, 3))
+    for c in (15, 16, 100, 1, 250):
+        reqs.add(c)
+    metas = W2.decode_steps(reqs, 20)
+    pool_a = W2.randn((256, 2, 16, hkv, d), 5, torch.bfloat16, 0.5).cuda()
+    pool_b = pool_a.clone()
+    inv = R.rope_inv_freq(d, 500000.0, "llama31", 8.0)
+    cfg = ops.RopeConfig(mode="table", cos_sin_table=dev(R.make_cos_sin_table(512, inv)))
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(_workspace(), "NHD")
+    for i, m in enumerate(metas):
+        q = W2.randn((5, hq, d), 100 + i, torch.bfloat16, 0.5).cuda()
+        k = W2.randn((5, hkv, d), 200 + i, torch.bfloat16, 0.5).cuda()
+        v = W2.randn((5, hkv, d), 300 + i, torch.bfloat16, 0.5).cuda()
+        indptr, indices, last = dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len)
+        w.plan(indptr, indices, last, hq, hkv, d, 16, q_data_type=torch.bfloat16)
+        oa = w.run_fused(q, k, v, dev(m.pos_ids), pool_a, cfg)
+        q2, k2 = q.clone(), k.clone()
+        ops._rope_inplace(q2, k2, dev(m.pos_ids), cfg, "rope")
+        sl = ops.get_seq_lens(indptr, last, 16)
+        bi, kp = ops.get_batch_indices_positions(dev(m.qo_indptr), sl, 5)
+        ops.append_paged_kv_cache(k2, v, bi, kp, pool_b, indices, indptr, last)
+        ob = w.run(q2, pool_b)
+        assert torch.equal(pool_a, pool_b), i
+        assert (oa.float() - ob.float()).abs().max().item() <= 4e-3
+    assert ops.device_error("cuda") is None
