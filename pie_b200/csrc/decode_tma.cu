@@ -23,6 +23,7 @@
 #include "attn.cuh"
 #include "common.cuh"
 #include "rope.cuh"
+#include "tma.cuh"
 
 namespace piekv {
 
@@ -522,27 +523,32 @@ __global__ void __launch_bounds__(kThreads, 1)
     consumer_bar_sync();  // everyone has read sh_last before a later segment rewrites it
     if (!last) continue;
     __threadfence();
-    // merge every partial of request b: thread -> (query head tid/32 + 8k, 4 consecutive d)
+    // merge every partial of request b: thread -> (query head tid/32 + 8k, 4 consecutive d).
+    // Two passes so that the loads of a pass are independent of one another and stay in flight
+    // together: first the global maximum, then the weighted sums.
     const int d4 = (tid & 31) * 4;
+    const int nparts = nseg * PG;
+    const size_t part0 = (size_t)(c_first + b) * PG;  // partial index of (first CTA, sub 0)
     for (int qh = tid >> 5; qh < a.hq; qh += kConsumerWarps) {
-      float M = -INFINITY, L = 0.f;
+      float M = -INFINITY;
+#pragma unroll 8
+      for (int pp = 0; pp < nparts; ++pp) {
+        const float2 ml = __ldcg(p.part_ml + (part0 + pp) * a.hq + qh);
+        M = ml.y > 0.f ? fmaxf(M, ml.x) : M;
+      }
+      float L = 0.f;
       float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int cc = c_first; cc <= c_last; ++cc) {
-        for (int sub = 0; sub < PG; ++sub) {
-          const size_t idx = ((size_t)(cc + b) * PG + sub) * a.hq + qh;
-          const float2 ml = __ldcg(p.part_ml + idx);
-          if (!(ml.y > 0.f)) continue;  // that warp saw no page of the segment
-          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
-          const float Mn = fmaxf(M, ml.x);
-          const float w_old = fast_exp2(M - Mn);
-          const float w_new = fast_exp2(ml.x - Mn);
-          L = L * w_old + ml.y * w_new;
-          acc.x = acc.x * w_old + po.x * w_new;
-          acc.y = acc.y * w_old + po.y * w_new;
-          acc.z = acc.z * w_old + po.z * w_new;
-          acc.w = acc.w * w_old + po.w * w_new;
-          M = Mn;
-        }
+#pragma unroll 8
+      for (int pp = 0; pp < nparts; ++pp) {
+        const size_t idx = (part0 + pp) * a.hq + qh;
+        const float2 ml = __ldcg(p.part_ml + idx);
+        const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
+        const float w = ml.y > 0.f ? fast_exp2(ml.x - M) : 0.f;  // a warp that saw no page: weight 0
+        L = fmaf(ml.y, w, L);
+        acc.x = fmaf(po.x, w, acc.x);
+        acc.y = fmaf(po.y, w, acc.y);
+        acc.z = fmaf(po.z, w, acc.z);
+        acc.w = fmaf(po.w, w, acc.w);
       }
       const float inv = L > 0.f ? 1.f / L : 0.f;
       uint2 pk;
@@ -554,38 +560,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     if (tid == 0) p.counters[b] = 0;  // leave the counter ready for the next launch
   }
-}
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
-                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn) return fn;
-  void *sym = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
-      qres != cudaDriverEntryPointSuccess)
-    return nullptr;
-  fn = reinterpret_cast<EncodeTiledFn>(sym);
-  return fn;
-}
-
-// Pool [P, 2, 16, Hkv, 128] seen as {64 d, 16 tokens, 2 d-halves, Hkv, 2P (page, K|V)}.
-int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int hkv, int dtype) {
-  EncodeTiledFn enc = get_encode_fn();
-  PIEKV_REQUIRE(enc != nullptr, "decode: cuTensorMapEncodeTiled is not available from the driver");
-  const cuuint64_t row = (cuuint64_t)hkv * kDim * 2;  // bytes of one token row (all heads)
-  cuuint64_t gdim[5] = {64, (cuuint64_t)kPage, 2, (cuuint64_t)hkv, (cuuint64_t)num_pages * 2};
-  cuuint64_t gstr[4] = {row, 128, 256, (cuuint64_t)kPage * row};
-  cuuint32_t box[5] = {64, (cuuint32_t)kPage, 2, (cuuint32_t)hkv, 2};
-  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  CUresult r = enc(tm, dtype == PIEKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5,
-                   const_cast<void *>(pool), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  PIEKV_REQUIRE(r == CUDA_SUCCESS, "decode: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return 0;
 }
 
 template <typename T, int HKV, bool FUSED>
@@ -654,7 +628,8 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
   p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
   const int64_t ml_bytes = ((slots * pg * a.hq * 8 + 255) / 256) * 256;
   p->part_o = reinterpret_cast<float *>(ws + kCounterBytes + ml_bytes);
-  return make_page_tensor_map(tm, a.pool, a.num_pages, a.hkv, dtype);
+  return make_page_tensor_map(tm, a.pool, a.num_pages, a.hkv, dtype, /*box_halves=*/2, /*box_heads=*/a.hkv,
+                              /*box_kv=*/2);
 }
 
 int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st) {
