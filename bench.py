@@ -348,6 +348,105 @@ def run_ours(args):
 
 
 # ---------------------------------------------------------------------------------------------
+# secondary workload: chunked prefill mix (tensor-core bound); `--workload prefill`
+# ---------------------------------------------------------------------------------------------
+def run_prefill(args):
+    """8 new prompts of 2048 tokens + 8 chunks of 512 tokens on 6144 cached tokens, causal, 32q/8kv
+    heads, D128, bf16, page 16.  A step = RoPE + append of all 20480 tokens, then paged prefill attention.
+    Reports causal-exact TFLOP/s (4*D*Hq*allowed pairs) of the attention kernel against the measured
+    bf16 matmul peak."""
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG3
+    scale = args.prefill_scale
+    meta = W.config3_meta(num_prompts=max(1, int(8 * scale)), num_chunks=max(1, int(8 * scale)), num_pages=args.pages
+                          if args.pages != 32768 else 8192)
+    num_pages = args.pages if args.pages != 32768 else 8192
+    HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    n = meta.nnz
+    pool = W.randn((num_pages, 2, 16, HKV, D), 300, cfg.dtype, 0.5, device=dev)
+    qkv = W.randn((n, (HQ + 2 * HKV) * D), 301, cfg.dtype, 0.5, device=dev)
+    q = qkv[:, : HQ * D].view(n, HQ, D)
+    k = qkv[:, HQ * D: (HQ + HKV) * D].view(n, HKV, D)
+    v = qkv[:, (HQ + HKV) * D:].view(n, HKV, D)
+
+    def t(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+    qo, indptr, indices, last, pos = t(meta.qo_indptr), t(meta.kv_indptr), t(meta.kv_indices), \
+        t(meta.kv_last_page_len), t(meta.pos_ids)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
+    out = torch.empty((n, HQ, D), dtype=cfg.dtype, device=dev)
+    seq = ops.get_seq_lens(indptr, last, 16)
+    bi, kp = ops.get_batch_indices_positions(qo, seq, n)
+    rope = ops.RopeConfig()
+    w = ops.BatchPrefillWithPagedKVCacheWrapper(ws, "NHD")
+    w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, causal=True, q_data_type=cfg.dtype)
+    mask = None
+    if args.prefill_mask:
+        from oracle import paged_kv_ref as R  # only to expand the reference-form boolean mask once
+        runs, rptr = [], [0]
+        for b in range(meta.batch):
+            qlen = int(meta.qo_indptr[b + 1] - meta.qo_indptr[b])
+            r, _ = R.causal_brle(int(meta.seq_lens[b]) - qlen, qlen)
+            runs += r
+            rptr += [rptr[-1] + i + 1 for i in range(qlen)]
+        mask = t(R.build_flat_mask(meta.qo_indptr, meta.kv_indptr, meta.kv_last_page_len, 16, runs, rptr))
+        w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, custom_mask=mask, q_data_type=cfg.dtype)
+
+    def step():
+        ops.rope_append_paged_kv_cache(q, k, v, pos, bi, kp, pool, indices, indptr, last, rope)
+        w.run(q, pool, out=out)
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(dev.index or 0)
+    with sampler:
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    # attention kernel alone
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record()
+    for _ in range(args.steps):
+        w.run(q, pool, out=out)
+    a1.record()
+    torch.cuda.synchronize(dev)
+    attn_ms = a0.elapsed_time(a1) / args.steps
+    pairs = W.causal_pairs(meta)
+    flops = 4.0 * D * HQ * pairs
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            pk = json.load(f)
+        peak, peak_kind = float(pk["bf16_tflops_sustained"]), "measured (sustained bf16 matmul)"
+    except Exception:
+        peak, peak_kind = 1400.0, "fallback"
+    tf = flops / (attn_ms * 1e-3) / 1e12
+    line = {
+        "metric": "prefill_tokens_per_s", "value": n / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": f"chunked prefill mix: {meta.batch} requests, {n} query tokens, causal "
+                               f"({'boolean custom mask' if mask is not None else 'native causal flag'}), "
+                               "32q/8kv heads, D128, bf16, page16", "pool_pages": num_pages},
+        "clocks": sampler.summary(),
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": tf, "peak": peak,
+                     "unit": "TFLOP/s", "frac": tf / peak, "peak_source": peak_kind, "traffic": None,
+                     "flops_causal_exact": flops, "ms_per_launch": attn_ms},
+        "device_error_word": ops.device_error(dev),
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
 # CPU arms
 # ---------------------------------------------------------------------------------------------
 class CpuPath:
@@ -450,7 +549,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1024)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-steps", type=int, default=0, help="CPU-baseline sample size in steps (0 = ~20 s)")
@@ -458,10 +557,16 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
     ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
     ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
+    ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
+    ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_ours(args)
 

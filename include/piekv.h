@@ -170,24 +170,39 @@ int piekv_decode_step_fused(const void *q, const void *k, const void *v, int64_t
                             const piekv_rope_params *rope, float sm_scale, void *workspace,
                             int64_t workspace_bytes, int32_t *err, void *stream);
 
-/* Bytes of scratch piekv_prefill_run needs. */
+/* Bytes of scratch the prefill entry points need for `batch` requests with `nnz` query tokens over
+ * a pool of `num_pages` pages; `mask_bytes` = number of entries of the flat boolean mask (0: none). */
 int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads,
-                                      int32_t head_dim);
+                                      int32_t head_dim, int32_t num_pages, int64_t mask_bytes);
+
+/* Once per batch (stream-ordered, no host synchronisation): builds in the workspace the work
+ * list of query tiles and, for a custom mask, its bit-packed form with a per-tile "any allowed"
+ * summary, so that the per-layer runs read 1 bit per pair instead of 1 byte and skip kv tiles no
+ * query of the tile may see.  Replaces BatchPrefillWithPagedKVCacheWrapper.plan
+ * (llama3.py:779-791), which the reference calls once per step before the layer loop. */
+int piekv_prefill_plan(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                       const int32_t *kv_last_page_len, const uint8_t *custom_mask,
+                       int64_t mask_bytes, int32_t causal, int32_t batch, int32_t nnz,
+                       int32_t page_size, int32_t num_pages, void *workspace,
+                       int64_t workspace_bytes, int32_t *err, void *stream);
 
 /* Packed variable-length attention over paged K/V: query token j of request b (rows
  * qo_indptr[b]..qo_indptr[b+1]) attends to cached token t of that request when
- *   (!causal || t <= kv_len_b - qo_len_b + j)  and
- *   (custom_mask == NULL || custom_mask[off_b + j*kv_len_b + t] != 0),
- * off_b = sum_{b'<b} qo_len_b' * kv_len_b'   (flat bool layout of
- * pie/src/pie_worker/batching.py:113-135).
- * Replaces BatchPrefillWithPagedKVCacheWrapper.plan/run (llama3.py:307-309,779-791,689). */
+ *   custom_mask != NULL:  custom_mask[off_b + j*kv_len_b + t] != 0,
+ *                         off_b = sum_{b'<b} qo_len_b' * kv_len_b'
+ *                         (flat bool layout of pie/src/pie_worker/batching.py:113-135);
+ *   otherwise:            !causal || t <= kv_len_b - qo_len_b + j.
+ * `planned` != 0: piekv_prefill_plan was already called on this workspace with the same
+ * metadata and mask (one plan, many layers); 0: the plan is built inside this call.
+ * Replaces BatchPrefillWithPagedKVCacheWrapper.run (llama3.py:307-309,689). */
 int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
                       void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
                       const int32_t *kv_indices, const int32_t *kv_last_page_len,
-                      const uint8_t *custom_mask, int32_t causal, int32_t batch, int32_t nnz,
-                      int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
-                      int32_t page_size, int32_t num_pages, int32_t dtype, float sm_scale,
-                      void *workspace, int64_t workspace_bytes, int32_t *err, void *stream);
+                      const uint8_t *custom_mask, int64_t mask_bytes, int32_t causal,
+                      int32_t planned, int32_t batch, int32_t nnz, int32_t num_qo_heads,
+                      int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                      int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
+                      int32_t *err, void *stream);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */
 

@@ -73,11 +73,15 @@ SIGNATURES = {
         [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
          _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
     ),
-    "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
+    "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32, _i64]),
+    "piekv_prefill_plan": (
+        C.c_int,
+        [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _p, _i64, _p, _p],
+    ),
     "piekv_prefill_run": (
         C.c_int,
-        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
-         _f32, _p, _i64, _p, _p],
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+         _i32, _i32, _f32, _p, _i64, _p, _p],
     ),
     "piekv_copy_pages": (
         C.c_int,

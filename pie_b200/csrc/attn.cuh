@@ -29,8 +29,13 @@ int launch_attn_generic(const AttnArgs &a, int dtype, cudaStream_t st);
 bool decode_tma_supported(const AttnArgs &a, int dtype);
 int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st);
 
-// tuned prefill (tcgen05): 16-bit, D=128, page 16
+// tuned prefill (tcgen05): 16-bit, D=128, page 16.  plan builds the work list (and packs a custom
+// mask) into the workspace; launch_prefill_tc consumes that plan.
 bool prefill_tc_supported(const AttnArgs &a, int dtype);
-int launch_prefill_tc(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st);
+int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t mask_bytes);
+int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                        cudaStream_t st);
+int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                      cudaStream_t st);
 
 }  // namespace piekv

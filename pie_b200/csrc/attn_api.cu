@@ -5,7 +5,6 @@
 
 namespace piekv {
 int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv);
-int64_t prefill_tc_workspace_bytes(int batch, int nnz, int hq);
 bool decode_fused_tma_supported(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn,
                                 int64_t k_sh, int64_t v_sn, int64_t v_sh);
 int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn, int64_t k_sh,
@@ -150,20 +149,11 @@ extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void 
   return launch_attn_generic(a, dtype, st);
 }
 
-extern "C" int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t head_dim) {
-  (void)head_dim;
-  if (batch < 0 || nnz < 0 || num_qo_heads <= 0) return 0;
-  return prefill_tc_workspace_bytes(batch, nnz, num_qo_heads);
-}
-
-extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
-                                 float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
-                                 const int32_t *kv_indices, const int32_t *kv_last_page_len,
-                                 const uint8_t *custom_mask, int32_t causal, int32_t batch, int32_t nnz,
-                                 int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
-                                 int32_t num_pages, int32_t dtype, float sm_scale, void *workspace,
-                                 int64_t workspace_bytes, int32_t *err, void *stream) {
-  AttnArgs a{};
+static void fill_prefill_args(AttnArgs &a, const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                              void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
+                              const int32_t *kv_indices, const int32_t *kv_last_page_len, const uint8_t *custom_mask,
+                              int32_t causal, int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t num_kv_heads,
+                              int32_t head_dim, int32_t page_size, int32_t num_pages, float sm_scale, int32_t *err) {
   a.q = q;
   a.q_sn = q_stride_n;
   a.q_sh = q_stride_h;
@@ -175,7 +165,7 @@ extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_st
   a.kv_indices = kv_indices;
   a.kv_last_page_len = kv_last_page_len;
   a.mask = custom_mask;
-  a.causal = causal;
+  a.causal = custom_mask ? 0 : causal;  // a mask alone decides, as in the reference
   a.batch = batch;
   a.nnz = nnz;
   a.hq = num_qo_heads;
@@ -185,9 +175,49 @@ extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_st
   a.num_pages = num_pages;
   a.sm_scale = sm_scale;
   a.err = err;
+}
+
+extern "C" int64_t piekv_prefill_workspace_bytes(int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t head_dim,
+                                                 int32_t num_pages, int64_t mask_bytes) {
+  (void)head_dim;
+  (void)num_qo_heads;
+  if (batch < 0 || nnz < 0 || num_pages < 0 || mask_bytes < 0) return 0;
+  return prefill_tc_workspace_bytes(batch, nnz, num_pages, mask_bytes);
+}
+
+extern "C" int piekv_prefill_plan(const int32_t *qo_indptr, const int32_t *kv_indptr, const int32_t *kv_last_page_len,
+                                  const uint8_t *custom_mask, int64_t mask_bytes, int32_t causal, int32_t batch,
+                                  int32_t nnz, int32_t page_size, int32_t num_pages, void *workspace,
+                                  int64_t workspace_bytes, int32_t *err, void *stream) {
+  PIEKV_REQUIRE(batch >= 0 && nnz >= 0 && page_size > 0 && num_pages > 0, "prefill_plan: bad sizes");
+  PIEKV_REQUIRE(nnz == 0 || (qo_indptr && kv_indptr && kv_last_page_len), "prefill_plan: null pointer");
+  PIEKV_REQUIRE(custom_mask == nullptr || mask_bytes >= 0, "prefill_plan: negative mask size");
+  if (page_size != 16) return 0;  // the general kernel needs no plan
+  AttnArgs a{};
+  fill_prefill_args(a, nullptr, 0, 0, nullptr, nullptr, nullptr, qo_indptr, kv_indptr, nullptr, kv_last_page_len,
+                    custom_mask, causal, batch, nnz, 1, 1, 128, page_size, num_pages, 1.f, err);
+  return launch_prefill_plan(a, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
+                                 float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
+                                 const int32_t *kv_indices, const int32_t *kv_last_page_len,
+                                 const uint8_t *custom_mask, int64_t mask_bytes, int32_t causal, int32_t planned,
+                                 int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t num_kv_heads,
+                                 int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype, float sm_scale,
+                                 void *workspace, int64_t workspace_bytes, int32_t *err, void *stream) {
+  AttnArgs a{};
+  fill_prefill_args(a, q, q_stride_n, q_stride_h, pool, out, lse, qo_indptr, kv_indptr, kv_indices, kv_last_page_len,
+                    custom_mask, causal, batch, nnz, num_qo_heads, num_kv_heads, head_dim, page_size, num_pages,
+                    sm_scale, err);
   if (int rc = check_common(a, dtype, "prefill_run")) return rc;
   PIEKV_REQUIRE(nnz == 0 || qo_indptr != nullptr, "prefill_run: qo_indptr is null");
   if (batch == 0 || nnz == 0) return 0;
-  if (prefill_tc_supported(a, dtype)) return launch_prefill_tc(a, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
+  if (prefill_tc_supported(a, dtype)) {
+    if (!planned) {
+      if (int rc = launch_prefill_plan(a, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream)) return rc;
+    }
+    return launch_prefill_tc(a, dtype, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream);
+  }
   return launch_attn_generic(a, dtype, (cudaStream_t)stream);
 }

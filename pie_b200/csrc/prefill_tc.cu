@@ -45,32 +45,198 @@ constexpr int kColS = 0, kColO = 256;
 constexpr int kCounterBytes = 65536;
 constexpr int kSortBins = 1024;
 
+// Plan of one batch, built on the device into the workspace (after the counter area):
+//   header | tile_base[B+1] | poff[B+1] | moff[B+1] | tiles[max_tiles] | summary[max_tiles][sw] | packed mask
+struct PlanView {
+  int *ntiles;             // header word 0
+  int32_t *tile_base;      // first q-tile index of every request (prefix of ceil(qo_len / 128))
+  long long *poff;         // packed-mask offset of every request, in 16-byte units
+  long long *moff;         // byte offset of every request in the flat boolean mask
+  int2 *tiles;             // (request, first row within the request), heaviest first
+  uint32_t *summary;       // bit j of row t: kv tile j of q tile t has at least one allowed pair
+  uint4 *packed;           // per query row ceil(kv_len/128) x 128 mask bits
+  int sw;                  // words per summary row
+  int max_tiles;
+  int64_t bytes;           // total workspace bytes including the counter area
+};
+
+PlanView plan_view(void *workspace, int batch, int nnz, int num_pages, int64_t mask_bytes) {
+  PlanView v;
+  v.max_tiles = (nnz + kBM - 1) / kBM + batch;
+  v.sw = mask_bytes > 0 ? ((num_pages + 7) / 8 + 31) / 32 : 0;
+  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
+  int64_t off = kCounterBytes;
+  auto take = [&](int64_t bytes) {
+    int64_t o = off;
+    off += (bytes + 255) / 256 * 256;
+    return ws ? ws + o : nullptr;
+  };
+  v.ntiles = reinterpret_cast<int *>(take(256));
+  v.tile_base = reinterpret_cast<int32_t *>(take((int64_t)(batch + 1) * 4));
+  v.poff = reinterpret_cast<long long *>(take((int64_t)(batch + 1) * 8));
+  v.moff = reinterpret_cast<long long *>(take((int64_t)(batch + 1) * 8));
+  v.tiles = reinterpret_cast<int2 *>(take((int64_t)v.max_tiles * 8));
+  v.summary = reinterpret_cast<uint32_t *>(take((int64_t)v.max_tiles * v.sw * 4));
+  // every row is padded to whole 128-bit groups: at most 16 bytes more than its share of mask_bytes / 8
+  v.packed = reinterpret_cast<uint4 *>(take(mask_bytes > 0 ? mask_bytes / 8 + (int64_t)nnz * 16 + 16 : 0));
+  v.bytes = off;
+  return v;
+}
+
 struct PrefillParams {
   AttnArgs a;
-  const int2 *tiles;  // (request, first row of the tile within the request), heaviest first
+  const int2 *tiles;
   const int *ntiles;
+  const int32_t *tile_base;
+  const long long *poff;
+  const uint32_t *summary;
+  const uint4 *packed;
+  int sw;
+  int has_mask;
 };
+
+__device__ __forceinline__ int kv_len_of(const int32_t *kv_indptr, const int32_t *last, int b, int page_size) {
+  const int np = kv_indptr[b + 1] - kv_indptr[b];
+  return np > 0 ? (np - 1) * page_size + last[b] : 0;
+}
+
+// per-request prefix sums: q tiles, packed-mask rows (16-byte units), flat-mask bytes.  One block.
+__global__ void prefill_scan_kernel(const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
+                                    const int32_t *__restrict__ last, int batch, int page_size, int32_t *tile_base,
+                                    long long *poff, long long *moff) {
+  __shared__ long long sh[3][32];
+  __shared__ long long carry[3];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  if (threadIdx.x < 3) carry[threadIdx.x] = 0;
+  __syncthreads();
+  for (int base = 0; base < batch; base += blockDim.x) {
+    const int b = base + threadIdx.x;
+    long long v[3] = {0, 0, 0};
+    if (b < batch) {
+      const long long qo = qo_indptr[b + 1] - qo_indptr[b];
+      const long long kv = kv_len_of(kv_indptr, last, b, page_size);
+      v[0] = (qo + kBM - 1) / kBM;
+      v[1] = qo * ((kv + 127) / 128);
+      v[2] = qo * kv;
+    }
+    long long incl[3];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      long long x = v[q];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        long long y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      incl[q] = x;
+      if (lane == 31) sh[q][warp] = x;
+    }
+    __syncthreads();
+    if (warp == 0) {
+#pragma unroll
+      for (int q = 0; q < 3; ++q) {
+        long long x = lane < nw ? sh[q][lane] : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          long long y = __shfl_up_sync(0xffffffffu, x, d);
+          if (lane >= d) x += y;
+        }
+        sh[q][lane] = x;  // inclusive over warps
+      }
+    }
+    __syncthreads();
+    long long excl[3];
+#pragma unroll
+    for (int q = 0; q < 3; ++q) excl[q] = carry[q] + (warp > 0 ? sh[q][warp - 1] : 0) + incl[q] - v[q];
+    if (b < batch) {
+      tile_base[b] = (int32_t)excl[0];
+      poff[b] = excl[1];
+      moff[b] = excl[2];
+    }
+    __syncthreads();
+    if (threadIdx.x == blockDim.x - 1) {
+#pragma unroll
+      for (int q = 0; q < 3; ++q) carry[q] = excl[q] + v[q];
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    tile_base[batch] = (int32_t)carry[0];
+    poff[batch] = carry[1];
+    moff[batch] = carry[2];
+  }
+}
+
+// flat boolean mask -> 128-bit groups per (query row, kv tile) + per-(q tile, kv tile) "any" bits.
+// One warp per query row.
+__global__ void prefill_pack_mask_kernel(const uint8_t *__restrict__ mask, const int32_t *__restrict__ qo_indptr,
+                                         const int32_t *__restrict__ kv_indptr, const int32_t *__restrict__ last,
+                                         int batch, int nnz, int page_size, const int32_t *__restrict__ tile_base,
+                                         const long long *__restrict__ poff, const long long *__restrict__ moff,
+                                         uint4 *packed, uint32_t *summary, int sw) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= nnz) return;
+  int lo = 0, hi = batch;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (qo_indptr[mid + 1] > i)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  const int b = lo < batch ? lo : batch - 1;
+  const int j = i - qo_indptr[b];
+  const int kv = kv_len_of(kv_indptr, last, b, page_size);
+  const int groups = (kv + 127) / 128;
+  const uint8_t *src = mask + moff[b] + (long long)j * kv;
+  uint32_t *dst = reinterpret_cast<uint32_t *>(packed + poff[b] + (long long)j * groups);
+  uint32_t *srow = summary + (size_t)(tile_base[b] + j / kBM) * sw;
+  for (int g = 0; g < groups; ++g) {
+    uint32_t any = 0;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const int t = g * 128 + w * 32 + lane;
+      const uint32_t word = __ballot_sync(0xffffffffu, t < kv && src[t] != 0);
+      if (lane == w) dst[g * 4 + w] = word;
+      any |= word;
+    }
+    if (lane == 0 && any != 0) {
+      uint32_t *sp = srow + (g >> 5);
+      const uint32_t bit = 1u << (g & 31);
+      if ((*(volatile uint32_t *)sp & bit) == 0) atomicOr(sp, bit);
+    }
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // work list: one entry per (request, 128-row tile), ordered by decreasing number of kv tiles
 // ------------------------------------------------------------------------------------------------
 __global__ void prefill_plan_kernel(const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
                                     const int32_t *__restrict__ kv_last_page_len, int batch, int page_size, int causal,
-                                    int2 *tiles, int *ntiles, int max_tiles) {
+                                    const int32_t *__restrict__ tile_base, const uint32_t *__restrict__ summary, int sw,
+                                    int has_mask, int2 *tiles, int *ntiles, int max_tiles) {
   __shared__ int hist[kSortBins];
   for (int i = threadIdx.x; i < kSortBins; i += blockDim.x) hist[i] = 0;
   __syncthreads();
-  auto key_of = [&](int qo_len, int kv_len, int r0) {
-    int hi = causal ? min(kv_len, kv_len - qo_len + r0 + kBM) : kv_len;
-    int nt = hi > 0 ? (hi + kBN - 1) / kBN : 0;
+  auto key_of = [&](int b, int qo_len, int kv_len, int r0) {
+    int nt;
+    if (has_mask) {
+      nt = 0;
+      const uint32_t *srow = summary + (size_t)(tile_base[b] + r0 / kBM) * sw;
+      const int words = ((kv_len + kBN - 1) / kBN + 31) / 32;
+      for (int w = 0; w < words; ++w) nt += __popc(srow[w]);
+    } else {
+      int hi = causal ? min(kv_len, kv_len - qo_len + r0 + kBM) : kv_len;
+      nt = hi > 0 ? (hi + kBN - 1) / kBN : 0;
+    }
     nt = nt < kSortBins ? nt : kSortBins - 1;
     return kSortBins - 1 - nt;  // bin 0 = most work
   };
   for (int b = threadIdx.x; b < batch; b += blockDim.x) {
     int qo_len = qo_indptr[b + 1] - qo_indptr[b];
-    int np = kv_indptr[b + 1] - kv_indptr[b];
-    int kv_len = np > 0 ? (np - 1) * page_size + kv_last_page_len[b] : 0;
-    for (int r0 = 0; r0 < qo_len; r0 += kBM) atomicAdd(&hist[key_of(qo_len, kv_len, r0)], 1);
+    int kv_len = kv_len_of(kv_indptr, kv_last_page_len, b, page_size);
+    for (int r0 = 0; r0 < qo_len; r0 += kBM) atomicAdd(&hist[key_of(b, qo_len, kv_len, r0)], 1);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -85,10 +251,9 @@ __global__ void prefill_plan_kernel(const int32_t *__restrict__ qo_indptr, const
   __syncthreads();
   for (int b = threadIdx.x; b < batch; b += blockDim.x) {
     int qo_len = qo_indptr[b + 1] - qo_indptr[b];
-    int np = kv_indptr[b + 1] - kv_indptr[b];
-    int kv_len = np > 0 ? (np - 1) * page_size + kv_last_page_len[b] : 0;
+    int kv_len = kv_len_of(kv_indptr, kv_last_page_len, b, page_size);
     for (int r0 = 0; r0 < qo_len; r0 += kBM) {
-      int pos = atomicAdd(&hist[key_of(qo_len, kv_len, r0)], 1);
+      int pos = atomicAdd(&hist[key_of(b, qo_len, kv_len, r0)], 1);
       if (pos < max_tiles) tiles[pos] = make_int2(b, r0);
     }
   }
@@ -139,11 +304,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   const int kv_len = np > 0 ? (np - 1) * kPage + last_len : 0;
   const int rows = min(kBM, qo_len - r0);  // valid query rows of this tile
-  const int kv_hi = a.causal ? min(kv_len, kv_len - qo_len + r0 + kBM) : kv_len;
+  const bool has_mask = p.has_mask != 0;
+  const int kv_hi = (a.causal && !has_mask) ? min(kv_len, kv_len - qo_len + r0 + kBM) : kv_len;
   const int n_tiles = kv_hi > 0 ? (kv_hi + kBN - 1) / kBN : 0;
+  const int groups = (kv_len + kBN - 1) / kBN;  // 128-bit mask groups per query row
+  // with a custom mask, kv tiles without a single allowed pair are skipped by every role
+  const uint32_t *srow = has_mask ? p.summary + (size_t)(p.tile_base[b] + r0 / kBM) * p.sw : nullptr;
+  auto active = [&](int j) { return !has_mask || ((__ldg(srow + (j >> 5)) >> (j & 31)) & 1u) != 0; };
+  int n_active = n_tiles;
+  if (has_mask) {
+    n_active = 0;
+    for (int w = 0; w < (n_tiles + 31) / 32; ++w) n_active += __popc(__ldg(srow + w));
+  }
   T *out = reinterpret_cast<T *>(a.out);
 
-  if (n_tiles == 0) {  // nothing to attend to: zeros (uniform for the whole CTA, before any allocation)
+  if (n_active == 0) {  // nothing to attend to: zeros (uniform for the whole CTA, before any allocation)
     for (int x = threadIdx.x; x < rows * (kDim / 8); x += kThreads) {
       const int r = x / (kDim / 8), c8 = x % (kDim / 8);
       *reinterpret_cast<uint4 *>(out + ((size_t)(q0 + r0 + r) * a.hq + h) * kDim + c8 * 8) = make_uint4(0, 0, 0, 0);
@@ -156,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;
-  const uint32_t kv_smem = base + kTileBytes;                    // stage s: K at +s*64K, V at +s*64K+32K
+  const uint32_t kv_smem = base + kTileBytes;  // stage s: K at +s*64K, V at +s*64K+32K
   const uint32_t p_smem = base + kTileBytes * (1 + 2 * kStages);
   uint8_t *p_ptr = base_ptr + kTileBytes * (1 + 2 * kStages);
 
@@ -184,18 +359,19 @@ __global__ void __launch_bounds__(kThreads, 1)
   tc::fence_after_sync();
   const uint32_t tmem = tmem_slot;
   volatile int *abort_flag = &sh_abort;
-  constexpr bool kBf16 = sizeof(T) == 2 && !std::is_same<T, __half>::value;
+  constexpr bool kBf16 = !std::is_same<T, __half>::value;
 
   if (warp == 4) {
     // ================================================================== TMA producer
-    int armed = 0;
+    int it = 0;  // tiles loaded so far
     if (lane == 0) {
       mbar_arrive_expect_tx(&q_full, kTileBytes);
       tma_load_4d(q_smem, &tmap_q, 0, q0 + r0, 0, h, &q_full);
     }
     for (int j = 0; j < n_tiles; ++j) {
-      const int s = j % kStages;
-      const uint32_t k = j / kStages;
+      if (!active(j)) continue;
+      const int s = it % kStages;
+      const uint32_t k = it / kStages;
       // page id of this lane's page (lanes 0-7), loaded before the wait so it is in flight
       const int pi = j * 8 + lane;
       int page = (lane < 8 && pi < np) ? __ldg(a.kv_indices + p0 + pi) : a.num_pages;
@@ -219,52 +395,56 @@ __global__ void __launch_bounds__(kThreads, 1)
         tma_load_5d(vdst, &tmap_kv, 0, 0, 0, hk, page * 2 + 1, &kv_full[s]);
         tma_load_5d(vdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2 + 1, &kv_full[s]);
       }
-      ++armed;
+      ++it;
     }
     // drain: the CTA must not retire while a bulk copy may still be landing
     __syncwarp();
     if (lane == 0) {
       mbar_wait(&q_full, 0, 200000000ull);
-      const int first = armed > kStages ? armed - kStages : 0;
-      for (int j = first; j < armed; ++j) mbar_wait(&kv_full[j % kStages], (j / kStages) & 1, 200000000ull);
+      const int first = it > kStages ? it - kStages : 0;
+      for (int x = first; x < it; ++x) mbar_wait(&kv_full[x % kStages], (x / kStages) & 1, 200000000ull);
     }
   } else if (warp == 5) {
     // ================================================================== MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::instr_desc(kBf16, false, false, kBM, kBN);
       constexpr uint32_t idesc_pv = tc::instr_desc(kBf16, false, true, kBM, kDim);
+      // O += P V for the it-th processed tile
+      auto issue_pv = [&](int jj) -> bool {
+        const int s = jj % kStages;
+        if (!wait_or_abort(&p_full, jj & 1, abort_flag)) return false;
+        tc::fence_after_sync();
+        const uint32_t v_smem = kv_smem + s * 2 * kTileBytes + kTileBytes;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          tc::mma_ss(tmem + kColO, tc::desc_k_major(p_smem + (ks >> 2) * kHalfBytes + (ks & 3) * 32),
+                     tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc::commit(&pv_done);
+        tc::commit(&kv_empty[s]);
+        return true;
+      };
       bool ok = wait_or_abort(&q_full, 0, abort_flag);
-      for (int j = 0; ok && j <= n_tiles; ++j) {
-        if (j < n_tiles) {
-          const int s = j % kStages, sb = j & 1;
-          ok = wait_or_abort(&kv_full[s], (j / kStages) & 1, abort_flag) &&
-               wait_or_abort(&s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag);
-          if (!ok) break;
-          tc::fence_after_sync();
-          const uint32_t k_smem = kv_smem + s * 2 * kTileBytes;
+      int it = 0;  // S tiles issued so far
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (!active(j)) continue;
+        const int s = it % kStages, sb = it & 1;
+        ok = wait_or_abort(&kv_full[s], (it / kStages) & 1, abort_flag) &&
+             wait_or_abort(&s_empty[sb], ((it >> 1) & 1) ^ 1, abort_flag);
+        if (!ok) break;
+        tc::fence_after_sync();
+        const uint32_t k_smem = kv_smem + s * 2 * kTileBytes;
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-            tc::mma_ss(tmem + kColS + sb * kBN, tc::desc_k_major(q_smem + off), tc::desc_k_major(k_smem + off),
-                       idesc_qk, ks > 0 ? 1u : 0u);
-          }
-          tc::commit(&s_full[sb]);
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
+          tc::mma_ss(tmem + kColS + sb * kBN, tc::desc_k_major(q_smem + off), tc::desc_k_major(k_smem + off), idesc_qk,
+                     ks > 0 ? 1u : 0u);
         }
-        if (j >= 1) {
-          const int jj = j - 1, s = jj % kStages;
-          ok = wait_or_abort(&p_full, jj & 1, abort_flag);
-          if (!ok) break;
-          tc::fence_after_sync();
-          const uint32_t v_smem = kv_smem + s * 2 * kTileBytes + kTileBytes;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            tc::mma_ss(tmem + kColO, tc::desc_k_major(p_smem + (ks >> 2) * kHalfBytes + (ks & 3) * 32),
-                       tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
-          }
-          tc::commit(&pv_done);
-          tc::commit(&kv_empty[s]);
-        }
+        tc::commit(&s_full[sb]);
+        if (it >= 1) ok = issue_pv(it - 1);
+        ++it;
       }
+      if (ok && it >= 1) ok = issue_pv(it - 1);
       if (!ok) {
         if (!*abort_flag) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 200);
         atomicExch(&sh_abort, 1);
@@ -272,19 +452,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ================================================================== softmax (thread = row)
-    const int row = warp * 32 + lane;             // row of the tile = TMEM lane
+    const int row = warp * 32 + lane;  // row of the tile = TMEM lane
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const bool row_valid = row < rows;
     // last allowed token of this row (inclusive)
-    const int limit = row_valid ? (a.causal ? min(kv_len - 1, kv_len - qo_len + r0 + row) : kv_len - 1) : -1;
+    const int limit = row_valid ? ((a.causal && !has_mask) ? min(kv_len - 1, kv_len - qo_len + r0 + row) : kv_len - 1) : -1;
+    const uint4 *mrow = has_mask ? p.packed + p.poff[b] + (long long)(r0 + (row_valid ? row : 0)) * groups : nullptr;
     const float c = a.sm_scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     uint32_t sreg[128];
+    int it = 0;
 
     for (int j = 0; j < n_tiles; ++j) {
-      const int sb = j & 1;
-      ok = wait_or_abort(&s_full[sb], (j >> 1) & 1, abort_flag);
+      if (!active(j)) continue;
+      const int sb = it & 1;
+      uint4 mw = make_uint4(0, 0, 0, 0);
+      if (has_mask && row_valid) mw = __ldg(mrow + j);  // in flight while we wait for S
+      ok = wait_or_abort(&s_full[sb], (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc::fence_after_sync();
       const uint32_t s_addr = tmem + lane_base + kColS + sb * kBN;
@@ -296,11 +481,19 @@ __global__ void __launch_bounds__(kThreads, 1)
 
       // ---- running maximum (lazy) and probabilities
       const int t0 = j * kBN;
-      const bool full_tile = t0 + kBN - 1 <= limit;  // no masking needed for this row
+      const bool full_tile = has_mask ? (mw.x & mw.y & mw.z & mw.w) == 0xffffffffu : t0 + kBN - 1 <= limit;
       float mx = -INFINITY;
       if (full_tile) {
 #pragma unroll
         for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+      } else if (has_mask) {
+        const uint32_t mwords[4] = {mw.x, mw.y, mw.z, mw.w};
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const float v = ((mwords[i >> 5] >> (i & 31)) & 1u) ? __uint_as_float(sreg[i]) : -INFINITY;
+          sreg[i] = __float_as_uint(v);
+          mx = fmaxf(mx, v);
+        }
       } else {
 #pragma unroll
         for (int i = 0; i < 128; ++i) {
@@ -316,7 +509,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         alpha = fast_exp2(m_ref - mx);  // m_ref = -inf on the first hit: 0
         l *= alpha;
         m_ref = mx;
-        rescale = j > 0;
+        rescale = it > 0;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
       float sum = 0.f;
@@ -330,8 +523,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       l += sum;
 
       // ---- P buffer free and O stable once PV of the previous tile has completed
-      if (j > 0) {
-        ok = wait_or_abort(&pv_done, (j - 1) & 1, abort_flag);
+      if (it > 0) {
+        ok = wait_or_abort(&pv_done, (it - 1) & 1, abort_flag);
         if (!ok) break;
         tc::fence_after_sync();
       }
@@ -361,10 +554,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       fence_proxy_async_smem();
       tc::fence_before_sync();
       mbar_arrive(&p_full);
+      ++it;
     }
 
     // ---- epilogue: O / l -> out
-    if (ok) ok = wait_or_abort(&pv_done, (n_tiles - 1) & 1, abort_flag);
+    if (ok) ok = wait_or_abort(&pv_done, (n_active - 1) & 1, abort_flag);
     if (ok) {
       tc::fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -409,7 +603,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 bool prefill_tc_supported(const AttnArgs &a, int dtype) {
   if (dtype != PIEKV_BF16 && dtype != PIEKV_F16) return false;
   if (a.dim != kDim || a.page_size != kPage) return false;
-  if (a.mask != nullptr) return false;
   if (a.hq % a.hkv != 0) return false;
   if ((reinterpret_cast<uintptr_t>(a.pool) & 15) || (reinterpret_cast<uintptr_t>(a.q) & 15) ||
       (reinterpret_cast<uintptr_t>(a.out) & 15))
@@ -418,11 +611,35 @@ bool prefill_tc_supported(const AttnArgs &a, int dtype) {
   return true;
 }
 
-static int64_t max_tiles_of(int batch, int nnz) { return (int64_t)(nnz + kBM - 1) / kBM + batch; }
+int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t mask_bytes) {
+  return plan_view(nullptr, batch, nnz, num_pages, mask_bytes).bytes;
+}
 
-int64_t prefill_tc_workspace_bytes(int batch, int nnz, int hq) {
-  (void)hq;
-  return kCounterBytes + 256 + max_tiles_of(batch, nnz) * (int64_t)sizeof(int2);
+// Build the plan of a batch in the workspace: per-request offsets, the bit-packed mask with its
+// tile summary (custom mask only) and the work list.  Stream-ordered, no host synchronisation.
+int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                        cudaStream_t st) {
+  if (a.nnz == 0 || a.batch == 0) return 0;
+  const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, a.mask ? mask_bytes : 0);
+  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= v.bytes, "prefill: workspace too small (%lld < %lld bytes)",
+                (long long)workspace_bytes, (long long)v.bytes);
+  PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "prefill: workspace must be 256-byte aligned");
+  prefill_scan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size,
+                                          v.tile_base, v.poff, v.moff);
+  PIEKV_LAUNCH_CHECK("prefill_scan_kernel");
+  if (a.mask != nullptr) {
+    cudaError_t e = cudaMemsetAsync(v.summary, 0, (size_t)v.max_tiles * v.sw * 4, st);
+    if (e != cudaSuccess) return cuda_status(e, "prefill: cudaMemsetAsync");
+    prefill_pack_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(a.mask, a.qo_indptr, a.kv_indptr, a.kv_last_page_len,
+                                                               a.batch, a.nnz, a.page_size, v.tile_base, v.poff, v.moff,
+                                                               v.packed, v.summary, v.sw);
+    PIEKV_LAUNCH_CHECK("prefill_pack_mask_kernel");
+  }
+  prefill_plan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size, a.causal,
+                                          v.tile_base, v.summary, v.sw, a.mask != nullptr ? 1 : 0, v.tiles, v.ntiles,
+                                          v.max_tiles);
+  PIEKV_LAUNCH_CHECK("prefill_plan_kernel");
+  return 0;
 }
 
 template <typename T>
@@ -442,26 +659,28 @@ static int launch_prefill_t(const AttnArgs &a, const CUtensorMap &tq, const CUte
   return 0;
 }
 
-int launch_prefill_tc(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, cudaStream_t st) {
+// Attention over a batch whose plan is already in the workspace.
+int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                      cudaStream_t st) {
   if (a.nnz == 0 || a.batch == 0) return 0;
-  const int64_t need = prefill_tc_workspace_bytes(a.batch, a.nnz, a.hq);
-  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "prefill: workspace too small (%lld < %lld bytes)",
-                (long long)workspace_bytes, (long long)need);
-  PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "prefill: workspace must be 256-byte aligned");
-  const int max_tiles = (int)max_tiles_of(a.batch, a.nnz);
-  uint8_t *ws = reinterpret_cast<uint8_t *>(workspace) + kCounterBytes;
+  const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, a.mask ? mask_bytes : 0);
+  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= v.bytes, "prefill: workspace too small (%lld < %lld bytes)",
+                (long long)workspace_bytes, (long long)v.bytes);
   PrefillParams p;
   p.a = a;
-  p.ntiles = reinterpret_cast<int *>(ws);
-  p.tiles = reinterpret_cast<int2 *>(ws + 256);
-  prefill_plan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size, a.causal,
-                                          const_cast<int2 *>(p.tiles), const_cast<int *>(p.ntiles), max_tiles);
-  PIEKV_LAUNCH_CHECK("prefill_plan_kernel");
+  p.ntiles = v.ntiles;
+  p.tiles = v.tiles;
+  p.tile_base = v.tile_base;
+  p.poff = v.poff;
+  p.summary = v.summary;
+  p.packed = v.packed;
+  p.sw = v.sw;
+  p.has_mask = a.mask != nullptr ? 1 : 0;
   CUtensorMap tq, tkv;
   if (int rc = make_q_tensor_map(&tq, a.q, a.nnz, a.hq, a.q_sn, a.q_sh, dtype, kBM)) return rc;
   if (int rc = make_page_tensor_map(&tkv, a.pool, a.num_pages, a.hkv, dtype, 1, 1, 1)) return rc;
-  if (dtype == PIEKV_BF16) return launch_prefill_t<__nv_bfloat16>(a, tq, tkv, p, max_tiles, st);
-  return launch_prefill_t<__half>(a, tq, tkv, p, max_tiles, st);
+  if (dtype == PIEKV_BF16) return launch_prefill_t<__nv_bfloat16>(a, tq, tkv, p, v.max_tiles, st);
+  return launch_prefill_t<__half>(a, tq, tkv, p, v.max_tiles, st);
 }
 
 }  // namespace piekv

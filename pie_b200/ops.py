@@ -550,8 +550,29 @@ class BatchPrefillWithPagedKVCacheWrapper:
         self._plan = dict(qo_indptr=qo_indptr, indptr=paged_kv_indptr, indices=paged_kv_indices,
                           last_page_len=paged_kv_last_page_len, batch=batch, hq=int(num_qo_heads),
                           hkv=int(num_kv_heads), d=int(head_dim_qk), page_size=int(page_size), mask=mask,
-                          causal=bool(causal), dtype=q_data_type,
+                          mask_bytes=int(mask.numel()) if mask is not None else 0,
+                          causal=bool(causal), dtype=q_data_type, planned_for=None,
                           sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim_qk))
+
+    def _device_plan(self, n: int, num_pages: int) -> None:
+        """Build the work list (and pack the mask) on the device once per plan(); later run() calls
+        of the same batch - one per layer in the reference - reuse it."""
+        pl = self._plan
+        key = (n, num_pages)
+        if pl["planned_for"] == key:
+            return
+        ws = self.workspace_buffer
+        need = lib.piekv_prefill_workspace_bytes(pl["batch"], n, pl["hq"], pl["d"], num_pages, pl["mask_bytes"])
+        if ws.numel() < need:
+            raise ValueError(f"workspace_buffer too small: {ws.numel()} < {need} bytes")
+        dev = pl["qo_indptr"].device
+        check(lib.piekv_prefill_plan(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
+                                     pl["last_page_len"].data_ptr(),
+                                     pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
+                                     1 if pl["causal"] else 0, pl["batch"], n, pl["page_size"], num_pages,
+                                     ws.data_ptr(), ws.numel(), _err_word(dev).data_ptr(), _stream(dev)),
+              "BatchPrefill.plan")
+        pl["planned_for"] = key
 
     def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, out: Optional[torch.Tensor] = None,
             return_lse: bool = False):
@@ -574,15 +595,13 @@ class BatchPrefillWithPagedKVCacheWrapper:
             raise ValueError("out must be a contiguous tensor shaped and typed like q")
         lse = torch.empty((n, pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
         ws = self.workspace_buffer
-        need = lib.piekv_prefill_workspace_bytes(pl["batch"], n, pl["hq"], pl["d"])
-        if ws.numel() < need:
-            raise ValueError(f"workspace_buffer too small: {ws.numel()} < {need} bytes")
+        self._device_plan(n, num_pages)
         check(lib.piekv_prefill_run(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
                                     lse.data_ptr() if lse is not None else None, pl["qo_indptr"].data_ptr(),
                                     pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
                                     pl["last_page_len"].data_ptr(),
-                                    pl["mask"].data_ptr() if pl["mask"] is not None else None,
-                                    1 if pl["causal"] else 0, pl["batch"], n, pl["hq"], pl["hkv"], pl["d"],
+                                    pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
+                                    1 if pl["causal"] else 0, 1, pl["batch"], n, pl["hq"], pl["hkv"], pl["d"],
                                     pl["page_size"], num_pages, _dtype_code(q.dtype, "prefill run"),
                                     pl["sm_scale"], ws.data_ptr(), ws.numel(), _err_word(q.device).data_ptr(),
                                     _stream(q.device)), "BatchPrefill.run")
