@@ -8,13 +8,15 @@
 //   K_j [2 d-halves][128 tokens][64 d]    K-major B operand            (2 TMA boxes per page)
 //   V_j [2 d-halves][128 tokens][64 d]    MN-major B operand           (2 TMA boxes per page)
 //   P_j [2 token-halves][128 rows][64 t]  K-major A operand, written by the softmax threads
-// Warp roles: warps 0-3 softmax (thread = query row = TMEM lane), warp 4 TMA producer, warp 5
-// MMA issuer and TMEM owner.  The MMA warp runs one tile ahead on S (S is double buffered), the
+// Warp roles: warps 0-7 softmax (two threads per query row, 64 kv columns each), warp 8 TMA
+// producer (K ring of 3 tiles, V ring of 2, independent cursors), warp 9 MMA issuer and TMEM owner.  The MMA warp runs one tile ahead on S (S is double buffered), the
 // softmax threads keep the running maximum lazily (O in TMEM is only rescaled when the maximum
 // grows by more than 2^8), so tile j's softmax overlaps QK of tile j+1 and PV of tile j-1.
 //
-// Masking: causal with offset (token t allowed iff t <= kv_len - qo_len + row) or none.  A flat
-// boolean custom mask is handled by the general kernel (see attn_api.cu).
+// Masking: causal with offset (token t allowed iff t <= kv_len - qo_len + row), none, or a custom
+// mask.  The flat boolean mask of the reference is bit-packed once per batch by the plan kernels
+// (128 bits per query row and kv tile) together with a per-(query tile, kv tile) "any allowed"
+// summary; kv tiles no row of the query tile may see are skipped by every role.
 //
 // Every wait is bounded; on a timeout the CTA records PIEKV_ERR_WAIT_TIMEOUT, all roles leave
 // their loops, outstanding bulk copies are drained and TMEM is released before the CTA exits.
@@ -35,11 +37,14 @@ constexpr int kDim = 128;
 constexpr int kPage = 16;
 constexpr int kBM = 128;  // query rows per CTA
 constexpr int kBN = 128;  // kv tokens per tile (8 pages)
-constexpr int kStages = 2;
-constexpr int kThreads = 192;
+constexpr int kKStages = 3;  // K tiles in flight (needed early, by S = Q K^T)
+constexpr int kVStages = 2;  // V tiles in flight (needed a softmax later, by O += P V)
+constexpr int kSoftmaxWarps = 8;  // two threads per query row: each owns 64 of the 128 kv columns
+constexpr int kProducerWarp = kSoftmaxWarps, kMmaWarp = kSoftmaxWarps + 1;
+constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr int kTileBytes = 32768;  // one 128 x 128 16-bit operand tile
 constexpr int kHalfBytes = 16384;  // one 128 x 64 half of it
-constexpr int kSmemBytes = kTileBytes * (1 + 2 * kStages + 1) + 1024;
+constexpr int kSmemBytes = kTileBytes * (1 + kKStages + kVStages + 1) + 1024;
 constexpr int kTmemCols = 512;
 constexpr int kColS = 0, kColO = 256;
 constexpr int kCounterBytes = 65536;
@@ -277,9 +282,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                       const __grid_constant__ PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, kv_full[kStages], kv_empty[kStages], s_full[2], s_empty[2], p_full, pv_done;
+  __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages],
+      s_full[2], s_empty[2], p_full, pv_done, pair_bar[4];
   __shared__ uint32_t tmem_slot;
   __shared__ int sh_abort;
+  __shared__ float xch_sum[2][kBM];  // [column half][row]: partial softmax denominators (epilogue)
 
   const AttnArgs &a = p.a;
   const int warp = threadIdx.x >> 5;
@@ -331,26 +338,32 @@ __global__ void __launch_bounds__(kThreads, 1)
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t *base_ptr = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t q_smem = base;
-  const uint32_t kv_smem = base + kTileBytes;  // stage s: K at +s*64K, V at +s*64K+32K
-  const uint32_t p_smem = base + kTileBytes * (1 + 2 * kStages);
-  uint8_t *p_ptr = base_ptr + kTileBytes * (1 + 2 * kStages);
+  const uint32_t k_smem0 = base + kTileBytes;                   // K stage s at + s * 32K
+  const uint32_t v_smem0 = base + kTileBytes * (1 + kKStages);  // V stage s at + s * 32K
+  const uint32_t p_smem = base + kTileBytes * (1 + kKStages + kVStages);
+  uint8_t *p_ptr = base_ptr + kTileBytes * (1 + kKStages + kVStages);
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < kStages; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+    for (int s = 0; s < kKStages; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+    }
+    for (int s = 0; s < kVStages; ++s) {
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 128);
+      mbar_init(&s_empty[s], kSoftmaxWarps * 32);
     }
-    mbar_init(&p_full, 128);
+    mbar_init(&p_full, kSoftmaxWarps * 32);
+    for (int s = 0; s < 4; ++s) mbar_init(&pair_bar[s], 64);
     mbar_init(&pv_done, 1);
     sh_abort = 0;
     mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc::tmem_alloc(&tmem_slot, kTmemCols);
     tc::tmem_relinquish();
   }
@@ -361,85 +374,121 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int *abort_flag = &sh_abort;
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ================================================================== TMA producer
-    int it = 0;  // tiles loaded so far
+    // K and V have their own rings and cursors, so K runs ahead of V by the depth of its ring
+    int k_armed = 0, v_armed = 0;  // K / V tiles issued so far
+    int jk = 0, jv = 0;            // next kv tile index to consider for K / for V
     if (lane == 0) {
       mbar_arrive_expect_tx(&q_full, kTileBytes);
       tma_load_4d(q_smem, &tmap_q, 0, q0 + r0, 0, h, &q_full);
     }
-    for (int j = 0; j < n_tiles; ++j) {
-      if (!active(j)) continue;
-      const int s = it % kStages;
-      const uint32_t k = it / kStages;
-      // page id of this lane's page (lanes 0-7), loaded before the wait so it is in flight
+    auto page_of = [&](int j) {
       const int pi = j * 8 + lane;
       int page = (lane < 8 && pi < np) ? __ldg(a.kv_indices + p0 + pi) : a.num_pages;
       if (lane < 8 && pi < np && (page < 0 || page >= a.num_pages)) {
         report_error(a.err, PIEKV_ERR_PAGE_ID, KID_PREFILL, p0 + pi, page);
         page = a.num_pages;  // outside the tensor map: zero fill
       }
-      if (!wait_or_abort(&kv_empty[s], (k & 1) ^ 1, abort_flag)) {
-        if (lane == 0 && !*abort_flag) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 100 + s);
-        if (lane == 0) atomicExch(&sh_abort, 1);
-        break;
+      return page;  // pages beyond the request's list are out of range too: their rows are zero-filled
+    };
+    uint64_t idle_since = 0;
+    while (k_armed < n_active || v_armed < n_active) {
+      bool progressed = false;
+      if (k_armed < n_active) {
+        const int ks = k_armed % kKStages;
+        if (mbar_try_wait(&k_empty[ks], ((k_armed / kKStages) & 1) ^ 1)) {
+          while (!active(jk)) ++jk;
+          const int page = page_of(jk);
+          if (lane == 0) mbar_arrive_expect_tx(&k_full[ks], kTileBytes);
+          __syncwarp();
+          if (lane < 8) {
+            const uint32_t kdst = k_smem0 + ks * kTileBytes + lane * 2048;
+            tma_load_5d(kdst, &tmap_kv, 0, 0, 0, hk, page * 2, &k_full[ks]);
+            tma_load_5d(kdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2, &k_full[ks]);
+          }
+          ++jk;
+          ++k_armed;
+          progressed = true;
+        }
       }
-      if (lane == 0) mbar_arrive_expect_tx(&kv_full[s], 2 * kTileBytes);
-      __syncwarp();
-      if (lane < 8) {
-        // pages beyond the request's list use an out-of-range coordinate: the rows are zero-filled
-        const uint32_t kdst = kv_smem + s * 2 * kTileBytes + lane * 2048;
-        const uint32_t vdst = kdst + kTileBytes;
-        tma_load_5d(kdst, &tmap_kv, 0, 0, 0, hk, page * 2, &kv_full[s]);
-        tma_load_5d(kdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2, &kv_full[s]);
-        tma_load_5d(vdst, &tmap_kv, 0, 0, 0, hk, page * 2 + 1, &kv_full[s]);
-        tma_load_5d(vdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2 + 1, &kv_full[s]);
+      if (v_armed < n_active && v_armed < k_armed) {
+        const int vs = v_armed % kVStages;
+        if (mbar_try_wait(&v_empty[vs], ((v_armed / kVStages) & 1) ^ 1)) {
+          while (!active(jv)) ++jv;
+          const int page = page_of(jv);
+          if (lane == 0) mbar_arrive_expect_tx(&v_full[vs], kTileBytes);
+          __syncwarp();
+          if (lane < 8) {
+            const uint32_t vdst = v_smem0 + vs * kTileBytes + lane * 2048;
+            tma_load_5d(vdst, &tmap_kv, 0, 0, 0, hk, page * 2 + 1, &v_full[vs]);
+            tma_load_5d(vdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2 + 1, &v_full[vs]);
+          }
+          ++jv;
+          ++v_armed;
+          progressed = true;
+        }
       }
-      ++it;
+      if (progressed) {
+        idle_since = 0;
+      } else {
+        if (*abort_flag) break;
+        const uint64_t now = global_timer_ns();
+        if (idle_since == 0) idle_since = now;
+        if (now - idle_since > 2000000000ull) {
+          if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 100);
+          if (lane == 0) atomicExch(&sh_abort, 1);
+          break;
+        }
+      }
     }
     // drain: the CTA must not retire while a bulk copy may still be landing
     __syncwarp();
     if (lane == 0) {
       mbar_wait(&q_full, 0, 200000000ull);
-      const int first = it > kStages ? it - kStages : 0;
-      for (int x = first; x < it; ++x) mbar_wait(&kv_full[x % kStages], (x / kStages) & 1, 200000000ull);
+      for (int x = k_armed > kKStages ? k_armed - kKStages : 0; x < k_armed; ++x)
+        mbar_wait(&k_full[x % kKStages], (x / kKStages) & 1, 200000000ull);
+      for (int x = v_armed > kVStages ? v_armed - kVStages : 0; x < v_armed; ++x)
+        mbar_wait(&v_full[x % kVStages], (x / kVStages) & 1, 200000000ull);
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ================================================================== MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::instr_desc(kBf16, false, false, kBM, kBN);
       constexpr uint32_t idesc_pv = tc::instr_desc(kBf16, false, true, kBM, kDim);
       // O += P V for the it-th processed tile
       auto issue_pv = [&](int jj) -> bool {
-        const int s = jj % kStages;
+        const int vs = jj % kVStages;
+        if (!wait_or_abort(&v_full[vs], (jj / kVStages) & 1, abort_flag)) return false;
         if (!wait_or_abort(&p_full, jj & 1, abort_flag)) return false;
         tc::fence_after_sync();
-        const uint32_t v_smem = kv_smem + s * 2 * kTileBytes + kTileBytes;
+        const uint32_t v_smem = v_smem0 + vs * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           tc::mma_ss(tmem + kColO, tc::desc_k_major(p_smem + (ks >> 2) * kHalfBytes + (ks & 3) * 32),
                      tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
         }
         tc::commit(&pv_done);
-        tc::commit(&kv_empty[s]);
+        tc::commit(&v_empty[vs]);
         return true;
       };
       bool ok = wait_or_abort(&q_full, 0, abort_flag);
       int it = 0;  // S tiles issued so far
       for (int j = 0; ok && j < n_tiles; ++j) {
         if (!active(j)) continue;
-        const int s = it % kStages, sb = it & 1;
-        ok = wait_or_abort(&kv_full[s], (it / kStages) & 1, abort_flag) &&
+        const int kst = it % kKStages, sb = it & 1;
+        ok = wait_or_abort(&k_full[kst], (it / kKStages) & 1, abort_flag) &&
              wait_or_abort(&s_empty[sb], ((it >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc::fence_after_sync();
-        const uint32_t k_smem = kv_smem + s * 2 * kTileBytes;
+        const uint32_t k_smem = k_smem0 + kst * kTileBytes;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
           tc::mma_ss(tmem + kColS + sb * kBN, tc::desc_k_major(q_smem + off), tc::desc_k_major(k_smem + off), idesc_qk,
                      ks > 0 ? 1u : 0u);
         }
+        tc::commit(&k_empty[kst]);
         tc::commit(&s_full[sb]);
         if (it >= 1) ok = issue_pv(it - 1);
         ++it;
@@ -451,9 +500,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ================================================================== softmax (thread = row)
-    const int row = warp * 32 + lane;  // row of the tile = TMEM lane
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // ============================================== softmax (two threads per row, 64 columns each)
+    const int q4 = warp & 3;    // TMEM lane quarter this warp may access
+    const int hh = warp >> 2;   // column half of the S tile (and token half of the P tile) it owns
+    const int row = q4 * 32 + lane;  // row of the tile = TMEM lane
+    const uint32_t lane_base = (uint32_t)(q4 * 32) << 16;
     const bool row_valid = row < rows;
     // last allowed token of this row (inclusive)
     const int limit = row_valid ? ((a.causal && !has_mask) ? min(kv_len - 1, kv_len - qo_len + r0 + row) : kv_len - 1) : -1;
@@ -461,47 +512,68 @@ __global__ void __launch_bounds__(kThreads, 1)
     const float c = a.sm_scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    uint32_t sreg[128];
+    uint32_t sreg[64];
     int it = 0;
+    // the two warps that share a lane quarter meet at their own mbarrier (bounded, abort-aware)
+    uint32_t pair_phase = 0;
+    auto pair_sync = [&]() -> bool {
+      mbar_arrive(&pair_bar[q4]);
+      const bool r = wait_or_abort(&pair_bar[q4], pair_phase & 1, abort_flag);
+      ++pair_phase;
+      return r;
+    };
 
     for (int j = 0; j < n_tiles; ++j) {
       if (!active(j)) continue;
       const int sb = it & 1;
-      uint4 mw = make_uint4(0, 0, 0, 0);
-      if (has_mask && row_valid) mw = __ldg(mrow + j);  // in flight while we wait for S
+      uint4 mw4 = make_uint4(0, 0, 0, 0);
+      if (has_mask && row_valid) mw4 = __ldg(mrow + j);  // in flight while we wait for S
       ok = wait_or_abort(&s_full[sb], (it >> 1) & 1, abort_flag);
       if (!ok) break;
       tc::fence_after_sync();
-      const uint32_t s_addr = tmem + lane_base + kColS + sb * kBN;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) tc::tmem_ld32(s_addr + ch * 32, sreg + ch * 32);
+      // own half of the row stays in registers; the other half is read only for the row maximum,
+      // so the two threads of a row agree on it without exchanging anything
+      const uint32_t s_row = tmem + lane_base + kColS + sb * kBN;
+      uint32_t oth[64];
+      tc::tmem_ld32(s_row + hh * 64, sreg);
+      tc::tmem_ld32(s_row + hh * 64 + 32, sreg + 32);
+      tc::tmem_ld32(s_row + (hh ^ 1) * 64, oth);
+      tc::tmem_ld32(s_row + (hh ^ 1) * 64 + 32, oth + 32);
       tc::tmem_wait_ld();
       tc::fence_before_sync();
       mbar_arrive(&s_empty[sb]);  // S is in registers: the MMA warp may overwrite this buffer
 
       // ---- running maximum (lazy) and probabilities
-      const int t0 = j * kBN;
-      const bool full_tile = has_mask ? (mw.x & mw.y & mw.z & mw.w) == 0xffffffffu : t0 + kBN - 1 <= limit;
-      float mx = -INFINITY;
-      if (full_tile) {
+      const int t0 = j * kBN + hh * 64;       // first token of the own half
+      const int t1 = j * kBN + (hh ^ 1) * 64;  // first token of the other half
+      const uint32_t mown[2] = {hh ? mw4.z : mw4.x, hh ? mw4.w : mw4.y};
+      const uint32_t moth[2] = {hh ? mw4.x : mw4.z, hh ? mw4.y : mw4.w};
+      const bool full_own = has_mask ? (mown[0] & mown[1]) == 0xffffffffu : t0 + 63 <= limit;
+      const bool full_oth = has_mask ? (moth[0] & moth[1]) == 0xffffffffu : t1 + 63 <= limit;
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (full_own) {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
-      } else if (has_mask) {
-        const uint32_t mwords[4] = {mw.x, mw.y, mw.z, mw.w};
-#pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const float v = ((mwords[i >> 5] >> (i & 31)) & 1u) ? __uint_as_float(sreg[i]) : -INFINITY;
-          sreg[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
-        }
+        for (int i = 0; i < 64; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], __uint_as_float(sreg[i]));
       } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const float v = (t0 + i <= limit) ? __uint_as_float(sreg[i]) : -INFINITY;
+        for (int i = 0; i < 64; ++i) {
+          const bool allow = has_mask ? ((mown[i >> 5] >> (i & 31)) & 1u) != 0 : t0 + i <= limit;
+          const float v = allow ? __uint_as_float(sreg[i]) : -INFINITY;
           sreg[i] = __float_as_uint(v);
-          mx = fmaxf(mx, v);
+          mxa[i & 3] = fmaxf(mxa[i & 3], v);
         }
       }
+      if (full_oth) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], __uint_as_float(oth[i]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const bool allow = has_mask ? ((moth[i >> 5] >> (i & 31)) & 1u) != 0 : t1 + i <= limit;
+          mxa[i & 3] = fmaxf(mxa[i & 3], allow ? __uint_as_float(oth[i]) : -INFINITY);
+        }
+      }
+      float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3]));
       mx *= c;  // c > 0
       float alpha = 1.f;
       bool rescale = false;
@@ -512,16 +584,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         rescale = it > 0;
       }
       const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
+      float suma[4] = {0.f, 0.f, 0.f, 0.f};
+      const float neg_m = -m_use;
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const float p0v = fast_exp2(fmaf(__uint_as_float(sreg[2 * i]), c, -m_use));
-        const float p1v = fast_exp2(fmaf(__uint_as_float(sreg[2 * i + 1]), c, -m_use));
-        sum += p0v + p1v;
-        sreg[i] = pack2<T>(p0v, p1v);  // tokens 2i, 2i+1
+      for (int i = 0; i < 32; ++i) {
+        const float p0v = fast_exp2(fmaf(__uint_as_float(sreg[2 * i]), c, neg_m));
+        const float p1v = fast_exp2(fmaf(__uint_as_float(sreg[2 * i + 1]), c, neg_m));
+        suma[i & 3] += p0v + p1v;
+        sreg[i] = pack2<T>(p0v, p1v);  // tokens 2i, 2i+1 of this half
       }
-      l += sum;
-
+      l += (suma[0] + suma[1]) + (suma[2] + suma[3]);
       // ---- P buffer free and O stable once PV of the previous tile has completed
       if (it > 0) {
         ok = wait_or_abort(&pv_done, (it - 1) & 1, abort_flag);
@@ -529,9 +601,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc::fence_after_sync();
       }
       if (__any_sync(0xffffffffu, rescale)) {
-        const uint32_t o_addr = tmem + lane_base + kColO;
+        const uint32_t o_addr = tmem + lane_base + kColO + hh * 64;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
           uint32_t oreg[32];
           tc::tmem_ld32(o_addr + ch * 32, oreg);
           tc::tmem_wait_ld();
@@ -541,14 +613,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         tc::tmem_wait_st();
       }
-      // ---- P -> shared memory, K-major with 128-byte swizzle: row r, 16-byte chunk ch of token half hf
+      // ---- P -> shared memory, K-major with 128-byte swizzle: row r, token half hh, 16-byte chunk cc
       {
-        uint8_t *prow = p_ptr + (row >> 3) * 1024 + (row & 7) * 128;
+        uint8_t *prow = p_ptr + hh * kHalfBytes + (row >> 3) * 1024 + (row & 7) * 128;
 #pragma unroll
-        for (int ch = 0; ch < 16; ++ch) {
-          const int hf = ch >> 3, cc = ch & 7;
-          *reinterpret_cast<uint4 *>(prow + hf * kHalfBytes + ((cc ^ (row & 7)) << 4)) =
-              make_uint4(sreg[ch * 4], sreg[ch * 4 + 1], sreg[ch * 4 + 2], sreg[ch * 4 + 3]);
+        for (int cc = 0; cc < 8; ++cc) {
+          *reinterpret_cast<uint4 *>(prow + ((cc ^ (row & 7)) << 4)) =
+              make_uint4(sreg[cc * 4], sreg[cc * 4 + 1], sreg[cc * 4 + 2], sreg[cc * 4 + 3]);
         }
       }
       fence_proxy_async_smem();
@@ -557,15 +628,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       ++it;
     }
 
-    // ---- epilogue: O / l -> out
+    // ---- epilogue: O / l -> out (each thread stores its 64 of the row's 128 values)
     if (ok) ok = wait_or_abort(&pv_done, (n_active - 1) & 1, abort_flag);
+    xch_sum[hh][row] = l;
+    if (ok) ok = pair_sync();
     if (ok) {
       tc::fence_after_sync();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      T *orow = out + ((size_t)(q0 + r0 + row) * a.hq + h) * kDim;
-      const uint32_t o_addr = tmem + lane_base + kColO;
+      const float lsum = l + xch_sum[hh ^ 1][row];
+      const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+      T *orow = out + ((size_t)(q0 + r0 + row) * a.hq + h) * kDim + hh * 64;
+      const uint32_t o_addr = tmem + lane_base + kColO + hh * 64;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t oreg[32];
         tc::tmem_ld32(o_addr + ch * 32, oreg);
         tc::tmem_wait_ld();
@@ -581,8 +655,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      if (a.lse != nullptr && row_valid)
-        a.lse[(size_t)(q0 + r0 + row) * a.hq + h] = l > 0.f ? (m_ref + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      if (a.lse != nullptr && row_valid && hh == 0)
+        a.lse[(size_t)(q0 + r0 + row) * a.hq + h] = lsum > 0.f ? (m_ref + log2f(lsum)) * 0.6931471805599453f : -INFINITY;
     } else {
       if (lane == 0 && !*abort_flag) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 300 + warp);
       if (lane == 0) atomicExch(&sh_abort, 1);
@@ -592,7 +666,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- teardown: every thread arrives here on every path
   tc::fence_before_sync();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc::fence_after_sync();
     tc::tmem_dealloc(tmem, kTmemCols);
   }
