@@ -151,6 +151,25 @@ int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, cons
                      int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
                      int32_t *err, void *stream);
 
+/* Same computation as piekv_decode_run for callers that cannot supply scratch memory and must not
+ * trigger an allocation: a runtime that has already given every free byte to the KV pool, a
+ * binding that can only forward its own tensors, or code running where cudaMalloc is forbidden.
+ * It has no counterpart in the reference.  The split-KV scratch is a fixed
+ * piekv_decode_noalloc_max_bytes() (8 MiB) array inside the library, held by every GPU that loads
+ * the library until the process exits.  Calls whose batch / head count need more are rejected with
+ * a >0 status and a message; nothing is launched.  The call never allocates (no cudaMalloc /
+ * cudaFree, no allocating library routine); it issues one small cudaMemsetAsync of the arrival
+ * counters and the kernel.  The first call on each device looks the array's device address up
+ * (cudaGetSymbolAddress) and should therefore happen before any stream capture.  All calls on a
+ * device share the one array: calls that may overlap on the GPU (different streams) race. */
+int64_t piekv_decode_noalloc_max_bytes(void);
+int piekv_decode_run_noalloc(const void *q, int64_t q_stride_n, int64_t q_stride_h,
+                             const void *pool, void *out, float *lse, const int32_t *kv_indptr,
+                             const int32_t *kv_indices, const int32_t *kv_last_page_len,
+                             int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
+                             int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype,
+                             float sm_scale, int32_t *err, void *stream);
+
 /* One decode step in a single launch: rotate q and the new token's k (RoPE at pos_ids[b]), write
  * k,v into slot kv_last_page_len[b]-1 of request b's last page, and attend over all of the
  * request's pages including the new token.  The page table must already include the new token

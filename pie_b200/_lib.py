@@ -68,6 +68,11 @@ SIGNATURES = {
         C.c_int,
         [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p],
     ),
+    "piekv_decode_noalloc_max_bytes": (_i64, []),
+    "piekv_decode_run_noalloc": (
+        C.c_int,
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _p],
+    ),
     "piekv_decode_step_fused": (
         C.c_int,
         [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,

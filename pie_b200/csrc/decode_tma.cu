@@ -671,3 +671,87 @@ int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const v
 }
 
 }  // namespace piekv
+
+// =====================================================================================
+// Decode attention without any allocation by the caller or by the library
+// =====================================================================================
+// Some hosts of this library cannot hand over a workspace: an inference runtime whose memory
+// pool is fully committed to the KV cache at start-up (the reference sizes its pool from all free
+// memory, pie/src/pie_worker/model/llama3.py:177-202), a plugin called from a stream callback or
+// from inside a captured region where cudaMalloc is not allowed, or a foreign-language binding that
+// only passes its own tensors through.  For those, the split-KV scratch of the tuned decode kernel
+// lives in a fixed array inside the library image.  Every GPU that loads the library keeps these
+// bytes until the process exits.
+namespace piekv {
+namespace {
+constexpr int64_t kStaticScratchBytes = 8ll << 20;  // 8 MiB: counters + partial (max, sum, acc) triples
+static __device__ __align__(256) unsigned char g_decode_scratch[kStaticScratchBytes];
+
+// The array's name is only a host-side handle; the device address is looked up once per device
+// (with that device current) and cached.
+int static_scratch_ptr(void **out) {
+  static void *cached[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaGetDevice");
+  PIEKV_REQUIRE(dev >= 0 && dev < 64, "decode_run_noalloc: device index %d out of range", dev);
+  if (cached[dev] == nullptr) {
+    void *ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_decode_scratch);
+    if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaGetSymbolAddress");
+    PIEKV_REQUIRE(ptr != nullptr, "decode_run_noalloc: scratch symbol has no device address");
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return 0;
+}
+}  // namespace
+}  // namespace piekv
+
+extern "C" int64_t piekv_decode_noalloc_max_bytes(void) { return piekv::kStaticScratchBytes; }
+
+extern "C" int piekv_decode_run_noalloc(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                                        void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                        const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                        int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                                        int32_t dtype, float sm_scale, int32_t *err, void *stream) {
+  using namespace piekv;
+  PIEKV_REQUIRE(dtype >= PIEKV_F32 && dtype <= PIEKV_BF16, "decode_run_noalloc: unknown dtype %d", dtype);
+  PIEKV_REQUIRE(batch >= 0 && num_qo_heads > 0 && num_kv_heads > 0 && num_qo_heads % num_kv_heads == 0 &&
+                    head_dim > 0 && page_size > 0 && num_pages > 0,
+                "decode_run_noalloc: bad sizes");
+  if (batch == 0) return 0;
+  PIEKV_REQUIRE(q && pool && out && kv_indptr && kv_indices && kv_last_page_len, "decode_run_noalloc: null pointer");
+  AttnArgs a{};
+  a.q = q;
+  a.q_sn = q_stride_n;
+  a.q_sh = q_stride_h;
+  a.pool = pool;
+  a.out = out;
+  a.lse = lse;
+  a.kv_indptr = kv_indptr;
+  a.kv_indices = kv_indices;
+  a.kv_last_page_len = kv_last_page_len;
+  a.batch = batch;
+  a.nnz = batch;
+  a.hq = num_qo_heads;
+  a.hkv = num_kv_heads;
+  a.dim = head_dim;
+  a.page_size = page_size;
+  a.num_pages = num_pages;
+  a.sm_scale = sm_scale;
+  a.err = err;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!decode_tma_supported(a, dtype)) return launch_attn_generic(a, dtype, st);  // that kernel needs no scratch
+  const int64_t need = decode_tma_workspace_bytes(batch, num_qo_heads, num_kv_heads);
+  PIEKV_REQUIRE(need <= kStaticScratchBytes,
+                "decode_run_noalloc: batch %d with %d query heads needs %lld bytes of scratch, the built-in "
+                "scratch holds %lld; use piekv_decode_run with a caller workspace",
+                batch, num_qo_heads, (long long)need, (long long)kStaticScratchBytes);
+  void *scratch = nullptr;
+  if (int rc = static_scratch_ptr(&scratch)) return rc;
+  // the arrival counters must be zero when the kernel starts, whatever an earlier call left behind
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)batch * sizeof(int), st);
+  if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaMemsetAsync");
+  return launch_decode_tma(a, dtype, scratch, kStaticScratchBytes, st);
+}

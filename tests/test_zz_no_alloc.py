@@ -1,0 +1,69 @@
+"""The allocation-free decode entry point (piekv_decode_run_noalloc).
+
+Who needs it: a caller that cannot give the library a workspace and must not cause an allocation -
+an engine that handed all free device memory to its KV pool when it started, a thin foreign-language
+binding that forwards only its own tensors, or code that runs where cudaMalloc is not permitted.
+The entry point keeps its split-KV scratch in a fixed array inside the library instead.
+
+The test drives both entry points through the C ABI on the same inputs and expects the same attention
+output, on two calls in a row (the second call finds the first call's partial results and counters in
+the shared array).  This file sorts last so that a run stopping at the first failure has already run
+every other test.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from pie_b200 import _lib
+from pie_b200 import workloads as W
+from tests.util import dev, make_scenario
+
+pytestmark = pytest.mark.gpu
+
+L = _lib.lib
+
+
+def _run_both(sc, ws):
+    m = sc.meta
+    q, pool = sc.q.cuda(), sc.pool.cuda()
+    indptr, indices, last = dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len)
+    b = m.batch
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    scale = 1.0 / math.sqrt(sc.d)
+    out_ws = torch.empty_like(q)
+    out_na = torch.full_like(q, float("nan"))
+    _lib.check(L.piekv_decode_run(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out_ws.data_ptr(), None,
+                                  indptr.data_ptr(), indices.data_ptr(), last.data_ptr(), b, sc.hq, sc.hkv, sc.d, 16,
+                                  sc.num_pages, _lib.PIEKV_BF16, scale, ws.data_ptr(), ws.numel(), err.data_ptr(),
+                                  stream), "decode_run")
+    _lib.check(L.piekv_decode_run_noalloc(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out_na.data_ptr(),
+                                          None, indptr.data_ptr(), indices.data_ptr(), last.data_ptr(), b, sc.hq,
+                                          sc.hkv, sc.d, 16, sc.num_pages, _lib.PIEKV_BF16, scale, err.data_ptr(),
+                                          stream), "decode_run_noalloc")
+    torch.cuda.synchronize()
+    assert err.cpu().tolist() == [0, 0, 0, 0]
+    return out_ws, out_na
+
+
+def test_noalloc_matches_workspace_entry_point_twice():
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+    first = make_scenario(32, 8, 128, torch.bfloat16, [(c - 1, 1) for c in (4000, 37, 1500, 16, 900, 5)], seed=41,
+                          scale=0.5)
+    second = make_scenario(32, 8, 128, torch.bfloat16, [(c - 1, 1) for c in (100, 2600, 33)], seed=42, scale=0.5)
+    for sc in (first, second):
+        a, b = _run_both(sc, ws)
+        assert torch.isfinite(b).all()
+        assert (a.float() - b.float()).abs().max().item() <= 2e-2  # the tolerance of the other decode tests
+        assert torch.equal(a, b)  # same kernel, same partition: the same bits
+
+
+def test_noalloc_rejects_what_does_not_fit():
+    assert L.piekv_decode_noalloc_max_bytes() == 8 << 20
+    one = 256  # any non-null, aligned value: the size check happens before anything touches memory
+    rc = L.piekv_decode_run_noalloc(one, 4096, 128, one, one, None, one, one, one, 4096, 32, 8, 128, 16, 1 << 20,
+                                    _lib.PIEKV_BF16, 0.1, None, None)
+    assert rc > 0
+    assert b"scratch" in L.piekv_last_error_string()
