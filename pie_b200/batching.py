@@ -1,0 +1,109 @@
+"""Host feeder of the path: wire fields of a batched forward-pass request -> index arrays and the
+flat boolean attention mask.
+
+Mirror of the part of `Batch.__init__` / `get_model_inputs` that feeds the paged-KV operators
+(pie/src/pie_worker/batching.py:28-135,196-239; wire layout runtime/src/model/request.rs:250-298):
+the fields arrive as little-endian uint32 byte strings (lists are accepted too), are decoded to int32
+arrays, and the per-token BRLE masks are expanded to one row of kv_len booleans per query token.
+BRLE = alternating run lengths starting with an ATTEND run (sdk/rust/inferlet/src/brle.rs:4-21);
+only the first `position + 1` bits of a row can be set, where position = context_len + index of the token
+in its request (pie/src/pie_worker/batching.py:113-122,367-387).
+
+The expansion is vectorised numpy (the reference uses a Numba loop); the result is the tensor that
+`BatchPrefillWithPagedKVCacheWrapper.plan(custom_mask=...)` takes, which the library then bit-packs
+on the device.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict
+
+import numpy as np
+import torch
+
+
+def _u32(data) -> np.ndarray:
+    if isinstance(data, (bytes, bytearray, memoryview)):
+        return np.frombuffer(data, dtype=np.uint32)
+    return np.asarray(data, dtype=np.uint32)
+
+
+def decode_brle_batch(flattened_masks: np.ndarray, mask_indptr: np.ndarray, position_ids: np.ndarray,
+                      token_acc_seq_lens: np.ndarray) -> np.ndarray:
+    """Flat boolean mask from per-token BRLE runs (semantics of pie/src/pie_worker/batching.py:337-389).
+
+    Vectorised: every run becomes a [start, end) interval inside its token's row, clipped to the row's
+    valid length; attend-runs (even index within the token) add +1 / -1 to a difference array whose
+    prefix sum is the mask."""
+    runs = np.asarray(flattened_masks, dtype=np.int64)
+    ptr = np.asarray(mask_indptr, dtype=np.int64)
+    valid = np.asarray(position_ids, dtype=np.int64) + 1
+    acc = np.asarray(token_acc_seq_lens, dtype=np.int64)
+    total = int(acc[-1])
+    if total == 0 or len(runs) == 0:
+        return np.zeros(total, dtype=np.bool_)
+    ntok = len(valid)
+    counts = np.diff(ptr)
+    tok = np.repeat(np.arange(ntok), counts)
+    # exclusive prefix of the run lengths inside each token
+    csum = np.cumsum(runs)
+    base = np.concatenate([[0], csum])[ptr[:-1]]
+    start = csum - runs - np.repeat(base, counts)
+    end = start + runs
+    v = valid[tok]
+    start = np.minimum(start, v)
+    end = np.minimum(end, v)
+    idx_in_tok = np.arange(len(runs)) - np.repeat(ptr[:-1], counts)
+    attend = (idx_in_tok % 2 == 0) & (end > start)
+    row0 = acc[:-1][tok]
+    diff = np.zeros(total + 1, dtype=np.int32)
+    np.add.at(diff, (row0 + start)[attend], 1)
+    np.add.at(diff, (row0 + end)[attend], -1)
+    return np.cumsum(diff[:-1]) > 0
+
+
+class Batch:
+    """The index arrays and mask of one batched forward pass."""
+
+    def __init__(self, args: Dict[str, Any], kv_page_size: int) -> None:
+        self.token_ids = _u32(args["token_ids"]).astype(np.int64)
+        self.position_ids = _u32(args["position_ids"]).astype(np.int32)
+        self.kv_page_indices = _u32(args["kv_page_indices"]).astype(np.int32)
+        self.kv_page_indptr = _u32(args["kv_page_indptr"]).astype(np.int32)
+        self.kv_last_page_lens = _u32(args["kv_last_page_lens"]).astype(np.int32)
+        self.qo_indptr = _u32(args["qo_indptr"]).astype(np.int32)
+        self.single_token_mode = bool(args.get("single_token_mode", False))
+        self.total_tokens = int(len(self.token_ids))
+
+        runs = _u32(args["flattened_masks"]).astype(np.int64)
+        mask_indptr = _u32(args["mask_indptr"]).astype(np.int64)
+        counts = np.diff(self.qo_indptr).astype(np.int64)
+        npages = np.diff(self.kv_page_indptr).astype(np.int64)
+        last = self.kv_last_page_lens.astype(np.int64)
+        # a request without pages keeps last_len as its length (pie/src/pie_worker/batching.py:104-111)
+        self.seq_lens = np.where(npages > 0, (npages - 1) * kv_page_size + last, last)
+        all_seq = np.repeat(self.seq_lens, counts)
+        ctx = self.seq_lens - counts
+        pos = np.arange(self.total_tokens, dtype=np.int64) - np.repeat(self.qo_indptr[:-1].astype(np.int64), counts) \
+            + np.repeat(ctx, counts)
+        acc = np.zeros(self.total_tokens + 1, dtype=np.int64)
+        np.cumsum(all_seq, out=acc[1:])
+        self.attention_masks = decode_brle_batch(runs, mask_indptr, pos, acc)
+
+    def get_model_inputs(self, device) -> Dict[str, Any]:
+        """Device tensors in the form the operators take (pie/src/pie_worker/batching.py:196-239)."""
+        dev = torch.device(device)
+
+        def t(a, dt):
+            return torch.as_tensor(a, device=dev, dtype=dt)
+
+        return {
+            "token_ids": t(self.token_ids, torch.long),
+            "position_ids": t(self.position_ids, torch.int32),
+            "qo_indptr": t(self.qo_indptr, torch.int32),
+            "kv_page_indices": t(self.kv_page_indices, torch.int32),
+            "kv_page_indptr": t(self.kv_page_indptr, torch.int32),
+            "kv_last_page_lens": t(self.kv_last_page_lens, torch.int32),
+            "custom_mask": t(self.attention_masks, torch.bool),
+            "single_token_inference_mode": self.single_token_mode,
+            "total_pages_cpu": self.kv_page_indptr[-1] if len(self.kv_page_indptr) else 0,
+        }

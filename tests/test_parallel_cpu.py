@@ -1,0 +1,72 @@
+"""The N > 1 paths on CPU: two gloo ranks run the oracle on their shard and must reproduce the
+single-process result (KV-head sharding + all-gather), and request sharding must partition the batch."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from pie_b200 import parallel
+from tests.util import make_scenario
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    return port
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import paged_kv_ref as R
+
+        sc = make_scenario(8, 4, 32, torch.float32, [(c - 1, 1) for c in (37, 5, 64, 100, 17)], seed=3)
+        m = sc.meta
+        full = R.decode_attention(sc.q, sc.pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len)
+        # KV-head sharding: this rank's slice of the pool and of q, identical page tables
+        qs, ks = parallel.shard_heads(sc.hq, sc.hkv, world, rank)
+        local = R.decode_attention(sc.q[:, qs].contiguous(), sc.pool[:, :, :, ks].contiguous(), m.kv_indptr,
+                                   m.kv_indices, m.kv_last_page_len)
+        gathered = parallel.allgather_heads(local)
+        ok_tp = torch.equal(gathered, full)
+        # request sharding: each rank attends over its own requests only; together they cover the batch
+        mine = parallel.shard_requests(m.batch, world, rank)
+        ptr = np.concatenate([[0], np.cumsum(np.diff(m.kv_indptr)[mine])]).astype(np.int32)
+        idx = np.concatenate([m.kv_indices[m.kv_indptr[b]: m.kv_indptr[b + 1]] for b in mine]).astype(np.int32)
+        part = R.decode_attention(sc.q[mine], sc.pool, ptr, idx, m.kv_last_page_len[mine])
+        ok_dp = torch.equal(part, full[mine])
+        counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(counts, torch.tensor([len(mine)]))
+        ok_cover = int(sum(c.item() for c in counts)) == m.batch
+        ret[rank] = (ok_tp, ok_dp, ok_cover)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_head_and_request_sharding_two_gloo_ranks():
+    world = 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for r in range(world):
+        assert ret[r] == (True, True, True), (r, ret[r])
+
+
+def test_shard_arithmetic():
+    assert parallel.shard_requests(7, 4, 1) == [1, 5]
+    q, k = parallel.shard_heads(64, 8, 4, 2)
+    assert (q.start, q.stop, k.start, k.stop) == (32, 48, 4, 6)
+    try:
+        parallel.shard_heads(32, 8, 3, 0)
+    except ValueError:
+        pass
+    else:
+        raise AssertionError("expected ValueError")
