@@ -447,6 +447,266 @@ def run_prefill(args):
 
 
 # ---------------------------------------------------------------------------------------------
+# secondary workload: 70B-shaped decode with eviction churn, KV heads sharded over the ranks
+# ---------------------------------------------------------------------------------------------
+def run_decode70b(args):
+    """64 q / 8 kv heads, D128, bf16, 256 requests with lognormal contexts (median 2048, clipped to
+    [128, 32768]); every 32 steps 20 % of the requests are evicted, their pages recycled and the slots
+    refilled with 1024-token contexts written through the RoPE + append kernel.  With G ranks every rank
+    holds 8/G KV heads (and 64/G query heads) of every request with identical page tables and the
+    attention outputs are all-gathered (NCCL) each step."""
+    import torch.distributed as dist
+
+    from pie_b200 import ops, parallel
+    from pie_b200 import workloads as W
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG5
+    B, D = args.requests if args.requests != 64 else 256, cfg.head_dim
+    hq, hkv = cfg.num_qo_heads // world, cfg.num_kv_heads // world
+    num_pages = args.pages if args.pages != 32768 else cfg.num_pages
+    steps, warmup = args.steps, args.warmup
+    reqs = W.config5_requests(B, 5, num_pages)
+
+    def t(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+    # the schedule is identical on every rank (seeded): per step the page table, per churn the refill lists
+    plan = []
+    for s in range(steps + warmup):
+        refill = None
+        if s > 0 and s % 32 == 0:
+            victims = W.eviction_victims(B, s)
+            for r in victims:
+                reqs.evict(r, 1024)
+            idx, ptr, last = reqs.csr()
+            qo = np.zeros(B + 1, np.int64)
+            for r in victims:
+                qo[r + 1] = 1024
+            qo = np.cumsum(qo).astype(np.int32)
+            pos = np.tile(np.arange(1024, dtype=np.int32), len(victims))
+            refill = dict(indices=t(idx), indptr=t(ptr), last=t(last), qo=t(qo), pos=t(pos), n=int(qo[-1]))
+        m = W.decode_steps(reqs, 1)[0]
+        plan.append(dict(meta=m, indices=t(m.kv_indices), indptr=t(m.kv_indptr), last=t(m.kv_last_page_len),
+                         pos=t(m.pos_ids), refill=refill))
+    pool = W.randn((num_pages, 2, 16, hkv, D), 100 + rank, cfg.dtype, 0.5, device=dev)
+    qkv = W.randn((4, B, (hq + 2 * hkv) * D), 200 + rank, cfg.dtype, 0.5, device=dev)
+    kv_refill = W.randn((2, (int(round(B * 0.2)) + 1) * 1024, hkv, D), 300 + rank, cfg.dtype, 0.5, device=dev)
+    out = torch.empty((B, hq, D), dtype=cfg.dtype, device=dev)
+    gather = torch.empty((world, B, hq, D), dtype=cfg.dtype, device=dev)
+    ws = torch.zeros(128 << 20, dtype=torch.uint8, device=dev)
+    rope = ops.RopeConfig()
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+    launches = [0]
+
+    def step(i):
+        pl = plan[i]
+        rf = pl["refill"]
+        if rf is not None:
+            seq = ops.get_seq_lens(rf["indptr"], rf["last"], 16)
+            bi, kp = ops.get_batch_indices_positions(rf["qo"], seq, rf["n"])
+            ops.rope_append_paged_kv_cache(None, kv_refill[0, : rf["n"]], kv_refill[1, : rf["n"]], rf["pos"], bi, kp,
+                                           pool, rf["indices"], rf["indptr"], rf["last"], rope)
+            launches[0] += 3
+        x = qkv[i % 4]
+        q = x[:, : hq * D].view(B, hq, D)
+        k = x[:, hq * D: (hq + hkv) * D].view(B, hkv, D)
+        v = x[:, (hq + hkv) * D:].view(B, hkv, D)
+        w.plan(pl["indptr"], pl["indices"], pl["last"], hq, hkv, D, 16, q_data_type=cfg.dtype)
+        o = w.run_fused(q, k, v, pl["pos"], pool, rope, out=out)
+        launches[0] += 1
+        return parallel.allgather_heads(o, gather_buffer=gather) if world > 1 else o
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for i in range(warmup):
+        step(i)
+    barrier()
+    launches[0] = 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local)
+    with sampler:
+        barrier()
+        e0.record()
+        for i in range(steps):
+            step(warmup + i)
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        tt = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    # attention kernel alone on a mid-run table (per-GPU bytes)
+    mid = plan[warmup + steps // 2]
+    x = qkv[0]
+    q = x[:, : hq * D].view(B, hq, D)
+    w.plan(mid["indptr"], mid["indices"], mid["last"], hq, hkv, D, 16, q_data_type=cfg.dtype)
+    for _ in range(3):
+        w.run(q, pool, out=out)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(20):
+        w.run(q, pool, out=out)
+    k1.record()
+    torch.cuda.synchronize(dev)
+    kern_ms = k0.elapsed_time(k1) / 20
+    tokens = int(mid["meta"].seq_lens.astype(np.int64).sum())
+    kern_bytes = tokens * 2 * hkv * D * 2 + B * 2 * hq * D * 2 + 4 * (len(mid["meta"].kv_indices) + 2 * B + 1)
+    peak, peak_kind = load_peaks()
+    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": B * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, "
+                                   f"{B} requests, lognormal ctx, 20% evicted+refilled every 32 steps",
+                       "parallelism": f"KV heads sharded x{world} ({hkv} kv / {hq} q heads per GPU), NCCL all-gather "
+                                      "of attention outputs", "pool_pages": num_pages,
+                       "l2": "inputs larger than L2; no flush", "launch": "eager, one fused kernel per step"},
+            "clocks": sampler.summary(), "gpu_launches": launches[0],
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only, per GPU)", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                         "traffic": None, "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
+                         "cached_tokens": tokens},
+            "device_error_word": ops.device_error(dev)}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# secondary workload: beam search with shared prefix pages and copy-on-write of the partial page
+# ---------------------------------------------------------------------------------------------
+def run_beam(args):
+    """16 prefixes of 1024 tokens, each forked into 4 beams that share the prefix pages; 64 decode steps;
+    every 8 steps the 2 best beams of a group (seeded random score) survive and fork again: full pages are
+    shared by reference count, a partially filled last page is copied (copy_pages_kernel), losers' private
+    pages return to the free list.  The page bookkeeping runs on the host each step (pie_b200.pages) and
+    its tables are copied to the device inside the timed region."""
+    from pie_b200 import ops, pages
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG2
+    HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    groups, beams, prefix = 16, 4, 1024
+    num_pages = 8192
+    B = groups * beams
+    pool = W.randn((num_pages, 2, 16, HKV, D), 400, cfg.dtype, 0.5, device=dev)
+    qkv = W.randn((4, B, (HQ + 2 * HKV) * D), 401, cfg.dtype, 0.5, device=dev)
+    out = torch.empty((B, HQ, D), dtype=cfg.dtype, device=dev)
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
+    rope = ops.RopeConfig()
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+    rng = np.random.default_rng(4)
+    host = torch.empty(4 * B + 2 + num_pages, dtype=torch.int32).pin_memory()
+    devbuf = torch.empty_like(host, device=dev)
+    cp_host = torch.empty(3 * B, dtype=torch.int32).pin_memory()
+    cp_dev = torch.empty_like(cp_host, device=dev)
+    stats = dict(copies=0, copy_bytes=0, freed=0, unique_tokens=0, logical_tokens=0)
+
+    def fresh():
+        pp = pages.PagePool(num_pages)
+        ctxs = []
+        for _ in range(groups):
+            root = pages.KvPageList(pp, 16)
+            root.grow(prefix)
+            grp = [root]
+            for _ in range(beams - 1):
+                child, cp = root.fork_cow()  # 1024 tokens = 64 full pages: shared, nothing to copy
+                grp.append(child)
+            ctxs.append(grp)
+        return pp, ctxs
+
+    def one_step(ctxs, i, count):
+        flat = [c for grp in ctxs for c in grp]
+        pos = np.fromiter((c.total_tokens for c in flat), dtype=np.int32, count=B)
+        for c in flat:
+            c.grow(1)
+        idx, ptr, last = pages.build_csr(flat)
+        n = len(idx)
+        hv = host.numpy()
+        hv[: B + 1] = ptr
+        hv[B + 1: 2 * B + 1] = last
+        hv[2 * B + 1: 3 * B + 1] = pos
+        hv[4 * B + 2: 4 * B + 2 + n] = idx
+        devbuf[: 4 * B + 2 + n].copy_(host[: 4 * B + 2 + n], non_blocking=True)
+        mv = views(devbuf, B)
+        x = qkv[i % 4]
+        q = x[:, : HQ * D].view(B, HQ, D)
+        k = x[:, HQ * D: (HQ + HKV) * D].view(B, HKV, D)
+        v = x[:, (HQ + HKV) * D:].view(B, HKV, D)
+        w.plan(mv["indptr"], mv["indices"][:n], mv["last"], HQ, HKV, D, 16, q_data_type=cfg.dtype)
+        w.run_fused(q, k, v, mv["pos"], pool, rope, out=out)
+        if count:
+            stats["logical_tokens"] += int(pos.sum()) + B
+            stats["unique_tokens"] += 16 * len(set(idx.tolist()))
+        if i % 8 == 7:
+            cps = []
+            for gi, grp in enumerate(ctxs):
+                order = rng.permutation(beams)
+                keep = [grp[j] for j in order[:2]]
+                for j in order[2:]:
+                    f = grp[j].release()
+                    if count:
+                        stats["freed"] += len(f)
+                new = []
+                for c in keep:
+                    child, cp = c.fork_cow()
+                    if cp is not None:
+                        cps.append(cp)
+                    new += [c, child]
+                ctxs[gi] = new
+            if cps:
+                m = len(cps)
+                arr = np.array(cps, dtype=np.int32).T.reshape(-1)  # src..., dst..., valid...
+                cp_host[: 3 * m].copy_(torch.from_numpy(arr))
+                cp_dev[: 3 * m].copy_(cp_host[: 3 * m], non_blocking=True)
+                ops.copy_kv_pages(pool, cp_dev[:m], cp_dev[m: 2 * m], cp_dev[2 * m: 3 * m])
+                if count:
+                    stats["copies"] += m
+                    stats["copy_bytes"] += int(sum(2 * c[2] * 2 * HKV * D * 2 for c in cps))
+
+    steps = 64
+    pp, ctxs = fresh()
+    for i in range(8):
+        one_step(ctxs, i, False)
+    torch.cuda.synchronize(dev)
+    pp, ctxs = fresh()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        one_step(ctxs, i, True)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    ms = e0.elapsed_time(e1)
+    print(json.dumps({
+        "metric": METRIC, "value": B * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": 8,
+        "ms_per_step": ms / steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "beam search page sharing: 16 prefixes x 1024 tokens x 4 beams, fork top-2 every 8 "
+                               "steps, copy-on-write of the partial last page; 32q/8kv heads, D128, bf16, page16",
+                   "host": "page bookkeeping + table upload every step inside the timed region"},
+        "wall_ms_per_step": wall_ms / steps,
+        "page_copies": stats["copies"], "page_copy_bytes": stats["copy_bytes"], "pages_recycled": stats["freed"],
+        "logical_kv_bytes_per_step": stats["logical_tokens"] * 4096 // steps,
+        "unique_page_kv_bytes_per_step": stats["unique_tokens"] * 4096 // steps,
+        "device_error_word": ops.device_error(dev)}), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------
 # CPU arms
 # ---------------------------------------------------------------------------------------------
 class CpuPath:
@@ -557,7 +817,7 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
     ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
     ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam"],
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
@@ -567,6 +827,10 @@ def main():
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "decode70b":
+        run_decode70b(args)
+    elif args.workload == "beam":
+        run_beam(args)
     else:
         run_ours(args)
 
