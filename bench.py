@@ -45,9 +45,10 @@ WORKLOAD = "llama3-8b-shaped decode layer: 32q/8kv heads, D128, bf16, page16, 32
            "64 requests/GPU, ctx U[512,4096], +1 token/request/step"
 HORIZON = 512  # distinct consecutive steps of metadata; longer runs wrap around
 
-# DRAM bytes per decode-kernel launch measured once with ncu (dram__bytes_read.sum + dram__bytes_write.sum),
-# scaled to this workload; see profiles/.  None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# DRAM traffic of the decode kernel = (dram__bytes_read.sum + dram__bytes_write.sum) / algorithmic bytes from
+# one ncu capture of a 32-request case (328.2 MB moved for 322.5 MB algorithmic; profiles/decode_tma_config2.md).
+# Traffic grows with the pages streamed, so the launch's traffic is its algorithmic bytes times this ratio.
+NCU_TRAFFIC_RATIO = 1.018
 
 
 def load_peaks():
@@ -334,7 +335,8 @@ def run_ours(args):
             "gpu_launches": timed_launches,
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only; the fused step adds RoPE + append to it)", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH, "bytes_per_launch": kern_bytes,
+                         "traffic": int(kern_bytes * NCU_TRAFFIC_RATIO), "traffic_source": "ncu capture of a 32-request case, scaled by bytes streamed",
+                         "bytes_per_launch": kern_bytes,
                          "us_per_launch": kern_ms * 1e3,
                          "frac_of_nominal_8tbs": achieved / 8000.0,
                          "step_frac": step_bytes / (ms / steps * 1e-3) / 1e9 / peak},
