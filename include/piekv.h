@@ -81,6 +81,16 @@ int piekv_version(void);
  * exceptions raised by the op library (pie/src/flashinfer_metal/ops.py:208-209). */
 const char *piekv_last_error_string(void);
 
+/* Process-wide options.  PIEKV_OPT_PDL: launch the tuned decode kernel with programmatic dependent
+ * launch so that its prologue overlaps the tail of the kernel before it on the stream.
+ *   0 off (default); 1 on, the kernel waits for the previous kernel before reading anything;
+ *   2 on, and the caller guarantees that kv_indptr is not written by the kernel immediately before
+ *     (the reference uploads the page tables once per step ahead of the layer loop,
+ *     pie/src/pie_worker/batching.py:196-239): the offsets are read before the wait.
+ * No reference counterpart. */
+#define PIEKV_OPT_PDL 0
+int piekv_set_option(int32_t key, int32_t value);
+
 /* ---- metadata (device-resident) ------------------------------------------------- */
 
 /* seq_lens[b] = max(npages_b - 1, 0) * page_size + last_page_len[b]  (a request without pages

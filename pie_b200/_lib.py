@@ -12,6 +12,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libpiekv.so"
 
 PIEKV_F32, PIEKV_F16, PIEKV_BF16 = 0, 1, 2
 ROPE_NONE, ROPE_PLAIN, ROPE_LLAMA31, ROPE_TABLE = 0, 1, 2, 3
+OPT_PDL = 0
 
 ERR_NAMES = {
     0: "ok",
@@ -50,6 +51,7 @@ _f32 = C.c_float
 SIGNATURES = {
     "piekv_version": (C.c_int, []),
     "piekv_last_error_string": (C.c_char_p, []),
+    "piekv_set_option": (C.c_int, [_i32, _i32]),
     "piekv_get_seq_lens": (C.c_int, [_p, _p, _i32, _i32, _p, _p]),
     "piekv_get_batch_indices_positions": (C.c_int, [_p, _p, _i32, _i32, _p, _p, _p]),
     "piekv_metadata": (C.c_int, [_p, _p, _p, _i32, _i32, _i32, _p, _p, _p, _p]),

@@ -30,6 +30,7 @@ int cuda_status(cudaError_t e, const char *what);  // 0 or -(int)e, records text
   } while (0)
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+int get_option(int key);  // library options set through piekv_set_option
 
 inline int dtype_size(int dtype) { return dtype == PIEKV_F32 ? 4 : 2; }
 

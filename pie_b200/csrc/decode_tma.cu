@@ -44,6 +44,7 @@ struct DecodeParams {
   float *part_o;    // [slot][PG][Hq][128]
   float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
   int *counters;    // [batch], zero between launches
+  int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets
 };
 
 // Extra inputs of the fused step (RoPE + append + attention in one launch): the new token's
@@ -106,6 +107,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   const AttnArgs &a = p.a;
   const int B = a.batch;
   const int c = blockIdx.x;
+  // Programmatic dependent launch: let the next kernel of the stream start its own prologue as SMs
+  // free up, and do not touch anything an earlier kernel may still be producing before the wait.
+  // Mode 2 is for callers whose page-table arrays are not written by the kernel just before this one
+  // (the reference uploads them once per step, ahead of the layer loop): the offsets are then read
+  // before the wait.  Both instructions do nothing in a launch without the attribute.
+  if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  if (p.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
   // one coalesced read of the page-table offsets instead of a chain of dependent searches in L2
   const int32_t *ip = a.kv_indptr;
   if (B <= kSmemBatch) {
@@ -122,6 +130,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_fence_init();
   }
   __syncthreads();
+  if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
   const int total_pages = ip[B];
   // With fewer pages than CTAs only the first `total_pages` CTAs take part, so that every
   // participating range is non-empty (the segment count of a request relies on that).
@@ -572,8 +581,23 @@ int launch_t(const CUtensorMap &tm, const DecodeParams &p, const FusedArgs &f, c
     if (e != cudaSuccess) return cuda_status(e, "decode: cudaFuncSetAttribute");
     configured = true;
   }
-  decode_tma_kernel<T, HKV, FUSED><<<sm_count(), kThreads, smem, st>>>(tm, p, f);
-  PIEKV_LAUNCH_CHECK("decode_tma_kernel");
+  if (p.pdl == 0) {
+    decode_tma_kernel<T, HKV, FUSED><<<sm_count(), kThreads, smem, st>>>(tm, p, f);
+    PIEKV_LAUNCH_CHECK("decode_tma_kernel");
+    return 0;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count());
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, decode_tma_kernel<T, HKV, FUSED>, tm, p, f);
+  if (e != cudaSuccess) return cuda_status(e, "decode_tma_kernel (programmatic dependent launch)");
   return 0;
 }
 
@@ -623,6 +647,7 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
                 (long long)workspace_bytes, (long long)need);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
   p->a = a;
+  p->pdl = get_option(PIEKV_OPT_PDL);
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p->counters = reinterpret_cast<int *>(ws);
   p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);

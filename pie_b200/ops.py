@@ -118,6 +118,12 @@ def device_error(device=None, clear: bool = True) -> Optional[dict]:
     }
 
 
+def set_programmatic_dependent_launch(mode: int) -> None:
+    """0 off, 1 on, 2 on with the promise that the page-table arrays are not written by the kernel that
+    runs immediately before a decode call (see PIEKV_OPT_PDL in include/piekv.h)."""
+    check(lib.piekv_set_option(_lib.OPT_PDL, int(mode)), "set_option")
+
+
 def _check_pool(pool: torch.Tensor, name: str = "paged_kv_cache"):
     if isinstance(pool, (tuple, list)):
         raise ValueError(f"{name}: separate (k_cache, v_cache) tensors are not supported; pass the "

@@ -378,3 +378,36 @@ def test_prefill_tensor_core_path_multi_tile(dtype, causal):
                custom_mask=torch.ones(total, dtype=torch.bool, device="cuda"), q_data_type=dtype)
         out2 = w.run(sc.q.cuda(), sc.pool.cuda())
         assert (out2.float() - out.float()).abs().max().item() <= 1e-2
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_decode_with_programmatic_dependent_launch(mode):
+    """Back-to-back fused steps launched with the PDL attribute give the same pages and outputs."""
+    from pie_b200 import workloads as W2
+    hq, hkv, d = 32, 8, 128
+    results = {}
+    for pdl in (0, mode):
+        ops.set_programmatic_dependent_launch(pdl)
+        try:
+            reqs = W2.PagedRequests(W2.seeded_perm(1024, 3))
+            for c in (15, 16, 1000, 1, 250, 3000, 77):
+                reqs.add(c)
+            metas = W2.decode_steps(reqs, 12)
+            pool = W2.randn((1024, 2, 16, hkv, d), 5, torch.bfloat16, 0.5).cuda()
+            w = ops.BatchDecodeWithPagedKVCacheWrapper(_workspace(), "NHD")
+            outs = []
+            q = W2.randn((7, hq, d), 100, torch.bfloat16, 0.5).cuda()
+            k = W2.randn((7, hkv, d), 200, torch.bfloat16, 0.5).cuda()
+            v = W2.randn((7, hkv, d), 300, torch.bfloat16, 0.5).cuda()
+            tabs = [(dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), dev(m.pos_ids)) for m in metas]
+            torch.cuda.synchronize()
+            for indptr, indices, last, pos in tabs:  # launched back to back, no host sync in between
+                w.plan(indptr, indices, last, hq, hkv, d, 16, q_data_type=torch.bfloat16)
+                outs.append(w.run_fused(q, k, v, pos, pool, ops.RopeConfig()))
+            torch.cuda.synchronize()
+            results[pdl] = (pool.clone(), torch.stack(outs))
+        finally:
+            ops.set_programmatic_dependent_launch(0)
+    assert ops.device_error("cuda") is None
+    assert torch.equal(results[0][0], results[mode][0])
+    assert torch.equal(results[0][1], results[mode][1])
