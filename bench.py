@@ -196,6 +196,8 @@ def run_ours(args):
     launches = [0]
     es = 2
 
+    ops.set_programmatic_dependent_launch(2)  # page tables are static inputs here: prologue overlaps the tail
+
     def qkv_views(t):
         q = t[:, : HQ * D].view(B, HQ, D)
         k = t[:, HQ * D: (HQ + HKV) * D].view(B, HKV, D)
@@ -327,7 +329,7 @@ def run_ours(args):
             "config": {"workload": WORKLOAD, "requests_per_gpu": B, "global_requests": B * n_gpus, "pool_pages": cfg.num_pages,
                        "parallelism": f"request-sharded x{n_gpus}, independent page pools, no collective",
                        "l2": "inputs larger than L2 (0.6 GB of KV per step vs 126 MB); no flush",
-                       "launch": "CUDA graph of all timed steps, one fused kernel per step",
+                       "launch": "CUDA graph of all timed steps, one fused kernel per step, programmatic dependent launch",
                        "step_algorithmic_bytes": step_bytes},
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -808,12 +810,97 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_flashinfer(args):
+    """Black-box comparator: the reference's CUDA dependency (FlashInfer, whatever version the box has)
+    driven through the call sequence of pie/src/pie_worker/model/llama3.py:660-689,745-791 on the headline
+    workload.  Never read, linked or copied - only called and timed."""
+    import flashinfer
+
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG2
+    B, HQ, HKV, D = 64, cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    steps, warmup = args.steps, args.warmup
+    horizon = min(HORIZON, steps + warmup)
+    metas = build_steps(0, horizon)
+
+    def t(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+    tabs = [dict(indptr=t(m.kv_indptr), indices=t(m.kv_indices), last=t(m.kv_last_page_len), pos=t(m.pos_ids),
+                 qo=t(m.qo_indptr)) for m in metas]
+    pool = W.randn(cfg.pool_shape(), 100, cfg.dtype, cfg.value_scale, device=dev)
+    qkv = W.randn((8, B, (HQ + 2 * HKV) * D), 200, cfg.dtype, cfg.value_scale, device=dev)
+    ws = torch.zeros(128 << 20, dtype=torch.uint8, device=dev)
+    w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+
+    def step(i, plan=True):
+        tb = tabs[i % horizon]
+        x = qkv[i % 8]
+        q = x[:, : HQ * D].view(B, HQ, D)
+        k = x[:, HQ * D: (HQ + HKV) * D].view(B, HKV, D)
+        v = x[:, (HQ + HKV) * D:].view(B, HKV, D)
+        seq = flashinfer.get_seq_lens(tb["indptr"], tb["last"], 16)
+        bi, kp = flashinfer.get_batch_indices_positions(tb["qo"], seq, B)
+        if plan:
+            w.plan(indptr=tb["indptr"], indices=tb["indices"], last_page_len=tb["last"], num_qo_heads=HQ,
+                   num_kv_heads=HKV, head_dim=D, page_size=16, pos_encoding_mode="NONE", q_data_type=cfg.dtype)
+        flashinfer.apply_llama31_rope_pos_ids_inplace(q=q, k=k, pos_ids=tb["pos"], rope_scale=8.0, rope_theta=5e5,
+                                                      low_freq_factor=1.0, high_freq_factor=4.0, old_context_len=8192)
+        flashinfer.append_paged_kv_cache(append_key=k, append_value=v, batch_indices=bi, positions=kp,
+                                         paged_kv_cache=pool, kv_indices=tb["indices"], kv_indptr=tb["indptr"],
+                                         kv_last_page_len=tb["last"], kv_layout="NHD")
+        return w.run(q, pool)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(warmup + i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    # attention kernel alone on one table
+    mid = (warmup + steps // 2) % horizon
+    tb = tabs[mid]
+    w.plan(indptr=tb["indptr"], indices=tb["indices"], last_page_len=tb["last"], num_qo_heads=HQ, num_kv_heads=HKV,
+           head_dim=D, page_size=16, pos_encoding_mode="NONE", q_data_type=cfg.dtype)
+    q = qkv[0][:, : HQ * D].view(B, HQ, D)
+    for _ in range(5):
+        w.run(q, pool)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(100):
+        w.run(q, pool)
+    k1.record()
+    torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / 100
+    m = metas[mid]
+    tokens = int(m.seq_lens.astype(np.int64).sum())
+    kern_bytes = tokens * 2 * HKV * D * 2 + B * 2 * HQ * D * 2 + 4 * (len(m.kv_indices) + 2 * B + 1)
+    peak, peak_kind = load_peaks()
+    print(json.dumps({
+        "impl": "flashinfer", "version": flashinfer.__version__, "metric": METRIC, "value": B * steps / (ms * 1e-3),
+        "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "launch": "eager: get_seq_lens, get_batch_indices_positions, plan, rope, "
+                                                   "append, run per step (the reference's per-step sequence)"},
+        "roofline": {"bound": "hbm", "kernel": "BatchDecodeWithPagedKVCacheWrapper.run", "achieved":
+                     kern_bytes / (kern_ms * 1e-3) / 1e9, "peak": peak, "unit": "GB/s",
+                     "frac": kern_bytes / (kern_ms * 1e-3) / 1e9 / peak, "peak_source": peak_kind,
+                     "us_per_launch": kern_ms * 1e3, "bytes_per_launch": kern_bytes}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=16)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flashinfer"])
     ap.add_argument("--cpu-steps", type=int, default=0, help="CPU-baseline sample size in steps (0 = ~20 s)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling runs)")
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
@@ -827,6 +914,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "flashinfer":
+        run_flashinfer(args)
     elif args.workload == "prefill":
         run_prefill(args)
     elif args.workload == "decode70b":
