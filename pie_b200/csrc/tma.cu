@@ -41,12 +41,12 @@ int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int h
 }
 
 int make_q_tensor_map(CUtensorMap *tm, const void *q, int64_t nnz, int hq, int64_t q_sn, int64_t q_sh, int dtype,
-                      int box_rows) {
+                      int box_rows, int box_heads) {
   EncodeTiledFn enc = get_encode_fn();
   PIEKV_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
   cuuint64_t gdim[4] = {64, (cuuint64_t)nnz, 2, (cuuint64_t)hq};
   cuuint64_t gstr[3] = {(cuuint64_t)q_sn * 2, 128, (cuuint64_t)q_sh * 2};
-  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 2, 1};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 2, (cuuint32_t)box_heads};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, tm_dtype(dtype), 4, const_cast<void *>(q), gdim, gstr, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

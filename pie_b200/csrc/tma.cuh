@@ -12,9 +12,9 @@ namespace piekv {
 int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int hkv, int dtype, int box_halves,
                          int box_heads, int box_kv);
 
-// q [n, Hq, 128] (strides in elements) seen as {64 d, n tokens, 2 d-halves, Hq}; box {64, rows, 2, 1}.
+// q [n, Hq, 128] (strides in elements) seen as {64 d, n tokens, 2 d-halves, Hq}; box {64, rows, 2, heads}.
 int make_q_tensor_map(CUtensorMap *tm, const void *q, int64_t nnz, int hq, int64_t q_sn, int64_t q_sh, int dtype,
-                      int box_rows);
+                      int box_rows, int box_heads = 1);
 
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *tmap, int c0, int c1, int c2, int c3,
                                             int c4, uint64_t *bar) {
