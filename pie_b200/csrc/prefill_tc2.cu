@@ -34,16 +34,37 @@ using namespace prefill;
 namespace {
 
 constexpr int k2SmemBytes = kTileBytes * (2 + kKStages + kVStages) + 1024;
+// Three warpgroups: two of softmax warps and one holding the producer and MMA warps (its other two
+// warps idle).  The third gives most of its registers to the softmax warps, which keep a whole row
+// of 128 scores in registers.
+constexpr int k2Threads = 384;
+constexpr int k2RegsLaunch = 168;  // what __launch_bounds__(384, 1) gives every thread at launch
+constexpr int k2RegsSoftmax = 200, k2RegsOther = 96;
+// setmaxnreg.inc waits until the registers exist: the CTA owns 384 * 168 and not one more
+static_assert(256 * k2RegsSoftmax + 128 * k2RegsOther <= k2Threads * k2RegsLaunch, "register budget of the CTA");
+static_assert(k2RegsSoftmax % 8 == 0 && k2RegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr int k2ColS = 0;    // + 128 * head
 constexpr int k2ColO = 256;  // + 128 * head
 
+// not volatile: the scheduler may interleave these with the surrounding arithmetic
+__device__ __forceinline__ float exp2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+  return y;
+}
+
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(k2Threads, 1)
     prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                        const __grid_constant__ PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages],
-      s_full[2], p_full[2], o_done[2];
+      s_full[2], p_full[2][2], o_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int sh_abort;
 
@@ -85,12 +106,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   T *out = reinterpret_cast<T *>(a.out);
 
   if (n_active == 0) {  // nothing to attend to: zeros for both heads
-    for (int x = threadIdx.x; x < rows * (2 * kDim / 8); x += kThreads) {
+    for (int x = threadIdx.x; x < rows * (2 * kDim / 8); x += k2Threads) {
       const int r = x / (2 * kDim / 8), c8 = x % (2 * kDim / 8);
       *reinterpret_cast<uint4 *>(out + ((size_t)(q0 + r0 + r) * a.hq + h0) * kDim + c8 * 8) = make_uint4(0, 0, 0, 0);
     }
     if (a.lse != nullptr)
-      for (int x = threadIdx.x; x < rows * 2; x += kThreads)
+      for (int x = threadIdx.x; x < rows * 2; x += k2Threads)
         a.lse[(size_t)(q0 + r0 + (x >> 1)) * a.hq + h0 + (x & 1)] = -INFINITY;
     return;
   }
@@ -112,7 +133,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(&s_full[x], 1);
-      mbar_init(&p_full[x], 128);
+      mbar_init(&p_full[x][0], 4);  // one arrival per softmax warp
+      mbar_init(&p_full[x][1], 4);
       mbar_init(&o_done[x], 1);
     }
     sh_abort = 0;
@@ -129,7 +151,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile int *abort_flag = &sh_abort;
   constexpr bool kBf16 = !std::is_same<T, __half>::value;
 
-  if (warp == kProducerWarp) {
+  if (warp >= kSoftmaxWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(k2RegsOther));
+  if (warp > kMmaWarp) {
+    // idle warps of the third warpgroup
+  } else if (warp == kProducerWarp) {
     // ================================================================== TMA producer
     int k_armed = 0, v_armed = 0;  // K / V tiles issued so far
     int jk = 0, jv = 0;            // next kv tile index to consider for K / for V
@@ -226,13 +252,16 @@ __global__ void __launch_bounds__(kThreads, 1)
       auto issue_pv = [&](int x, int jj) -> bool {
         const int vs = jj % kVStages;
         if (!wait_or_abort(&v_full[vs], (jj / kVStages) & 1, abort_flag)) return false;
-        if (!wait_or_abort(&p_full[x], jj & 1, abort_flag)) return false;
-        tc::fence_after_sync();
         const uint32_t v_smem = v_smem0 + vs * kTileBytes;
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          tc::mma_ts(tmem + k2ColO + x * 128, tmem + k2ColS + x * 128 + ks * 8,
-                     tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
+        for (int half = 0; half < 2; ++half) {  // P_x arrives in two halves of 64 kv tokens
+          if (!wait_or_abort(&p_full[x][half], jj & 1, abort_flag)) return false;
+          tc::fence_after_sync();
+#pragma unroll
+          for (int ks = half * 4; ks < half * 4 + 4; ++ks) {
+            tc::mma_ts(tmem + k2ColO + x * 128, tmem + k2ColS + x * 128 + ks * 8,
+                       tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
+          }
         }
         tc::commit(&o_done[x]);
         return true;
@@ -265,8 +294,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         atomicExch(&sh_abort, 1);
       }
     }
+  }
   } else {
     // ================================================ softmax of head x (thread = row = TMEM lane)
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(k2RegsSoftmax));
     const int x = warp >> 2;   // 0: head A, 1: head B
     const int q4 = warp & 3;   // TMEM lane quarter of this warp
     const int row = q4 * 32 + lane;
@@ -292,29 +323,30 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool full_tile = has_mask ? (mw.x & mw.y & mw.z & mw.w) == 0xffffffffu : t0 + kBN - 1 <= limit;
       const uint32_t mwords[4] = {mw.x, mw.y, mw.z, mw.w};
 
-      // ---- pass 1 over the row's 128 scores, 32 at a time: running maximum (four independent chains)
-      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      // ---- the row's 128 scores into registers (one wait for the four loads)
+      uint32_t sr[128];
+      tc::tmem_ld32(s_addr, sr);
+      tc::tmem_ld32(s_addr + 32, sr + 32);
+      tc::tmem_ld32(s_addr + 64, sr + 64);
+      tc::tmem_ld32(s_addr + 96, sr + 96);
+      tc::tmem_wait_ld();
+      if (!full_tile) {  // mask in place: -inf scores give probability 0 below
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        tc::tmem_ld32(s_addr + ch * 32, r);
-        tc::tmem_wait_ld();
-        if (full_tile) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mxa[i & 3] = fmaxf(mxa[i & 3], __uint_as_float(r[i]));
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const bool allow = has_mask ? ((mwords[ch] >> i) & 1u) != 0 : t0 + ch * 32 + i <= limit;
-            mxa[i & 3] = fmaxf(mxa[i & 3], allow ? __uint_as_float(r[i]) : -INFINITY);
-          }
+        for (int i = 0; i < 128; ++i) {
+          const bool allow = has_mask ? ((mwords[i >> 5] >> (i & 31)) & 1u) != 0 : t0 + i <= limit;
+          sr[i] = allow ? sr[i] : 0xff800000u;
         }
       }
+      // ---- running maximum: four independent chains of three-input max
+      float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int i = 0; i < 64; ++i)
+        mxa[i & 3] = max3(mxa[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
       float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * c;  // c > 0
       float alpha = 1.f;
       bool rescale = false;
       if (mx > m_ref + 8.f) {
-        alpha = fast_exp2(m_ref - mx);  // m_ref = -inf on the first hit: 0
+        alpha = exp2_approx(m_ref - mx);  // m_ref = -inf on the first hit: 0
         l *= alpha;
         m_ref = mx;
         rescale = it > 0;
@@ -331,37 +363,30 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc::tmem_st32(o_addr + ch * 32, oreg);
         }
       }
-      // ---- pass 2: probabilities, packed two per column and written back over the row's first 64
-      // score columns (chunk ch of the scores, columns 32ch.., lands in columns 16ch.., which earlier
-      // chunks have already consumed)
+      // ---- probabilities, packed two per column, written back over the row's first 64 score columns
+      // in four pieces of 16 columns; the MMA warp is released after each half (64 kv tokens) so that
+      // O += P V starts while the second half is still being exponentiated
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float suma[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
         uint32_t pk[16];
-        tc::tmem_ld32(s_addr + ch * 32, r);
-        tc::tmem_wait_ld();
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          float s0 = __uint_as_float(r[2 * i]), s1 = __uint_as_float(r[2 * i + 1]);
-          if (!full_tile) {
-            const bool a0 = has_mask ? ((mwords[ch] >> (2 * i)) & 1u) != 0 : t0 + ch * 32 + 2 * i <= limit;
-            const bool a1 = has_mask ? ((mwords[ch] >> (2 * i + 1)) & 1u) != 0 : t0 + ch * 32 + 2 * i + 1 <= limit;
-            s0 = a0 ? s0 : -INFINITY;
-            s1 = a1 ? s1 : -INFINITY;
-          }
-          const float p0v = fast_exp2(fmaf(s0, c, neg_m));
-          const float p1v = fast_exp2(fmaf(s1, c, neg_m));
+          const float p0v = exp2_approx(fmaf(__uint_as_float(sr[ch * 32 + 2 * i]), c, neg_m));
+          const float p1v = exp2_approx(fmaf(__uint_as_float(sr[ch * 32 + 2 * i + 1]), c, neg_m));
           suma[i & 3] += p0v + p1v;
           pk[i] = pack2<T>(p0v, p1v);  // tokens 32ch + 2i (low half) and + 2i + 1 (high half)
         }
         tc::tmem_st16(s_addr + ch * 16, pk);
+        if (ch & 1) {
+          tc::tmem_wait_st();
+          tc::fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&p_full[x][ch >> 1]);
+        }
       }
       l += (suma[0] + suma[1]) + (suma[2] + suma[3]);
-      tc::tmem_wait_st();
-      tc::fence_before_sync();
-      mbar_arrive(&p_full[x]);
       ++it;
     }
 
@@ -417,7 +442,7 @@ int launch_t(const AttnArgs &a, const CUtensorMap &tq, const CUtensorMap &tkv, c
   }
   const long long blocks = (long long)max_tiles * (a.hq / 2);
   PIEKV_REQUIRE(blocks < (1ll << 31), "prefill: too many tiles");
-  prefill_tc2_kernel<T><<<(unsigned)blocks, kThreads, k2SmemBytes, st>>>(tq, tkv, p);
+  prefill_tc2_kernel<T><<<(unsigned)blocks, k2Threads, k2SmemBytes, st>>>(tq, tkv, p);
   PIEKV_LAUNCH_CHECK("prefill_tc2_kernel");
   return 0;
 }
