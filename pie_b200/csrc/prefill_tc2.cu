@@ -321,27 +321,28 @@ __global__ void __launch_bounds__(k2Threads, 1)
       tc::fence_after_sync();
       const int t0 = j * kBN;
       const bool full_tile = has_mask ? (mw.x & mw.y & mw.z & mw.w) == 0xffffffffu : t0 + kBN - 1 <= limit;
-      const uint32_t mwords[4] = {mw.x, mw.y, mw.z, mw.w};
 
-      // ---- the row's 128 scores into registers (one wait for the four loads)
-      uint32_t sr[128];
-      tc::tmem_ld32(s_addr, sr);
-      tc::tmem_ld32(s_addr + 32, sr + 32);
-      tc::tmem_ld32(s_addr + 64, sr + 64);
-      tc::tmem_ld32(s_addr + 96, sr + 96);
-      tc::tmem_wait_ld();
-      if (!full_tile) {  // mask in place: -inf scores give probability 0 below
-#pragma unroll
-        for (int i = 0; i < 128; ++i) {
-          const bool allow = has_mask ? ((mwords[i >> 5] >> (i & 31)) & 1u) != 0 : t0 + i <= limit;
-          sr[i] = allow ? sr[i] : 0xff800000u;
-        }
-      }
-      // ---- running maximum: four independent chains of three-input max
+      // ---- pass 1: running maximum, 64 columns at a time (rolled: the unrolled body of a whole row is
+      // ~10 KB of code per softmax warp, which evicts the MMA thread's code from the instruction cache)
       float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t sr[64];
+        tc::tmem_ld32(s_addr + h * 64, sr);
+        tc::tmem_ld32(s_addr + h * 64 + 32, sr + 32);
+        tc::tmem_wait_ld();
+        if (!full_tile) {
+          const uint32_t w0 = h ? mw.z : mw.x, w1 = h ? mw.w : mw.y;
 #pragma unroll
-      for (int i = 0; i < 64; ++i)
-        mxa[i & 3] = max3(mxa[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+          for (int i = 0; i < 64; ++i) {
+            const bool allow = has_mask ? (((i < 32 ? w0 : w1) >> (i & 31)) & 1u) != 0 : t0 + h * 64 + i <= limit;
+            sr[i] = allow ? sr[i] : 0xff800000u;
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          mxa[i & 3] = max3(mxa[i & 3], __uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]));
+      }
       float mx = fmaxf(fmaxf(mxa[0], mxa[1]), fmaxf(mxa[2], mxa[3])) * c;  // c > 0
       float alpha = 1.f;
       bool rescale = false;
@@ -353,7 +354,7 @@ __global__ void __launch_bounds__(k2Threads, 1)
       }
       // O_x is stable here: S_x(it) was committed after O_x(it-1) in the pipe's issue order
       if (__any_sync(0xffffffffu, rescale)) {
-#pragma unroll
+#pragma unroll 1
         for (int ch = 0; ch < 4; ++ch) {
           uint32_t oreg[32];
           tc::tmem_ld32(o_addr + ch * 32, oreg);
@@ -363,28 +364,40 @@ __global__ void __launch_bounds__(k2Threads, 1)
           tc::tmem_st32(o_addr + ch * 32, oreg);
         }
       }
-      // ---- probabilities, packed two per column, written back over the row's first 64 score columns
-      // in four pieces of 16 columns; the MMA warp is released after each half (64 kv tokens) so that
-      // O += P V starts while the second half is still being exponentiated
+      // ---- pass 2: probabilities, packed two per column, written back over the row's first 64 score
+      // columns; the MMA warp is released after each half (64 kv tokens) so that O += P V starts while
+      // the second half is still being exponentiated.  Half h reads score columns [64h, 64h + 64) and
+      // writes packed columns [32h, 32h + 32), which only cover scores already consumed.
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float suma[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        uint32_t sr[64];
+        uint32_t pk[32];
+        tc::tmem_ld32(s_addr + h * 64, sr);
+        tc::tmem_ld32(s_addr + h * 64 + 32, sr + 32);
+        tc::tmem_wait_ld();
+        if (!full_tile) {
+          const uint32_t w0 = h ? mw.z : mw.x, w1 = h ? mw.w : mw.y;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t pk[16];
+          for (int i = 0; i < 64; ++i) {
+            const bool allow = has_mask ? (((i < 32 ? w0 : w1) >> (i & 31)) & 1u) != 0 : t0 + h * 64 + i <= limit;
+            sr[i] = allow ? sr[i] : 0xff800000u;
+          }
+        }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0v = exp2_approx(fmaf(__uint_as_float(sr[ch * 32 + 2 * i]), c, neg_m));
-          const float p1v = exp2_approx(fmaf(__uint_as_float(sr[ch * 32 + 2 * i + 1]), c, neg_m));
+        for (int i = 0; i < 32; ++i) {
+          const float p0v = exp2_approx(fmaf(__uint_as_float(sr[2 * i]), c, neg_m));
+          const float p1v = exp2_approx(fmaf(__uint_as_float(sr[2 * i + 1]), c, neg_m));
           suma[i & 3] += p0v + p1v;
-          pk[i] = pack2<T>(p0v, p1v);  // tokens 32ch + 2i (low half) and + 2i + 1 (high half)
+          pk[i] = pack2<T>(p0v, p1v);  // tokens 64h + 2i (low half) and + 2i + 1 (high half)
         }
-        tc::tmem_st16(s_addr + ch * 16, pk);
-        if (ch & 1) {
-          tc::tmem_wait_st();
-          tc::fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&p_full[x][ch >> 1]);
-        }
+        tc::tmem_st16(s_addr + h * 32, pk);
+        tc::tmem_st16(s_addr + h * 32 + 16, pk + 16);
+        tc::tmem_wait_st();
+        tc::fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&p_full[x][h]);
       }
       l += (suma[0] + suma[1]) + (suma[2] + suma[3]);
       ++it;
