@@ -3,8 +3,8 @@
 // A CTA works on one (request, 128-token query tile) for TWO query heads of the same GQA group,
 // so both 128 x 128 problems share every K and V tile brought into shared memory: half the K/V
 // fill and twice the tensor work per tile compared with one head per CTA.  The two heads
-// ("A" and "B") are processed in ping-pong: while the softmax warps of A work on S_A, the tensor
-// pipe runs B's MMAs and vice versa.
+// ("A" and "B") overlap: while the softmax warps of one head work on its scores, the tensor pipe
+// runs the other head's MMAs.
 //
 //   TMEM (512 columns): S_A/P_A [0,128)  S_B/P_B [128,256)  O_A [256,384)  O_B [384,512)
 //   smem: Q_A, Q_B (64 KiB, one TMA box), K ring (3 x 32 KiB), V ring (2 x 32 KiB)
@@ -12,15 +12,22 @@
 // P never goes through shared memory: a softmax thread owns a whole row (one TMEM lane), reads the
 // row's 128 scores, and writes the probabilities back over the same columns as packed 16-bit pairs
 // (64 columns); O += P V then takes its A operand from TMEM.  S is therefore single-buffered per
-// head, and the order of MMAs per kv tile j issued by the one MMA thread is
-//     S_A(j)   O_B(j-1)   S_B(j)   O_A(j)
-// so that every softmax has the time of two MMAs of the other head.  The tensor pipe executes MMAs
-// in issue order, hence S_X(j) implicitly follows O_X(j-1), which consumed P_X(j-1) in the same
-// columns, and O_X is stable whenever S_X(j) has been committed.
+// head.  One thread issues every MMA, in the order
+//     S_A(0) S_B(0)   then per kv tile t:   O_A(t) S_A(t+1)   O_B(t) S_B(t+1)
+// The tensor pipe executes MMAs in issue order, hence S_x(t+1) follows O_x(t), which consumed P_x(t)
+// in the same columns, and O_x is stable whenever S_x has been committed.
 //
-// Roles: warps 0-3 softmax of head A (thread = row), warps 4-7 softmax of head B, warp 8 TMA
-// producer, warp 9 MMA issuer and TMEM owner.  Masking, the device-built work list, the packed custom
-// mask and the bounded waits are those of the one-head kernel (prefill_tc.cu).
+// What bounds the kernel: a 128 x 128 tile needs 16384 exponentials, and the SM's special-function
+// units deliver 16 per clock, i.e. 1024 clocks - as long as the tile's two MMAs (2 x 512 clocks at
+// 8192 flop/clk).  Measured on B200, one softmax pass of a tile takes ~1.8k clocks when it has the
+// SM to itself, the MMAs run at 64 clocks each once queued, and the pipe accepts only about two
+// MMAs ahead of the running one, so every wait of the issuing thread shows as idle tensor time.
+//
+// Roles (384 threads, three warpgroups): warps 0-3 softmax of head A (thread = row), warps 4-7
+// softmax of head B, warp 8 TMA producer, warp 9 MMA issuer and TMEM owner, warps 10-11 idle.  The
+// third warpgroup gives registers to the softmax warps (setmaxnreg).  Masking, the device-built work
+// list, the packed custom mask and the bounded waits are those of the one-head kernel
+// (prefill_tc.cu).
 #include <type_traits>
 
 #include "prefill_common.cuh"
@@ -236,58 +243,74 @@ __global__ void __launch_bounds__(k2Threads, 1)
     if (lane == 0) {
       constexpr uint32_t idesc_qk = tc::instr_desc(kBf16, false, false, kBM, kBN);
       constexpr uint32_t idesc_pv = tc::instr_desc(kBf16, false, true, kBM, kDim);
-      // S_x = Q_x K^T into the head's score columns (P_x of the previous tile has been consumed:
-      // the pipe runs O_x(prev) before this)
-      auto issue_qk = [&](int x, int kst) {
-        const uint32_t k_smem = k_smem0 + kst * kTileBytes;
+      // Descriptors are built once; per MMA only the 14-bit start-address field (bytes >> 4) moves, by
+      // amounts known at compile time.
+      const uint64_t q_desc[2] = {tc::desc_k_major(q_smem), tc::desc_k_major(q_smem + kTileBytes)};
+      const uint64_t k_desc0 = tc::desc_k_major(k_smem0);
+      const uint64_t v_desc0 = tc::desc_mn_major(v_smem0, kHalfBytes);
+      // S_x = Q_x K^T into the head's score columns; K tile number t has landed
+      auto issue_qk = [&](int x, int t) {
+        const uint64_t kd = k_desc0 + (uint64_t)(((t % kKStages) * kTileBytes) >> 4);
+        const uint64_t qd = q_desc[x];
+        const uint32_t d = tmem + k2ColS + x * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t off = (ks >> 2) * kHalfBytes + (ks & 3) * 32;
-          tc::mma_ss(tmem + k2ColS + x * 128, tc::desc_k_major(q_smem + x * kTileBytes + off),
-                     tc::desc_k_major(k_smem + off), idesc_qk, ks > 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((ks >> 2) * kHalfBytes + (ks & 3) * 32) >> 4);
+          tc::mma_ss(d, qd + off, kd + off, idesc_qk, ks > 0 ? 1u : 0u);
         }
         tc::commit(&s_full[x]);
       };
-      // O_x += P_x V for processed tile number jj; P_x is read from TMEM (two 16-bit values per column)
-      auto issue_pv = [&](int x, int jj) -> bool {
-        const int vs = jj % kVStages;
-        if (!wait_or_abort(&v_full[vs], (jj / kVStages) & 1, abort_flag)) return false;
-        const uint32_t v_smem = v_smem0 + vs * kTileBytes;
+      // O_x += P_x V for tile number t (V tile t has landed); P_x is read from TMEM (two 16-bit values
+      // per column) and arrives in two halves of 64 kv tokens
+      auto issue_pv = [&](int x, int t) -> bool {
+        const uint64_t vd = v_desc0 + (uint64_t)(((t % kVStages) * kTileBytes) >> 4);
+        const uint32_t d = tmem + k2ColO + x * 128;
+        const uint32_t pa = tmem + k2ColS + x * 128;
+        if (!wait_or_abort(&p_full[x][0], t & 1, abort_flag)) return false;
+        tc::fence_after_sync();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {  // P_x arrives in two halves of 64 kv tokens
-          if (!wait_or_abort(&p_full[x][half], jj & 1, abort_flag)) return false;
-          tc::fence_after_sync();
+        for (int ks = 0; ks < 4; ++ks)
+          tc::mma_ts(d, pa + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, (t > 0 || ks > 0) ? 1u : 0u);
+        if (!wait_or_abort(&p_full[x][1], t & 1, abort_flag)) return false;
+        tc::fence_after_sync();
 #pragma unroll
-          for (int ks = half * 4; ks < half * 4 + 4; ++ks) {
-            tc::mma_ts(tmem + k2ColO + x * 128, tmem + k2ColS + x * 128 + ks * 8,
-                       tc::desc_mn_major(v_smem + ks * 2048, kHalfBytes), idesc_pv, (jj > 0 || ks > 0) ? 1u : 0u);
-          }
-        }
-        tc::commit(&o_done[x]);
+        for (int ks = 4; ks < 8; ++ks)
+          tc::mma_ts(d, pa + ks * 8, vd + (uint64_t)((ks * 2048) >> 4), idesc_pv, 1u);
         return true;
       };
-      bool ok = wait_or_abort(&q_full, 0, abort_flag);
-      int it = 0;
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (!active(j)) continue;
-        const int kst = it % kKStages;
-        ok = wait_or_abort(&k_full[kst], (it / kKStages) & 1, abort_flag);
-        if (!ok) break;
-        tc::fence_after_sync();
-        issue_qk(0, kst);  // S_A(it)
-        if (it >= 1) {     // O_B(it-1); after it both heads are done with V tile it-1
-          ok = issue_pv(1, it - 1);
-          if (!ok) break;
-          tc::commit(&v_empty[(it - 1) % kVStages]);
-        }
-        issue_qk(1, kst);  // S_B(it); K tile free once both S are done
-        tc::commit(&k_empty[kst]);
-        ok = issue_pv(0, it);  // O_A(it)
-        ++it;
+      // Issue order: S_A(0) S_B(0), then per tile t:  O_A(t) S_A(t+1)  O_B(t) S_B(t+1).
+      // A head's next scores follow its O += P V immediately, so the time from the end of one softmax
+      // to the start of the next is one and a half MMA batches; the softmax of a 128 x 128 tile (bound
+      // by the 16 exp/clk of the SM) takes about twice as long as the two MMAs, so that turnaround, not
+      // tensor time, is what the order has to keep short.  The pipe executes in issue order, hence
+      // S_x(t+1) follows O_x(t), which consumed P_x(t) in the same columns, and O_x is stable whenever
+      // S_x has been committed.
+      bool ok = wait_or_abort(&q_full, 0, abort_flag) && wait_or_abort(&k_full[0], 0, abort_flag);
+      if (ok) {
+        issue_qk(0, 0);
+        issue_qk(1, 0);
+        tc::commit(&k_empty[0]);
       }
-      if (ok && it >= 1) {
-        ok = issue_pv(1, it - 1);
-        if (ok) tc::commit(&v_empty[(it - 1) % kVStages]);
+      for (int t = 0; ok && t < n_active; ++t) {
+        const bool more = t + 1 < n_active;
+        ok = wait_or_abort(&v_full[t % kVStages], (t / kVStages) & 1, abort_flag) && issue_pv(0, t);
+        if (!ok) break;
+        if (more) {
+          ok = wait_or_abort(&k_full[(t + 1) % kKStages], ((t + 1) / kKStages) & 1, abort_flag);
+          if (!ok) break;
+          issue_qk(0, t + 1);
+        } else {
+          tc::commit(&o_done[0]);  // all of head A's MMAs
+        }
+        ok = issue_pv(1, t);
+        if (!ok) break;
+        tc::commit(&v_empty[t % kVStages]);  // both heads are done with V tile t
+        if (more) {
+          issue_qk(1, t + 1);
+          tc::commit(&k_empty[(t + 1) % kKStages]);  // and with K tile t + 1
+        } else {
+          tc::commit(&o_done[1]);
+        }
       }
       if (!ok) {
         if (!*abort_flag) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 200);
@@ -404,7 +427,7 @@ __global__ void __launch_bounds__(k2Threads, 1)
     }
 
     // ---- epilogue: O_x / l -> out, head h0 + x
-    if (ok) ok = wait_or_abort(&o_done[x], (n_active - 1) & 1, abort_flag);
+    if (ok) ok = wait_or_abort(&o_done[x], 0, abort_flag);  // committed once, after the last tile
     if (ok) {
       tc::fence_after_sync();
       const float inv = l > 0.f ? 1.f / l : 0.f;
