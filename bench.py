@@ -470,7 +470,7 @@ def run_prefill(args):
                                f"({'boolean custom mask' if mask is not None else 'native causal flag'}), "
                                "32q/8kv heads, D128, bf16, page16", "pool_pages": num_pages},
         "clocks": sampler.summary(),
-        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel", "achieved": tf, "peak": peak,
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc2_kernel (two query heads per CTA)", "achieved": tf, "peak": peak,
                      "unit": "TFLOP/s", "frac": tf / peak, "peak_source": peak_kind, "traffic": None,
                      "flops_causal_exact": flops, "ms_per_launch": attn_ms},
         "device_error_word": ops.device_error(dev),
