@@ -217,6 +217,9 @@ def run_ours(args):
         launches[0] += 1
 
     def barrier():
+        # device idle first: the barrier's own NCCL kernel would otherwise run (and spin) beside the
+        # timed kernels and take an SM away from a grid that fills all of them
+        torch.cuda.synchronize(dev)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
@@ -418,16 +421,59 @@ def run_prefill(args):
     w = ops.BatchPrefillWithPagedKVCacheWrapper(ws, "NHD")
     w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, causal=True, q_data_type=cfg.dtype)
     mask = None
-    if args.prefill_mask:
-        from oracle import paged_kv_ref as R  # only to expand the reference-form boolean mask once
-        runs, rptr = [], [0]
-        for b in range(meta.batch):
-            qlen = int(meta.qo_indptr[b + 1] - meta.qo_indptr[b])
-            r, _ = R.causal_brle(int(meta.seq_lens[b]) - qlen, qlen)
-            runs += r
-            rptr += [rptr[-1] + i + 1 for i in range(qlen)]
-        mask = t(R.build_flat_mask(meta.qo_indptr, meta.kv_indptr, meta.kv_last_page_len, 16, runs, rptr))
-        w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, custom_mask=mask, q_data_type=cfg.dtype)
+    mask_plan = None
+    if args.prefill_mask or args.prefill_brle:
+        # the causal mask in the wire form (one attend run of position + 1 entries per query token), then
+        # either expanded on the host to the reference's flat boolean mask and uploaded, or uploaded as
+        # runs and expanded to bits on the device
+        from pie_b200.batching import decode_brle_batch
+        counts = np.diff(meta.qo_indptr).astype(np.int64)
+        seq_l = np.asarray(meta.seq_lens, dtype=np.int64)
+        tok_pos = np.arange(n, dtype=np.int64) - np.repeat(meta.qo_indptr[:-1].astype(np.int64), counts) \
+            + np.repeat(seq_l - counts, counts)
+        runs_np = (tok_pos + 1).astype(np.uint32)
+        rptr_np = np.arange(n + 1, dtype=np.int32)
+        acc = np.zeros(n + 1, dtype=np.int64)
+        np.cumsum(np.repeat(seq_l, counts), out=acc[1:])
+        mask_bits = int(acc[-1])
+        reps = 5
+        m0, m1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if args.prefill_brle:
+            h_runs = torch.from_numpy(runs_np.view(np.int32).copy()).pin_memory()
+            h_ptr = torch.from_numpy(rptr_np).pin_memory()
+            d_runs, d_ptr = torch.empty_like(h_runs, device=dev), torch.empty_like(h_ptr, device=dev)
+            t_host0 = time.perf_counter()
+            t_host = time.perf_counter() - t_host0  # nothing to expand on the host
+            for i in range(reps + 1):
+                if i == 1:
+                    m0.record()
+                d_runs.copy_(h_runs, non_blocking=True)
+                d_ptr.copy_(h_ptr, non_blocking=True)
+                w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, brle_mask=(d_runs, d_ptr, mask_bits),
+                       q_data_type=cfg.dtype)
+                w._device_plan(n, num_pages)
+            m1.record()
+            h2d = h_runs.numel() * 4 + h_ptr.numel() * 4
+            form = "BRLE runs expanded to bits on the device"
+            mask = d_runs
+        else:
+            t_host0 = time.perf_counter()
+            flat = decode_brle_batch(runs_np, rptr_np, tok_pos, acc)
+            t_host = time.perf_counter() - t_host0
+            h_mask = torch.from_numpy(flat).pin_memory()
+            mask = torch.empty_like(h_mask, device=dev)
+            for i in range(reps + 1):
+                if i == 1:
+                    m0.record()
+                mask.copy_(h_mask, non_blocking=True)
+                w.plan(qo, indptr, indices, last, HQ, HKV, D, 16, custom_mask=mask, q_data_type=cfg.dtype)
+                w._device_plan(n, num_pages)
+            m1.record()
+            h2d = h_mask.numel()
+            form = "flat boolean mask (reference form), bit-packed on the device"
+        torch.cuda.synchronize(dev)
+        mask_plan = {"form": form, "h2d_bytes": int(h2d), "upload_plus_plan_ms": m0.elapsed_time(m1) / reps,
+                     "host_expand_ms": t_host * 1e3, "pairs": mask_bits}
 
     def step():
         ops.rope_append_paged_kv_cache(q, k, v, pos, bi, kp, pool, indices, indptr, last, rope)
@@ -467,12 +513,13 @@ def run_prefill(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "dtype": "bf16",
         "data": "synthetic",
         "config": {"workload": f"chunked prefill mix: {meta.batch} requests, {n} query tokens, causal "
-                               f"({'boolean custom mask' if mask is not None else 'native causal flag'}), "
+                               f"({'BRLE mask' if args.prefill_brle else 'boolean custom mask' if mask is not None else 'native causal flag'}), "
                                "32q/8kv heads, D128, bf16, page16", "pool_pages": num_pages},
         "clocks": sampler.summary(),
         "roofline": {"bound": "tensor", "kernel": "prefill_tc2_kernel (two query heads per CTA)", "achieved": tf, "peak": peak,
                      "unit": "TFLOP/s", "frac": tf / peak, "peak_source": peak_kind, "traffic": None,
                      "flops_causal_exact": flops, "ms_per_launch": attn_ms},
+        "mask_plan": mask_plan,
         "device_error_word": ops.device_error(dev),
     }
     print(json.dumps(line), flush=True)
@@ -556,6 +603,9 @@ def run_decode70b(args):
         return parallel.allgather_heads(o, gather_buffer=gather) if world > 1 else o
 
     def barrier():
+        # device idle first: the barrier's own NCCL kernel would otherwise run (and spin) beside the
+        # timed kernels and take an SM away from a grid that fills all of them
+        torch.cuda.synchronize(dev)
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize(dev)
@@ -938,6 +988,8 @@ def main():
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
+    ap.add_argument("--prefill-brle", action="store_true",
+                    help="prefill: pass the mask as BRLE runs (wire form), expanded to bits on the device")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

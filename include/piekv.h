@@ -215,14 +215,32 @@ int piekv_prefill_plan(const int32_t *qo_indptr, const int32_t *kv_indptr,
                        int32_t page_size, int32_t num_pages, void *workspace,
                        int64_t workspace_bytes, int32_t *err, void *stream);
 
+/* The same plan built from the wire form of the mask: per query token a list of run lengths that
+ * alternate attend / skip starting with attend (BRLE, sdk/rust/inferlet/src/brle.rs:4-21), runs of
+ * token i at brle_runs[brle_indptr[i] .. brle_indptr[i+1]), and only the first position + 1 entries
+ * of a row can be set (position = kv_len_b - qo_len_b + index of the token in its request).  The
+ * bit-packed mask is produced on the device, so neither the host expansion to one byte per pair
+ * nor its upload happens.  `mask_bits` = sum over requests of qo_len_b * kv_len_b (sizes the
+ * packed mask; the same number piekv_prefill_workspace_bytes takes as mask_bytes).  Run the batch
+ * with piekv_prefill_run(custom_mask = NULL, mask_bytes = mask_bits, planned = 2).  Needs the
+ * tensor-core path (fp16 / bf16, head_dim 128, page size 16).
+ * Replaces Batch.__init__'s decode_brle_batch (pie/src/pie_worker/batching.py:113-135,337-389)
+ * followed by the `custom_mask` upload (batching.py:196-239). */
+int piekv_prefill_plan_brle(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                            const int32_t *kv_last_page_len, const uint32_t *brle_runs,
+                            const int32_t *brle_indptr, int64_t mask_bits, int32_t batch,
+                            int32_t nnz, int32_t page_size, int32_t num_pages, void *workspace,
+                            int64_t workspace_bytes, int32_t *err, void *stream);
+
 /* Packed variable-length attention over paged K/V: query token j of request b (rows
  * qo_indptr[b]..qo_indptr[b+1]) attends to cached token t of that request when
  *   custom_mask != NULL:  custom_mask[off_b + j*kv_len_b + t] != 0,
  *                         off_b = sum_{b'<b} qo_len_b' * kv_len_b'
  *                         (flat bool layout of pie/src/pie_worker/batching.py:113-135);
  *   otherwise:            !causal || t <= kv_len_b - qo_len_b + j.
- * `planned` != 0: piekv_prefill_plan was already called on this workspace with the same
- * metadata and mask (one plan, many layers); 0: the plan is built inside this call.
+ * `planned` 1: piekv_prefill_plan was already called on this workspace with the same metadata
+ * and mask (one plan, many layers); 2: piekv_prefill_plan_brle was (the mask lives in the
+ * workspace only; custom_mask is ignored); 0: the plan is built inside this call.
  * Replaces BatchPrefillWithPagedKVCacheWrapper.run (llama3.py:307-309,689). */
 int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
                       void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,

@@ -85,6 +85,10 @@ SIGNATURES = {
         C.c_int,
         [_p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _p, _i64, _p, _p],
     ),
+    "piekv_prefill_plan_brle": (
+        C.c_int,
+        [_p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _p, _i64, _p, _p],
+    ),
     "piekv_prefill_run": (
         C.c_int,
         [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,

@@ -74,8 +74,10 @@ class Batch:
         self.single_token_mode = bool(args.get("single_token_mode", False))
         self.total_tokens = int(len(self.token_ids))
 
-        runs = _u32(args["flattened_masks"]).astype(np.int64)
-        mask_indptr = _u32(args["mask_indptr"]).astype(np.int64)
+        self.flattened_masks = _u32(args["flattened_masks"]).astype(np.uint32)
+        self.mask_indptr = _u32(args["mask_indptr"]).astype(np.int32)
+        runs = self.flattened_masks.astype(np.int64)
+        mask_indptr = self.mask_indptr.astype(np.int64)
         counts = np.diff(self.qo_indptr).astype(np.int64)
         npages = np.diff(self.kv_page_indptr).astype(np.int64)
         last = self.kv_last_page_lens.astype(np.int64)
@@ -87,7 +89,17 @@ class Batch:
             + np.repeat(ctx, counts)
         acc = np.zeros(self.total_tokens + 1, dtype=np.int64)
         np.cumsum(all_seq, out=acc[1:])
+        self.mask_bits = int(acc[-1])
         self.attention_masks = decode_brle_batch(runs, mask_indptr, pos, acc)
+
+    def brle_inputs(self, device):
+        """The mask in its wire form for `BatchPrefillWithPagedKVCacheWrapper.plan(brle_mask=...)`:
+        (run lengths, per-token offsets into them, number of (query, key) pairs).  A few bytes per query
+        token instead of one byte per pair; the library expands it to bits on the device."""
+        dev = torch.device(device)
+        # int32 view of the unsigned words: the kernel reads them as unsigned again
+        runs = torch.from_numpy(np.ascontiguousarray(self.flattened_masks).view(np.int32).copy())
+        return (runs.to(dev), torch.as_tensor(self.mask_indptr, dtype=torch.int32, device=dev), self.mask_bits)
 
     def get_model_inputs(self, device) -> Dict[str, Any]:
         """Device tensors in the form the operators take (pie/src/pie_worker/batching.py:196-239)."""

@@ -33,8 +33,10 @@ int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t wor
 // mask) into the workspace; launch_prefill_tc consumes that plan.
 bool prefill_tc_supported(const AttnArgs &a, int dtype);
 int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t mask_bytes);
+// brle_runs / brle_indptr (both or neither): build the packed mask from per-token run lengths
+// instead of a.mask
 int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
-                        cudaStream_t st);
+                        cudaStream_t st, const uint32_t *brle_runs = nullptr, const int32_t *brle_indptr = nullptr);
 int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
                       cudaStream_t st);
 

@@ -199,6 +199,21 @@ extern "C" int piekv_prefill_plan(const int32_t *qo_indptr, const int32_t *kv_in
   return launch_prefill_plan(a, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
+extern "C" int piekv_prefill_plan_brle(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                                       const int32_t *kv_last_page_len, const uint32_t *brle_runs,
+                                       const int32_t *brle_indptr, int64_t mask_bits, int32_t batch, int32_t nnz,
+                                       int32_t page_size, int32_t num_pages, void *workspace, int64_t workspace_bytes,
+                                       int32_t *err, void *stream) {
+  PIEKV_REQUIRE(batch >= 0 && nnz >= 0 && page_size > 0 && num_pages > 0 && mask_bits >= 0, "prefill_plan_brle: bad sizes");
+  PIEKV_REQUIRE(page_size == 16, "prefill_plan_brle: page size %d (the tensor-core path needs 16)", page_size);
+  PIEKV_REQUIRE(nnz == 0 || (qo_indptr && kv_indptr && kv_last_page_len && brle_indptr),
+                "prefill_plan_brle: null pointer");
+  AttnArgs a{};
+  fill_prefill_args(a, nullptr, 0, 0, nullptr, nullptr, nullptr, qo_indptr, kv_indptr, nullptr, kv_last_page_len,
+                    nullptr, 0, batch, nnz, 1, 1, 128, page_size, num_pages, 1.f, err);
+  return launch_prefill_plan(a, mask_bits, workspace, workspace_bytes, (cudaStream_t)stream, brle_runs, brle_indptr);
+}
+
 extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
                                  float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
                                  const int32_t *kv_indices, const int32_t *kv_last_page_len,
@@ -213,6 +228,12 @@ extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_st
   if (int rc = check_common(a, dtype, "prefill_run")) return rc;
   PIEKV_REQUIRE(nnz == 0 || qo_indptr != nullptr, "prefill_run: qo_indptr is null");
   if (batch == 0 || nnz == 0) return 0;
+  if (planned == 2) {
+    PIEKV_REQUIRE(prefill_tc_supported(a, dtype),
+                  "prefill_run: a BRLE plan needs the tensor-core path (fp16/bf16, head_dim 128, page size 16)");
+    a.mask = reinterpret_cast<const uint8_t *>(workspace);  // marks "masked"; the packed form is what is read
+    a.causal = 0;
+  }
   if (prefill_tc_supported(a, dtype)) {
     if (!planned) {
       if (int rc = launch_prefill_plan(a, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream)) return rc;

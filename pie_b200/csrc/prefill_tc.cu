@@ -173,6 +173,83 @@ __global__ void prefill_pack_mask_kernel(const uint8_t *__restrict__ mask, const
   }
 }
 
+// BRLE runs -> the same 128-bit groups and "any" bits, without the flat boolean mask ever existing.
+// Semantics of the reference's host expansion (pie/src/pie_worker/batching.py:337-389): the runs of a
+// query token alternate attend / skip starting with attend, lie end to end from kv position 0, and
+// only the first position + 1 entries of the row can be set, position = kv_len - qo_len + index of
+// the token in its request.  One warp per query row: the row is cleared, then every attend run ORs
+// its clipped interval into the words it touches (word w belongs to lane w % 32, so the read-modify-
+// writes of a row never collide), then the groups are summarised.
+__global__ void prefill_brle_mask_kernel(const uint32_t *__restrict__ runs, const int32_t *__restrict__ run_indptr,
+                                         const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
+                                         const int32_t *__restrict__ last, int batch, int nnz, int page_size,
+                                         const int32_t *__restrict__ tile_base, const long long *__restrict__ poff,
+                                         uint4 *packed, uint32_t *summary, int sw) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= nnz) return;
+  int lo = 0, hi = batch;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (qo_indptr[mid + 1] > i)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  const int b = lo < batch ? lo : batch - 1;
+  const int j = i - qo_indptr[b];
+  const int qo = qo_indptr[b + 1] - qo_indptr[b];
+  const int kv = kv_len_of(kv_indptr, last, b, page_size);
+  const int groups = (kv + 127) / 128;
+  const int words = groups * 4;
+  const long long valid = max(0, min(kv, kv - qo + j + 1));
+  uint32_t *dst = reinterpret_cast<uint32_t *>(packed + poff[b] + (long long)j * groups);
+  for (int w = lane; w < words; w += 32) dst[w] = 0;
+  const int r0 = run_indptr[i], r1 = run_indptr[i + 1];
+  long long carry = 0;  // kv position where the next run starts
+  for (int base = r0; base < r1 && carry < valid; base += 32) {
+    const int r = base + lane;
+    const long long len = r < r1 ? (long long)runs[r] : 0;
+    long long end = len;  // inclusive scan of the run lengths of this chunk
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const long long up = __shfl_up_sync(0xffffffffu, end, o);
+      if (lane >= o) end += up;
+    }
+    end += carry;
+    const long long start = end - len;
+    const int n_here = min(32, r1 - base);
+    for (int k = 0; k < n_here; k += 2) {  // attend runs: even index within the token (r0 is index 0)
+      const int src_lane = k;  // chunks start 32 runs apart, so even lanes hold the even-numbered runs
+      long long s = __shfl_sync(0xffffffffu, start, src_lane);
+      long long e = __shfl_sync(0xffffffffu, end, src_lane);
+      if (s >= valid) break;
+      e = min(e, valid);
+      if (e <= s) continue;
+      const int w_first = (int)(s >> 5), w_last = (int)((e - 1) >> 5);
+      // lane's first owned word at or after w_first
+      int w = w_first + ((lane - w_first) & 31);
+      for (; w <= w_last; w += 32) {
+        const long long wb = (long long)w << 5;
+        const uint32_t lo_mask = s > wb ? 0xffffffffu << (int)(s - wb) : 0xffffffffu;
+        const uint32_t hi_mask = e < wb + 32 ? 0xffffffffu >> (int)(wb + 32 - e) : 0xffffffffu;
+        dst[w] |= lo_mask & hi_mask;
+      }
+    }
+    carry = __shfl_sync(0xffffffffu, end, 31);
+  }
+  __syncwarp();
+  uint32_t *srow = summary + (size_t)(tile_base[b] + j / kBM) * sw;
+  for (int g = lane; g < groups; g += 32) {
+    const uint4 v = reinterpret_cast<const uint4 *>(dst)[g];
+    if ((v.x | v.y | v.z | v.w) != 0) {
+      uint32_t *sp = srow + (g >> 5);
+      const uint32_t bit = 1u << (g & 31);
+      if ((*(volatile uint32_t *)sp & bit) == 0) atomicOr(sp, bit);
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // work list: one entry per (request, 128-row tile), ordered by decreasing number of kv tiles
 // ------------------------------------------------------------------------------------------------
@@ -638,26 +715,34 @@ int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t ma
 // Build the plan of a batch in the workspace: per-request offsets, the bit-packed mask with its
 // tile summary (custom mask only) and the work list.  Stream-ordered, no host synchronisation.
 int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
-                        cudaStream_t st) {
+                        cudaStream_t st, const uint32_t *brle_runs, const int32_t *brle_indptr) {
   if (a.nnz == 0 || a.batch == 0) return 0;
-  const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, a.mask ? mask_bytes : 0);
+  const bool brle = brle_runs != nullptr || brle_indptr != nullptr;
+  const bool masked = a.mask != nullptr || brle;
+  const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, masked ? mask_bytes : 0);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= v.bytes, "prefill: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)v.bytes);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "prefill: workspace must be 256-byte aligned");
   prefill_scan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size,
                                           v.tile_base, v.poff, v.moff);
   PIEKV_LAUNCH_CHECK("prefill_scan_kernel");
-  if (a.mask != nullptr) {
+  if (masked) {
     cudaError_t e = cudaMemsetAsync(v.summary, 0, (size_t)v.max_tiles * v.sw * 4, st);
     if (e != cudaSuccess) return cuda_status(e, "prefill: cudaMemsetAsync");
+  }
+  if (brle) {
+    prefill_brle_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(brle_runs, brle_indptr, a.qo_indptr, a.kv_indptr,
+                                                               a.kv_last_page_len, a.batch, a.nnz, a.page_size,
+                                                               v.tile_base, v.poff, v.packed, v.summary, v.sw);
+    PIEKV_LAUNCH_CHECK("prefill_brle_mask_kernel");
+  } else if (a.mask != nullptr) {
     prefill_pack_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(a.mask, a.qo_indptr, a.kv_indptr, a.kv_last_page_len,
                                                                a.batch, a.nnz, a.page_size, v.tile_base, v.poff, v.moff,
                                                                v.packed, v.summary, v.sw);
     PIEKV_LAUNCH_CHECK("prefill_pack_mask_kernel");
   }
   prefill_plan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size, a.causal,
-                                          v.tile_base, v.summary, v.sw, a.mask != nullptr ? 1 : 0, v.tiles, v.ntiles,
-                                          v.max_tiles);
+                                          v.tile_base, v.summary, v.sw, masked ? 1 : 0, v.tiles, v.ntiles, v.max_tiles);
   PIEKV_LAUNCH_CHECK("prefill_plan_kernel");
   return 0;
 }

@@ -509,7 +509,11 @@ class BatchPrefillWithPagedKVCacheWrapper:
 
     Reference construction and use: pie/src/pie_worker/model/llama3.py:307-309, plan 779-791,
     run 689.  `custom_mask` is the flat boolean mask of pie/src/pie_worker/batching.py:113-135:
-    for every query token a row of kv_len_b entries."""
+    for every query token a row of kv_len_b entries.
+
+    Extension: `plan(..., brle_mask=(runs, indptr, mask_bits))` takes the mask in its wire form (per
+    query token a list of alternating attend / skip run lengths, `pie_b200.batching.Batch.brle_inputs`)
+    and builds the bit-packed mask on the device; the flat boolean mask is never materialised."""
 
     def __init__(self, float_workspace_buffer: torch.Tensor, kv_layout: str = "NHD", **_ignored) -> None:
         if kv_layout != "NHD":
@@ -526,7 +530,7 @@ class BatchPrefillWithPagedKVCacheWrapper:
              packed_custom_mask: Optional[torch.Tensor] = None, causal: bool = False,
              pos_encoding_mode: str = "NONE", window_left: int = -1, logits_soft_cap: Optional[float] = None,
              sm_scale: Optional[float] = None, q_data_type: torch.dtype = torch.float16,
-             kv_data_type: Optional[torch.dtype] = None, **_ignored) -> None:
+             kv_data_type: Optional[torch.dtype] = None, brle_mask=None, **_ignored) -> None:
         _require_i32(qo_indptr, "qo_indptr")
         _require_i32(paged_kv_indptr, "paged_kv_indptr")
         _require_i32(paged_kv_indices, "paged_kv_indices")
@@ -552,12 +556,27 @@ class BatchPrefillWithPagedKVCacheWrapper:
                 raise ValueError("custom_mask must be a contiguous bool (or uint8) tensor")
             mask = custom_mask.view(torch.uint8) if custom_mask.dtype == torch.bool else custom_mask
             causal = False  # the mask alone decides, as in the reference
+        brle = None
+        if brle_mask is not None:
+            if custom_mask is not None:
+                raise ValueError("pass either custom_mask or brle_mask, not both")
+            runs, run_indptr, mask_bits = brle_mask
+            _require_cuda(runs, "brle runs")
+            _require_i32(run_indptr, "brle indptr")
+            if runs.dtype not in (torch.int32, torch.uint32) or not runs.is_contiguous():
+                raise ValueError("brle runs must be a contiguous int32 / uint32 tensor")
+            if page_size != 16 or head_dim_qk != 128 or q_data_type not in (torch.float16, torch.bfloat16):
+                raise ValueError("brle_mask needs the tensor-core prefill path (fp16/bf16, head_dim 128, page size 16)")
+            if run_indptr.shape[0] < 1:
+                raise ValueError("brle indptr must have nnz + 1 entries")
+            brle = (runs, run_indptr, int(mask_bits))
+            causal = False
         batch = qo_indptr.shape[0] - 1
         self._plan = dict(qo_indptr=qo_indptr, indptr=paged_kv_indptr, indices=paged_kv_indices,
                           last_page_len=paged_kv_last_page_len, batch=batch, hq=int(num_qo_heads),
                           hkv=int(num_kv_heads), d=int(head_dim_qk), page_size=int(page_size), mask=mask,
-                          mask_bytes=int(mask.numel()) if mask is not None else 0,
-                          causal=bool(causal), dtype=q_data_type, planned_for=None,
+                          mask_bytes=int(mask.numel()) if mask is not None else (brle[2] if brle else 0),
+                          brle=brle, causal=bool(causal), dtype=q_data_type, planned_for=None,
                           sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim_qk))
 
     def _device_plan(self, n: int, num_pages: int) -> None:
@@ -572,6 +591,17 @@ class BatchPrefillWithPagedKVCacheWrapper:
         if ws.numel() < need:
             raise ValueError(f"workspace_buffer too small: {ws.numel()} < {need} bytes")
         dev = pl["qo_indptr"].device
+        if pl["brle"] is not None:
+            runs, run_indptr, mask_bits = pl["brle"]
+            if run_indptr.shape[0] != n + 1:
+                raise ValueError(f"brle indptr has {run_indptr.shape[0]} entries for {n} query tokens")
+            check(lib.piekv_prefill_plan_brle(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
+                                              pl["last_page_len"].data_ptr(), runs.data_ptr(), run_indptr.data_ptr(),
+                                              mask_bits, pl["batch"], n, pl["page_size"], num_pages, ws.data_ptr(),
+                                              ws.numel(), _err_word(dev).data_ptr(), _stream(dev)),
+                  "BatchPrefill.plan (BRLE)")
+            pl["planned_for"] = key
+            return
         check(lib.piekv_prefill_plan(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
                                      pl["last_page_len"].data_ptr(),
                                      pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
@@ -607,7 +637,8 @@ class BatchPrefillWithPagedKVCacheWrapper:
                                     pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
                                     pl["last_page_len"].data_ptr(),
                                     pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
-                                    1 if pl["causal"] else 0, 1, pl["batch"], n, pl["hq"], pl["hkv"], pl["d"],
+                                    1 if pl["causal"] else 0, 2 if pl["brle"] is not None else 1, pl["batch"], n,
+                                    pl["hq"], pl["hkv"], pl["d"],
                                     pl["page_size"], num_pages, _dtype_code(q.dtype, "prefill run"),
                                     pl["sm_scale"], ws.data_ptr(), ws.numel(), _err_word(q.device).data_ptr(),
                                     _stream(q.device)), "BatchPrefill.run")
