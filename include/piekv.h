@@ -251,6 +251,55 @@ int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, con
                       int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
                       int32_t *err, void *stream);
 
+/* ---- head-sharded decode over the GPUs of one node: results stored straight to every GPU ----
+ *
+ * The reference's tensor parallelism (llama3.py:607-610,963-965) gives every GPU Hkv/G kv heads and
+ * their query heads with identical page tables, and joins the GPUs with an NCCL collective per
+ * layer (all_reduce after o_proj, llama3.py:705-706).  On a path that ends at the attention output
+ * the join is an all-gather of [batch, Hq/G * D] slices.  These entry points remove the separate
+ * collective: the decode kernel stores its slice into the output buffer of every GPU over NVLink
+ * (plain peer stores from the same kernel that computes the rows) and, when its last row is out,
+ * raises this GPU's flag on every GPU; a consumer waits for all G flags (bounded) and reads the full
+ * rows locally.  One process per GPU; buffers are cudaMalloc'd here and mapped into the other
+ * processes with CUDA IPC handles that the host exchanges (e.g. torch.distributed
+ * all_gather_object).  No counterpart in the reference. */
+#define PIEKV_MAX_PEERS 8
+#define PIEKV_PEER_HANDLE_BYTES 64
+
+/* cudaMalloc `bytes` (zero-filled) on the current device and export its IPC handle (64 bytes). */
+int piekv_peer_alloc(int64_t bytes, void **ptr, void *handle);
+/* Map another process's buffer (handle from its piekv_peer_alloc); enables peer access lazily. */
+int piekv_peer_open(const void *handle, void **ptr);
+int piekv_peer_close(void *ptr); /* unmap a pointer from piekv_peer_open   */
+int piekv_peer_free(void *ptr);  /* free a pointer from piekv_peer_alloc    */
+
+typedef struct piekv_peer_outputs {
+  void *out[PIEKV_MAX_PEERS];      /* out[r]: this step's output rows [batch, row_heads, head_dim] on rank r */
+  int32_t *flags[PIEKV_MAX_PEERS]; /* flags[r]: int32[world] on rank r; word i is raised by rank i           */
+  int32_t world, rank;
+  int32_t row_heads;               /* query heads per output row (>= world * num_qo_heads of the call)       */
+  int32_t step;                    /* published in the flags; must grow from call to call                     */
+} piekv_peer_outputs;
+
+/* piekv_decode_step_fused with the results of this rank's heads written to columns
+ * [rank * num_qo_heads, (rank + 1) * num_qo_heads) of out[r] for every r, then flags[r][rank] = step.
+ * Use two alternating output buffers: a rank may start step s + 1 while another still reads step s. */
+int piekv_decode_step_fused_peer(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                 int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                 int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids,
+                                 void *pool, const piekv_peer_outputs *peers,
+                                 const int32_t *kv_indptr, const int32_t *kv_indices,
+                                 const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                 int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
+                                 int32_t num_pages, int32_t dtype, const piekv_rope_params *rope,
+                                 float sm_scale, void *workspace, int64_t workspace_bytes, int32_t *err,
+                                 void *stream);
+
+/* Stream-ordered wait until flags[0..world) (this rank's own flag array) have all reached `step`;
+ * gives up after 2 s with PIEKV_ERR_WAIT_TIMEOUT in the error word.  Work queued behind it on the
+ * stream sees every rank's rows of that step. */
+int piekv_peer_wait(const int32_t *flags, int32_t world, int32_t step, int32_t *err, void *stream);
+
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */
 
 /* For every pair j and every layer l: pool_l[dst[j], :, :valid_j] = pool_l[src[j], :, :valid_j]

@@ -14,6 +14,7 @@ PIEKV_F32, PIEKV_F16, PIEKV_BF16 = 0, 1, 2
 ROPE_NONE, ROPE_PLAIN, ROPE_LLAMA31, ROPE_TABLE = 0, 1, 2, 3
 OPT_PDL = 0
 
+PIEKV_ERR_WAIT_TIMEOUT = 5
 ERR_NAMES = {
     0: "ok",
     1: "batch index out of range",
@@ -39,6 +40,23 @@ class RopeParams(C.Structure):
         ("old_context_len", C.c_float),
         ("table_len", C.c_int32),
         ("cos_sin_table", C.c_void_p),
+    ]
+
+
+MAX_PEERS = 8
+PEER_HANDLE_BYTES = 64
+
+
+class PeerOutputsC(C.Structure):
+    """Mirror of `piekv_peer_outputs`."""
+
+    _fields_ = [
+        ("out", C.c_void_p * MAX_PEERS),
+        ("flags", C.c_void_p * MAX_PEERS),
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("row_heads", C.c_int32),
+        ("step", C.c_int32),
     ]
 
 
@@ -80,6 +98,16 @@ SIGNATURES = {
         [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
          _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
     ),
+    "piekv_peer_alloc": (C.c_int, [_i64, C.POINTER(C.c_void_p), _p]),
+    "piekv_peer_open": (C.c_int, [_p, C.POINTER(C.c_void_p)]),
+    "piekv_peer_close": (C.c_int, [_p]),
+    "piekv_peer_free": (C.c_int, [_p]),
+    "piekv_decode_step_fused_peer": (
+        C.c_int,
+        [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32,
+         _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
+    ),
+    "piekv_peer_wait": (C.c_int, [_p, _i32, _i32, _p, _p]),
     "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32, _i64]),
     "piekv_prefill_plan": (
         C.c_int,

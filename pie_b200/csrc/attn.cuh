@@ -22,6 +22,18 @@ struct AttnArgs {
   int32_t *err;
 };
 
+// Destinations of a head-sharded decode step on several GPUs: the same output buffer on every GPU
+// (own GPU included), mapped into this process; `flag[d]` is this GPU's word in GPU d's flag array.
+struct PeerOut {
+  void *dst[8];
+  int *flag[8];
+  int n;          // 0: not used
+  int row_heads;  // query heads per output row at the destinations (all GPUs' heads)
+  int head_off;   // first head of this GPU inside a row
+  int step;       // value published in the flags when every result of the launch has been stored
+  int *done;      // device counter, zero between launches
+};
+
 // any dtype / shape
 int launch_attn_generic(const AttnArgs &a, int dtype, cudaStream_t st);
 

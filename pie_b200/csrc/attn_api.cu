@@ -9,7 +9,7 @@ bool decode_fused_tma_supported(const AttnArgs &a, int dtype, const void *k, con
                                 int64_t k_sh, int64_t v_sn, int64_t v_sh);
 int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn, int64_t k_sh,
                             int64_t v_sn, int64_t v_sh, const int32_t *pos_ids, const RopeDev &rope, void *workspace,
-                            int64_t workspace_bytes, cudaStream_t st);
+                            int64_t workspace_bytes, cudaStream_t st, const PeerOut *peer = nullptr);
 int launch_decode_append_general(void *q_out, const void *q, const void *k, const void *v, int64_t q_sn, int64_t q_sh,
                                  int64_t k_sn, int64_t k_sh, int64_t v_sn, int64_t v_sh, const int32_t *pos_ids,
                                  int32_t *bi_scratch, int32_t *pos_scratch, void *pool, const int32_t *kv_indices,
@@ -86,14 +86,14 @@ extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_str
   return launch_attn_generic(a, dtype, (cudaStream_t)stream);
 }
 
-extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void *v, int64_t q_stride_n,
-                                       int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
-                                       int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
-                                       void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
-                                       const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
-                                       int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
-                                       int32_t dtype, const piekv_rope_params *rope, float sm_scale, void *workspace,
-                                       int64_t workspace_bytes, int32_t *err, void *stream) {
+static int decode_step_fused_impl(const void *q, const void *k, const void *v, int64_t q_stride_n, int64_t q_stride_h,
+                                  int64_t k_stride_n, int64_t k_stride_h, int64_t v_stride_n, int64_t v_stride_h,
+                                  const int32_t *pos_ids, void *pool, void *out, float *lse, const int32_t *kv_indptr,
+                                  const int32_t *kv_indices, const int32_t *kv_last_page_len, int32_t batch,
+                                  int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
+                                  int32_t num_pages, int32_t dtype, const piekv_rope_params *rope, float sm_scale,
+                                  void *workspace, int64_t workspace_bytes, int32_t *err, void *stream,
+                                  const piekv::PeerOut *peer) {
   AttnArgs a{};
   a.q = q;
   a.q_sn = q_stride_n;
@@ -124,7 +124,9 @@ extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void 
   cudaStream_t st = (cudaStream_t)stream;
   if (decode_fused_tma_supported(a, dtype, k, v, k_stride_n, k_stride_h, v_stride_n, v_stride_h))
     return launch_decode_fused_tma(a, dtype, k, v, k_stride_n, k_stride_h, v_stride_n, v_stride_h, pos_ids, rp,
-                                   workspace, workspace_bytes, st);
+                                   workspace, workspace_bytes, st, peer);
+  PIEKV_REQUIRE(peer == nullptr, "decode_step_fused_peer: needs the tuned kernel (fp16/bf16, head_dim 128, page size 16, "
+                                 "1/2/4/8 kv heads, 16-byte aligned buffers)");
   // general path: metadata -> RoPE + append (rotated q into scratch) -> general attention
   const int64_t need = general_fused_bytes(batch, num_qo_heads, head_dim);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need,
@@ -147,6 +149,52 @@ extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void 
     a.q_sh = head_dim;
   }
   return launch_attn_generic(a, dtype, st);
+}
+
+extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                       int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                       int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
+                                       void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                       const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                       int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                                       int32_t dtype, const piekv_rope_params *rope, float sm_scale, void *workspace,
+                                       int64_t workspace_bytes, int32_t *err, void *stream) {
+  return decode_step_fused_impl(q, k, v, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h,
+                                pos_ids, pool, out, lse, kv_indptr, kv_indices, kv_last_page_len, batch, num_qo_heads,
+                                num_kv_heads, head_dim, page_size, num_pages, dtype, rope, sm_scale, workspace,
+                                workspace_bytes, err, stream, nullptr);
+}
+
+extern "C" int piekv_decode_step_fused_peer(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                            int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                            int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids,
+                                            void *pool, const piekv_peer_outputs *peers, const int32_t *kv_indptr,
+                                            const int32_t *kv_indices, const int32_t *kv_last_page_len, int32_t batch,
+                                            int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
+                                            int32_t page_size, int32_t num_pages, int32_t dtype,
+                                            const piekv_rope_params *rope, float sm_scale, void *workspace,
+                                            int64_t workspace_bytes, int32_t *err, void *stream) {
+  PIEKV_REQUIRE(peers != nullptr, "decode_step_fused_peer: null peer description");
+  PIEKV_REQUIRE(peers->world >= 1 && peers->world <= PIEKV_MAX_PEERS && peers->rank >= 0 && peers->rank < peers->world,
+                "decode_step_fused_peer: world %d / rank %d", peers->world, peers->rank);
+  PIEKV_REQUIRE(peers->row_heads >= num_qo_heads * peers->world, "decode_step_fused_peer: rows of %d heads cannot hold %d x %d",
+                peers->row_heads, peers->world, num_qo_heads);
+  piekv::PeerOut po{};
+  po.n = peers->world;
+  po.row_heads = peers->row_heads;
+  po.head_off = peers->rank * num_qo_heads;
+  po.step = peers->step;
+  for (int d = 0; d < peers->world; ++d) {
+    PIEKV_REQUIRE(peers->out[d] != nullptr && peers->flags[d] != nullptr, "decode_step_fused_peer: null pointer for rank %d", d);
+    PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(peers->out[d]) & 15) == 0, "decode_step_fused_peer: output of rank %d not 16-byte aligned", d);
+    po.dst[d] = peers->out[d];
+    po.flag[d] = peers->flags[d] + peers->rank;
+  }
+  // the tuned kernel checks a.out for alignment only; results go to the peers' buffers
+  return decode_step_fused_impl(q, k, v, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h,
+                                pos_ids, pool, peers->out[peers->rank], nullptr, kv_indptr, kv_indices,
+                                kv_last_page_len, batch, num_qo_heads, num_kv_heads, head_dim, page_size, num_pages,
+                                dtype, rope, sm_scale, workspace, workspace_bytes, err, stream, &po);
 }
 
 static void fill_prefill_args(AttnArgs &a, const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,

@@ -1,6 +1,7 @@
 // Shared helpers for the libpiekv.so translation units: status handling, the device
 // error word, element-type traits and small PTX wrappers (mbarrier, TMA, ldmatrix, mma).
 #pragma once
+#include <string.h>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -43,6 +44,7 @@ enum KernelId : int {
   KID_ATTN_GENERIC = 5,
   KID_DECODE = 6,
   KID_PREFILL = 7,
+  KID_PEER = 8,
 };
 
 // ---- device side -------------------------------------------------------------------

@@ -45,6 +45,7 @@ struct DecodeParams {
   float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
   int *counters;    // [batch], zero between launches
   int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets
+  PeerOut peer;     // n == 0: results go to a.out only
 };
 
 // Extra inputs of the fused step (RoPE + append + attention in one launch): the new token's
@@ -202,18 +203,49 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int quad = lane >> 2;    // MMA row (and row + 8)
   const int qlane = lane & 3;
   const float scale_log2 = a.sm_scale * 1.4426950408889634f;
-  T *out = reinterpret_cast<T *>(a.out);
+  // Where results go: a.out, or (head-sharded run over several GPUs) the same rows of an output
+  // buffer on every GPU, this GPU's heads at column head_off of rows that hold row_heads heads.
+  const int n_dst = p.peer.n > 0 ? p.peer.n : 1;
+  const int row_heads = p.peer.n > 0 ? p.peer.row_heads : a.hq;
+  const int head_off = p.peer.n > 0 ? p.peer.head_off : 0;
+  auto dst_row = [&](int d, int b_, int qh) -> T * {
+    T *base = reinterpret_cast<T *>(p.peer.n > 0 ? p.peer.dst[d] : a.out);
+    return base + ((size_t)b_ * row_heads + head_off + qh) * kDim;
+  };
+  // Every CTA passes here exactly once after its last result store.  The CTA that arrives last
+  // publishes this step's number in every GPU's flag array: all stores of this launch, fenced at
+  // system scope by their threads, are ordered before it.
+  auto finish = [&]() {
+    if (p.peer.n == 0) return;
+    __threadfence_system();
+    consumer_bar_sync();
+    if (tid == 0) {
+      __threadfence_system();
+      const int old = atomicAdd(p.peer.done, 1);
+      if (old == (int)gridDim.x - 1) {
+        atomicExch(p.peer.done, 0);  // ready for the next launch
+        __threadfence_system();
+        for (int d = 0; d < p.peer.n; ++d)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(p.peer.step) : "memory");
+      }
+    }
+  };
 
   // requests without any page: softmax over nothing -> zeros
   for (int b = c; b < B; b += gridDim.x) {
     if (ip[b + 1] == ip[b]) {
-      for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32)
-        out[(size_t)b * a.hq * kDim + x] = Elem<T>::from_f32(0.f);
+      for (int d = 0; d < n_dst; ++d) {
+        T *row = dst_row(d, b, 0);
+        for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32) row[x] = Elem<T>::from_f32(0.f);
+      }
       if (a.lse != nullptr)
         for (int x = tid; x < a.hq; x += kConsumerWarps * 32) a.lse[(size_t)b * a.hq + x] = -INFINITY;
     }
   }
-  if (lo >= hi) return;
+  if (lo >= hi) {
+    finish();
+    return;
+  }
 
   uint32_t qa[8][4];
   float o[16][4];
@@ -497,10 +529,12 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int qh = h * group + row;
           const float lsum = half ? ls1 : ls0;
           const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-          uint32_t *orow = reinterpret_cast<uint32_t *>(out + ((size_t)b * a.hq + qh) * kDim);
+          for (int d = 0; d < n_dst; ++d) {
+            uint32_t *orow = reinterpret_cast<uint32_t *>(dst_row(d, b, qh));
 #pragma unroll
-          for (int nt = 0; nt < 16; ++nt)
-            orow[nt * 4 + qlane] = pack2<T>(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+            for (int nt = 0; nt < 16; ++nt)
+              orow[nt * 4 + qlane] = pack2<T>(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+          }
           if (a.lse != nullptr && qlane == 0) {
             const float mm = half ? m1 : m0;
             a.lse[(size_t)b * a.hq + qh] = lsum > 0.f ? (mm + log2f(lsum)) * 0.6931471805599453f : -INFINITY;
@@ -563,12 +597,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint2 pk;
       pk.x = pack2<T>(acc.x * inv, acc.y * inv);
       pk.y = pack2<T>(acc.z * inv, acc.w * inv);
-      *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
+      for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
       if (a.lse != nullptr && (tid & 31) == 0)
         a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
     }
     if (tid == 0) p.counters[b] = 0;  // leave the counter ready for the next launch
   }
+  finish();
 }
 
 template <typename T, int HKV, bool FUSED>
@@ -647,6 +682,7 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
                 (long long)workspace_bytes, (long long)need);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
   p->a = a;
+  p->peer = PeerOut{};
   p->pdl = get_option(PIEKV_OPT_PDL);
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p->counters = reinterpret_cast<int *>(ws);
@@ -677,11 +713,16 @@ bool decode_fused_tma_supported(const AttnArgs &a, int dtype, const void *k, con
 
 int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const void *v, int64_t k_sn, int64_t k_sh,
                             int64_t v_sn, int64_t v_sh, const int32_t *pos_ids, const RopeDev &rope, void *workspace,
-                            int64_t workspace_bytes, cudaStream_t st) {
+                            int64_t workspace_bytes, cudaStream_t st, const PeerOut *peer) {
   if (a.batch == 0) return 0;
   DecodeParams p;
   CUtensorMap tm;
   if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
+  if (peer != nullptr && peer->n > 0) {
+    PIEKV_REQUIRE(a.batch < kMaxBatch, "decode (peer outputs): batch %d too large", a.batch);
+    p.peer = *peer;
+    p.peer.done = p.counters + (kMaxBatch - 1);  // last word of the counter block, never a request's
+  }
   FusedArgs f;
   f.k_new = k;
   f.v_new = v;

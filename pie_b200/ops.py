@@ -503,6 +503,45 @@ class BatchDecodeWithPagedKVCacheWrapper:
               "BatchDecode.run_fused")
         return (out, lse) if return_lse else out
 
+    def run_fused_peer(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
+                       paged_kv_cache: torch.Tensor, peers, rope: Optional["RopeConfig"] = None) -> torch.Tensor:
+        """`run_fused` for head-sharded ranks (the reference's tensor parallelism,
+        pie/src/pie_worker/model/llama3.py:607-610): this rank's heads are stored into the output rows of
+        every rank by the kernel itself (`peers`: a `pie_b200.parallel.PeerOutputs`), the wait for the
+        other ranks' rows is queued on the stream, and the full [batch, all heads, head_dim] tensor of
+        this rank is returned.  Takes the place of attention followed by an NCCL collective."""
+        if self._plan is None:
+            raise RuntimeError("Must call plan() before run()")
+        pl = self._plan
+        for t, name in ((q, "q"), (k, "k"), (v, "v")):
+            _require_cuda(t, name)
+        _require_i32(pos_ids, "pos_ids")
+        num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
+        qs, ks, vs = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
+        b = pl["batch"]
+        if tuple(q.shape) != (b, pl["hq"], pl["d"]) or tuple(k.shape) != (b, pl["hkv"], pl["d"]) \
+                or tuple(v.shape) != tuple(k.shape) or pos_ids.shape[0] < b:
+            raise ValueError(f"q {tuple(q.shape)} / k {tuple(k.shape)} / v {tuple(v.shape)} differ from the plan")
+        if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
+            raise ValueError("paged_kv_cache shape differs from the plan")
+        if not (q.dtype == k.dtype == v.dtype == paged_kv_cache.dtype == peers.dtype):
+            raise ValueError("q, k, v, the cache and the peer buffers must share one dtype")
+        if b > peers.batch_max or d != peers.head_dim or pl["hq"] * peers.world > peers.row_heads:
+            raise ValueError("peer buffers are too small for this plan")
+        rp = (rope if rope is not None else RopeConfig()).to_c(d)
+        ws = self.workspace_buffer
+        desc = peers.begin_step()
+        check(lib.piekv_decode_step_fused_peer(q.data_ptr(), k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1],
+                                               vs[0], vs[1], pos_ids.data_ptr(), paged_kv_cache.data_ptr(),
+                                               C.byref(desc), pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
+                                               pl["last_page_len"].data_ptr(), b, pl["hq"], pl["hkv"], pl["d"],
+                                               pl["page_size"], num_pages, _dtype_code(q.dtype, "fused decode"),
+                                               C.byref(rp), pl["sm_scale"], ws.data_ptr(), ws.numel(),
+                                               _err_word(q.device).data_ptr(), _stream(q.device)),
+              "BatchDecode.run_fused_peer")
+        peers.wait()
+        return peers.full(b)
+
 
 class BatchPrefillWithPagedKVCacheWrapper:
     """Packed variable-length (prefill / chunked / multi-token) attention over paged K/V.

@@ -10,10 +10,13 @@ Two schemes, both taken from the reference:
   all-reduces after the row-parallel o_proj (llama3.py:698-706); on a path that ends at the attention
   output the equivalent exchange is an all-gather of the per-rank head slices.
 
-The collective is NCCL's (gloo on CPU for the tests); nothing here touches peer memory directly.
+`allgather_heads` uses NCCL's collective (gloo on CPU for the tests).  `PeerOutputs` is the other way
+to join head-sharded ranks: output buffers mapped into every process of the node, which the decode
+kernel itself fills on all GPUs with plain peer stores, so no collective follows the attention.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import List, Optional, Tuple
 
 import torch
@@ -53,3 +56,97 @@ def allgather_heads(out_local: torch.Tensor, group: Optional[dist.ProcessGroup] 
     except (RuntimeError, NotImplementedError):
         dist.all_gather([buf[g] for g in range(world)], src, group=group)
     return buf.permute(1, 0, 2, 3).reshape(n, world * hl, d)
+
+
+class _RawCuda:
+    """Lets torch view device memory that the library allocated (CUDA array interface)."""
+
+    def __init__(self, ptr: int, nbytes: int) -> None:
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def peer_layout(batch_max: int, row_heads: int, head_dim: int, elem_size: int) -> Tuple[int, int, int]:
+    """(offset of output buffer 0, offset of output buffer 1, total bytes) inside a rank's shared
+    allocation; the flag words sit at offset 0."""
+    buf = (batch_max * row_heads * head_dim * elem_size + 255) // 256 * 256
+    return 256, 256 + buf, 256 + 2 * buf
+
+
+class PeerOutputs:
+    """Head-sharded decode without a collective: every rank's decode kernel writes its heads into the
+    output rows of ALL ranks (NVLink peer stores) and raises a flag; `wait()` queues a bounded wait for
+    all flags on the stream, after which `full(batch)` is the [batch, row_heads, head_dim] result on
+    this rank.  Two output buffers alternate from step to step.
+
+    One process per GPU on one node.  Collective constructor and `close()` (every rank must call them
+    together): the IPC handles travel through `torch.distributed.all_gather_object`."""
+
+    def __init__(self, batch_max: int, row_heads: int, head_dim: int, dtype: torch.dtype, device,
+                 group: Optional[dist.ProcessGroup] = None) -> None:
+        from . import _lib
+        self._lib = _lib
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"{self.world} ranks: at most {_lib.MAX_PEERS} GPUs of one node")
+        self.device = torch.device(device)
+        self.batch_max, self.row_heads, self.head_dim, self.dtype = int(batch_max), int(row_heads), int(head_dim), dtype
+        es = torch.empty((), dtype=dtype).element_size()
+        self._off0, self._off1, self.nbytes = peer_layout(batch_max, row_heads, head_dim, es)
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.piekv_peer_alloc(self.nbytes, C.byref(ptr), handle), "peer_alloc")
+            handles: List[Optional[bytes]] = [None] * self.world
+            dist.all_gather_object(handles, handle.raw, group=group)
+            self._own = int(ptr.value)
+            self._base: List[int] = []
+            for r in range(self.world):
+                if r == self.rank:
+                    self._base.append(self._own)
+                    continue
+                q = C.c_void_p()
+                _lib.check(_lib.lib.piekv_peer_open(handles[r], C.byref(q)), f"peer_open(rank {r})")
+                self._base.append(int(q.value))
+        self._local = torch.as_tensor(_RawCuda(self._own, self.nbytes), device=self.device)
+        self.step = 0
+        dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores
+
+    def begin_step(self):
+        """Descriptor (ctypes struct) of the next step's destinations."""
+        self.step += 1
+        off = self._off0 if (self.step & 1) else self._off1
+        d = self._lib.PeerOutputsC()
+        for r in range(self.world):
+            d.out[r] = self._base[r] + off
+            d.flags[r] = self._base[r]
+        d.world, d.rank, d.row_heads, d.step = self.world, self.rank, self.row_heads, self.step
+        return d
+
+    def wait(self) -> None:
+        """Queue, on the current stream, the wait for every rank's flag of the current step."""
+        from .ops import _err_word, _stream
+        self._lib.check(self._lib.lib.piekv_peer_wait(self._own, self.world, self.step,
+                                                      _err_word(self.device).data_ptr(), _stream(self.device)),
+                        "peer_wait")
+
+    def full(self, batch: int) -> torch.Tensor:
+        """[batch, row_heads, head_dim] rows of the current step on this rank (valid after `wait()`)."""
+        off = self._off0 if (self.step & 1) else self._off1
+        n = batch * self.row_heads * self.head_dim
+        return self._local[off:].view(self.dtype)[:n].view(batch, self.row_heads, self.head_dim)
+
+    def close(self) -> None:
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)  # nobody is still storing into a buffer about to go away
+        with torch.cuda.device(self.device):
+            for r, b in enumerate(self._base):
+                if r != self.rank:
+                    self._lib.lib.piekv_peer_close(b)
+            self._local = None
+            dist.barrier(group=self.group)  # everyone has unmapped before the owners free
+            self._lib.lib.piekv_peer_free(self._own)
+        self._base = None
