@@ -532,8 +532,10 @@ def run_decode70b(args):
     """64 q / 8 kv heads, D128, bf16, 256 requests with lognormal contexts (median 2048, clipped to
     [128, 32768]); every 32 steps 20 % of the requests are evicted, their pages recycled and the slots
     refilled with 1024-token contexts written through the RoPE + append kernel.  With G ranks every rank
-    holds 8/G KV heads (and 64/G query heads) of every request with identical page tables and the
-    attention outputs are all-gathered (NCCL) each step."""
+    holds 8/G KV heads (and 64/G query heads) of every request with identical page tables.  The ranks are
+    joined either by the decode kernel itself, which stores its heads into every rank's output buffer
+    over NVLink and raises a flag (`--join peer`, default), or by an NCCL all-gather after the attention
+    (`--join nccl`)."""
     import torch.distributed as dist
 
     from pie_b200 import ops, parallel
@@ -583,6 +585,9 @@ def run_decode70b(args):
     rope = ops.RopeConfig()
     w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
     launches = [0]
+    peers = None
+    if world > 1 and args.join == "peer":
+        peers = parallel.PeerOutputs(B, cfg.num_qo_heads, D, cfg.dtype, dev)
 
     def step(i):
         pl = plan[i]
@@ -598,6 +603,9 @@ def run_decode70b(args):
         k = x[:, hq * D: (hq + hkv) * D].view(B, hkv, D)
         v = x[:, (hq + hkv) * D:].view(B, hkv, D)
         w.plan(pl["indptr"], pl["indices"], pl["last"], hq, hkv, D, 16, q_data_type=cfg.dtype)
+        if peers is not None:
+            launches[0] += 2  # the fused step and the flag wait
+            return w.run_fused_peer(q, k, v, pl["pos"], pool, peers, rope)
         o = w.run_fused(q, k, v, pl["pos"], pool, rope, out=out)
         launches[0] += 1
         return parallel.allgather_heads(o, gather_buffer=gather) if world > 1 else o
@@ -653,8 +661,10 @@ def run_decode70b(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, "
                                    f"{B} requests, lognormal ctx, 20% evicted+refilled every 32 steps",
-                       "parallelism": f"KV heads sharded x{world} ({hkv} kv / {hq} q heads per GPU), NCCL all-gather "
-                                      "of attention outputs", "pool_pages": num_pages,
+                       "parallelism": f"KV heads sharded x{world} ({hkv} kv / {hq} q heads per GPU), " + (
+                           "outputs stored to every GPU by the decode kernel (NVLink peer stores + flags)"
+                           if peers is not None else "NCCL all-gather of attention outputs"),
+                       "pool_pages": num_pages,
                        "l2": "inputs larger than L2; no flush", "launch": "eager, one fused kernel per step"},
             "clocks": sampler.summary(), "gpu_launches": launches[0],
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only, per GPU)", "achieved": achieved,
@@ -662,6 +672,8 @@ def run_decode70b(args):
                          "traffic": None, "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
                          "cached_tokens": tokens},
             "device_error_word": ops.device_error(dev)}), flush=True)
+    if peers is not None:
+        peers.close()
     if world > 1:
         dist.destroy_process_group()
 
@@ -988,6 +1000,8 @@ def main():
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
+    ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
+                    help="decode70b on several GPUs: how the head-sharded outputs are joined")
     ap.add_argument("--prefill-brle", action="store_true",
                     help="prefill: pass the mask as BRLE runs (wire form), expanded to bits on the device")
     args = ap.parse_args()
