@@ -205,6 +205,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const float scale_log2 = a.sm_scale * 1.4426950408889634f;
   // Where results go: a.out, or (head-sharded run over several GPUs) the same rows of an output
   // buffer on every GPU, this GPU's heads at column head_off of rows that hold row_heads heads.
+  T *out = reinterpret_cast<T *>(a.out);
   const int n_dst = p.peer.n > 0 ? p.peer.n : 1;
   const int row_heads = p.peer.n > 0 ? p.peer.row_heads : a.hq;
   const int head_off = p.peer.n > 0 ? p.peer.head_off : 0;
@@ -529,11 +530,18 @@ __global__ void __launch_bounds__(kThreads, 1)
           const int qh = h * group + row;
           const float lsum = half ? ls1 : ls0;
           const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-          for (int d = 0; d < n_dst; ++d) {
-            uint32_t *orow = reinterpret_cast<uint32_t *>(dst_row(d, b, qh));
+          if (p.peer.n == 0) {  // the usual case keeps its own straight-line stores
+            uint32_t *orow = reinterpret_cast<uint32_t *>(out + ((size_t)b * a.hq + qh) * kDim);
 #pragma unroll
             for (int nt = 0; nt < 16; ++nt)
               orow[nt * 4 + qlane] = pack2<T>(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+          } else {
+            for (int d = 0; d < n_dst; ++d) {
+              uint32_t *orow = reinterpret_cast<uint32_t *>(dst_row(d, b, qh));
+#pragma unroll
+              for (int nt = 0; nt < 16; ++nt)
+                orow[nt * 4 + qlane] = pack2<T>(o[nt][half * 2] * inv, o[nt][half * 2 + 1] * inv);
+            }
           }
           if (a.lse != nullptr && qlane == 0) {
             const float mm = half ? m1 : m0;
@@ -597,7 +605,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       uint2 pk;
       pk.x = pack2<T>(acc.x * inv, acc.y * inv);
       pk.y = pack2<T>(acc.z * inv, acc.w * inv);
-      for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
+      if (p.peer.n == 0) {
+        *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
+      } else {
+        for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
+      }
       if (a.lse != nullptr && (tid & 31) == 0)
         a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
     }
