@@ -312,6 +312,40 @@ int piekv_copy_pages(void *const *pools, int32_t num_layers, const int32_t *src_
                      int32_t page_size, int32_t num_kv_heads, int32_t head_dim, int32_t num_pages,
                      int32_t dtype, int32_t *err, void *stream);
 
+/* ---- page bookkeeping on the host (no GPU work) ---------------------------------------------
+ *
+ * Native counterpart of the reference's id pool (runtime/src/utils.rs:42-158: smallest free id
+ * first, tail compaction above 1000 free ids) and of its resource manager for KV pages of one
+ * device group (runtime/src/model/resource.rs:62-463): instances own pages; an allocation that
+ * does not fit terminates instances that started after the requester, newest first, and fails
+ * with PIEKV_STATUS_OUT_OF_PAGES if that is not enough; export moves pages to a name, import
+ * reads them, release_exported frees them.  Reference counts (piekv_pages_share) are an addition
+ * for forked contexts that keep full pages in common: a page returns to the pool when its last
+ * holder lets go.  Calls return 0, 1 (invalid argument, see piekv_last_error_string) or
+ * PIEKV_STATUS_OUT_OF_PAGES.  One manager per pool, driven from one thread. */
+#define PIEKV_STATUS_OUT_OF_PAGES 8
+typedef struct piekv_page_manager piekv_page_manager;
+piekv_page_manager *piekv_pages_create(int32_t num_pages);
+void piekv_pages_destroy(piekv_page_manager *m);
+int32_t piekv_pages_available(const piekv_page_manager *m);
+int32_t piekv_pages_refcount(const piekv_page_manager *m, int32_t page);   /* -1: no such page */
+int32_t piekv_pages_owned(const piekv_page_manager *m, uint64_t instance); /* pages the instance holds */
+/* `count` pages for `instance` (allocate_with_oom, resource.rs:112-175); the instances terminated
+ * to make room are reported by piekv_pages_last_victims. */
+int piekv_pages_alloc(piekv_page_manager *m, uint64_t instance, int32_t count, int32_t *out);
+int32_t piekv_pages_last_victims(const piekv_page_manager *m, uint64_t *out, int32_t max_count);
+/* deallocate (resource.rs:225-254): pages the instance does not hold are skipped */
+int piekv_pages_free(piekv_page_manager *m, uint64_t instance, const int32_t *pages, int32_t count);
+/* the instance becomes a co-holder of pages that are already allocated (fork of full pages) */
+int piekv_pages_share(piekv_page_manager *m, uint64_t instance, const int32_t *pages, int32_t count);
+/* everything the instance holds (cleanup, resource.rs:321-354) */
+int piekv_pages_cleanup(piekv_page_manager *m, uint64_t instance);
+int piekv_pages_export(piekv_page_manager *m, uint64_t instance, const int32_t *pages, int32_t count,
+                       const char *name);
+/* number of pages under `name` (-1: not found); up to max_count ids are written to `out` */
+int32_t piekv_pages_import(const piekv_page_manager *m, const char *name, int32_t *out, int32_t max_count);
+int piekv_pages_release_exported(piekv_page_manager *m, const char *name);
+
 #ifdef __cplusplus
 }
 #endif

@@ -15,6 +15,7 @@ ROPE_NONE, ROPE_PLAIN, ROPE_LLAMA31, ROPE_TABLE = 0, 1, 2, 3
 OPT_PDL = 0
 
 PIEKV_ERR_WAIT_TIMEOUT = 5
+STATUS_OUT_OF_PAGES = 8
 ERR_NAMES = {
     0: "ok",
     1: "batch index out of range",
@@ -108,6 +109,19 @@ SIGNATURES = {
          _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
     ),
     "piekv_peer_wait": (C.c_int, [_p, _i32, _i32, _p, _p]),
+    "piekv_pages_create": (C.c_void_p, [_i32]),
+    "piekv_pages_destroy": (None, [_p]),
+    "piekv_pages_available": (_i32, [_p]),
+    "piekv_pages_refcount": (_i32, [_p, _i32]),
+    "piekv_pages_owned": (_i32, [_p, C.c_uint64]),
+    "piekv_pages_alloc": (C.c_int, [_p, C.c_uint64, _i32, _p]),
+    "piekv_pages_last_victims": (_i32, [_p, _p, _i32]),
+    "piekv_pages_free": (C.c_int, [_p, C.c_uint64, _p, _i32]),
+    "piekv_pages_share": (C.c_int, [_p, C.c_uint64, _p, _i32]),
+    "piekv_pages_cleanup": (C.c_int, [_p, C.c_uint64]),
+    "piekv_pages_export": (C.c_int, [_p, C.c_uint64, _p, _i32, C.c_char_p]),
+    "piekv_pages_import": (_i32, [_p, C.c_char_p, _p, _i32]),
+    "piekv_pages_release_exported": (C.c_int, [_p, C.c_char_p]),
     "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32, _i64]),
     "piekv_prefill_plan": (
         C.c_int,

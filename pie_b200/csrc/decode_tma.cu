@@ -37,7 +37,10 @@ constexpr int kStages = 3;
 constexpr int kTileBytes = 8192;               // one (page, head): K 4 KiB + V 4 KiB
 constexpr int kStageBytes = 8 * kTileBytes;    // 64 KiB
 constexpr int kCounterBytes = 65536;           // head of the workspace: arrival counters
-constexpr int kMaxBatch = kCounterBytes / 4;
+constexpr int kMergeGroup = 16;                // partials folded by one CTA at a time
+constexpr int kGroupCounters = 256;            // group counters, indexed by the group's first CTA (grid <= 256)
+constexpr int kMaxBatch = kCounterBytes / 4 - kGroupCounters - 1;  // request counters; then the group counters; then one word
+constexpr int kGroupCounter0 = kMaxBatch;
 
 struct DecodeParams {
   AttnArgs a;
@@ -563,57 +566,86 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (qlane == 0) p.part_ml[pidx * a.hq + qh] = make_float2(half ? m1 : m0, half ? ls1 : ls0);
       }
     }
-    __threadfence();
-    consumer_bar_sync();
-    if (tid == 0) {
-      const int old = atomicAdd(&p.counters[b], 1);
-      sh_last = (old == nseg - 1) ? 1 : 0;
-    }
-    consumer_bar_sync();
-    const bool last = sh_last != 0;
-    consumer_bar_sync();  // everyone has read sh_last before a later segment rewrites it
-    if (!last) continue;
-    __threadfence();
-    // merge every partial of request b: thread -> (query head tid/32 + 8k, 4 consecutive d).
-    // Two passes so that the loads of a pass are independent of one another and stay in flight
-    // together: first the global maximum, then the weighted sums.
-    const int d4 = (tid & 31) * 4;
-    const int nparts = nseg * PG;
-    const size_t part0 = (size_t)(c_first + b) * PG;  // partial index of (first CTA, sub 0)
-    for (int qh = tid >> 5; qh < a.hq; qh += kConsumerWarps) {
-      float M = -INFINITY;
+    // Combine `n` partials of request b, `stride` slots apart starting at slot `first`: thread ->
+    // (query head tid/32 + 8k, 4 consecutive d).  Two passes so that the loads of a pass are
+    // independent of one another and stay in flight together: first the global maximum, then the
+    // weighted sums.  The result is either the request's output row (normalised) or again a partial
+    // (maximum, sum, unnormalised accumulator) written over slot `first`.
+    auto merge_parts = [&](size_t first, size_t stride, int n, bool to_partial) {
+      const int d4 = (tid & 31) * 4;
+      for (int qh = tid >> 5; qh < a.hq; qh += kConsumerWarps) {
+        float M = -INFINITY;
 #pragma unroll 8
-      for (int pp = 0; pp < nparts; ++pp) {
-        const float2 ml = __ldcg(p.part_ml + (part0 + pp) * a.hq + qh);
-        M = ml.y > 0.f ? fmaxf(M, ml.x) : M;
-      }
-      float L = 0.f;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int pp = 0; pp < n; ++pp) {
+          const float2 ml = __ldcg(p.part_ml + (first + pp * stride) * a.hq + qh);
+          M = ml.y > 0.f ? fmaxf(M, ml.x) : M;
+        }
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 8
-      for (int pp = 0; pp < nparts; ++pp) {
-        const size_t idx = (part0 + pp) * a.hq + qh;
-        const float2 ml = __ldcg(p.part_ml + idx);
-        const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
-        const float w = ml.y > 0.f ? fast_exp2(ml.x - M) : 0.f;  // a warp that saw no page: weight 0
-        L = fmaf(ml.y, w, L);
-        acc.x = fmaf(po.x, w, acc.x);
-        acc.y = fmaf(po.y, w, acc.y);
-        acc.z = fmaf(po.z, w, acc.z);
-        acc.w = fmaf(po.w, w, acc.w);
+        for (int pp = 0; pp < n; ++pp) {
+          const size_t idx = (first + pp * stride) * a.hq + qh;
+          const float2 ml = __ldcg(p.part_ml + idx);
+          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
+          const float w = ml.y > 0.f ? fast_exp2(ml.x - M) : 0.f;  // a warp that saw no page: weight 0
+          L = fmaf(ml.y, w, L);
+          acc.x = fmaf(po.x, w, acc.x);
+          acc.y = fmaf(po.y, w, acc.y);
+          acc.z = fmaf(po.z, w, acc.z);
+          acc.w = fmaf(po.w, w, acc.w);
+        }
+        if (to_partial) {
+          __syncwarp();  // every lane has read slot `first` of this head before it is overwritten
+          const size_t idx = first * a.hq + qh;
+          *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc;
+          if ((tid & 31) == 0) p.part_ml[idx] = make_float2(M, L);
+          continue;
+        }
+        const float inv = L > 0.f ? 1.f / L : 0.f;
+        uint2 pk;
+        pk.x = pack2<T>(acc.x * inv, acc.y * inv);
+        pk.y = pack2<T>(acc.z * inv, acc.w * inv);
+        if (p.peer.n == 0) {
+          *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
+        } else {
+          for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
+        }
+        if (a.lse != nullptr && (tid & 31) == 0)
+          a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
       }
-      const float inv = L > 0.f ? 1.f / L : 0.f;
-      uint2 pk;
-      pk.x = pack2<T>(acc.x * inv, acc.y * inv);
-      pk.y = pack2<T>(acc.z * inv, acc.w * inv);
-      if (p.peer.n == 0) {
-        *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
-      } else {
-        for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
+    };
+    // whoever arrives last on a counter sees everybody else's partials
+    auto arrive_last = [&](int *counter, int expected) -> bool {
+      __threadfence();
+      consumer_bar_sync();
+      if (tid == 0) {
+        const int old = atomicAdd(counter, 1);
+        sh_last = (old == expected - 1) ? 1 : 0;
+        if (sh_last) *counter = 0;  // ready for the next launch (nobody else touches it any more)
       }
-      if (a.lse != nullptr && (tid & 31) == 0)
-        a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+      consumer_bar_sync();
+      const bool last = sh_last != 0;
+      consumer_bar_sync();  // everyone has read sh_last before it is rewritten
+      if (last) __threadfence();
+      return last;
+    };
+    if (nseg <= kMergeGroup) {
+      if (!arrive_last(&p.counters[b], nseg)) continue;
+      merge_parts((size_t)(c_first + b) * PG, 1, nseg * PG, false);
+      continue;
     }
-    if (tid == 0) p.counters[b] = 0;  // leave the counter ready for the next launch
+    // A request cut over many CTAs (one long context): merging 100+ partials in a single CTA would sit
+    // on the critical path of the whole launch.  Segments are grouped kMergeGroup at a time; the last
+    // CTA of a group folds the group into one partial (groups fold concurrently on different SMs), and
+    // the last group to finish folds the groups.
+    const int gi = (c - c_first) / kMergeGroup;
+    const int g_first = c_first + gi * kMergeGroup;
+    const int g_size = min(kMergeGroup, c_last + 1 - g_first);
+    const int n_groups = (nseg + kMergeGroup - 1) / kMergeGroup;
+    if (!arrive_last(&p.counters[kGroupCounter0 + g_first], g_size)) continue;
+    merge_parts((size_t)(g_first + b) * PG, 1, g_size * PG, true);
+    if (!arrive_last(&p.counters[b], n_groups)) continue;
+    merge_parts((size_t)(c_first + b) * PG, (size_t)kMergeGroup * PG, n_groups, false);
   }
   finish();
 }
@@ -693,6 +725,7 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "decode: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)need);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
+  PIEKV_REQUIRE(sm_count() <= kGroupCounters, "decode: %d SMs, the group counters hold %d", sm_count(), kGroupCounters);
   p->a = a;
   p->peer = PeerOut{};
   p->pdl = get_option(PIEKV_OPT_PDL);
@@ -731,9 +764,8 @@ int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const v
   CUtensorMap tm;
   if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
   if (peer != nullptr && peer->n > 0) {
-    PIEKV_REQUIRE(a.batch < kMaxBatch, "decode (peer outputs): batch %d too large", a.batch);
     p.peer = *peer;
-    p.peer.done = p.counters + (kMaxBatch - 1);  // last word of the counter block, never a request's
+    p.peer.done = p.counters + (kCounterBytes / 4 - 1);  // last word of the counter block
   }
   FusedArgs f;
   f.k_new = k;
@@ -830,6 +862,10 @@ extern "C" int piekv_decode_run_noalloc(const void *q, int64_t q_stride_n, int64
   if (int rc = static_scratch_ptr(&scratch)) return rc;
   // the arrival counters must be zero when the kernel starts, whatever an earlier call left behind
   cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)batch * sizeof(int), st);
+  if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaMemsetAsync");
+  // and the group counters of the two-level merge, at the tail of the counter block
+  e = cudaMemsetAsync(reinterpret_cast<uint8_t *>(scratch) + (size_t)kGroupCounter0 * sizeof(int), 0,
+                      (size_t)(kGroupCounters + 1) * sizeof(int), st);
   if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaMemsetAsync");
   return launch_decode_tma(a, dtype, scratch, kStaticScratchBytes, st);
 }

@@ -66,5 +66,18 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
   }
 }
 
+// Zero the rows of a staged V tile that belong to the request's last page but lie beyond its last
+// token (rows [first, end) of the 128-token tile; a row is 128 bytes in each 64-column half,
+// whatever the swizzle does inside it).  Their probabilities are zero, but 0 x NaN is NaN, and a
+// recycled page may hold anything there.  Executed by one full warp after the tile has landed.
+__device__ __forceinline__ void zero_v_rows(uint32_t v_tile_smem, int first, int end, int lane) {
+  for (int x = lane; x < (end - first) * 16; x += 32) {
+    const int row = first + (x >> 4), half = (x >> 3) & 1, ch = x & 7;
+    asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(v_tile_smem + half * kHalfBytes + row * 128 + ch * 16),
+                 "r"(0)
+                 : "memory");
+  }
+}
+
 }  // namespace prefill
 }  // namespace piekv

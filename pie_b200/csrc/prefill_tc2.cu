@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(k2Threads, 1)
     prefill_tc2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
                        const __grid_constant__ PrefillParams p) {
   extern __shared__ uint8_t smem_raw[];
-  __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages],
+  __shared__ __align__(8) uint64_t q_full, k_full[kKStages], k_empty[kKStages], v_full[kVStages], v_empty[kVStages], v_land,
       s_full[2], p_full[2][2], o_done[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int sh_abort;
@@ -130,6 +130,7 @@ __global__ void __launch_bounds__(k2Threads, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
+    mbar_init(&v_land, 1);
     for (int s = 0; s < kKStages; ++s) {
       mbar_init(&k_full[s], 1);
       mbar_init(&k_empty[s], 1);
@@ -204,12 +205,28 @@ __global__ void __launch_bounds__(k2Threads, 1)
         if (mbar_try_wait(&v_empty[vs], ((v_armed / kVStages) & 1) ^ 1)) {
           while (!active(jv)) ++jv;
           const int page = page_of(jv);
-          if (lane == 0) mbar_arrive_expect_tx(&v_full[vs], kTileBytes);
+          // The tile that holds a partly filled last page lands on a barrier of its own, has its stale
+          // rows zeroed, and only then is handed to the MMA warp (at most once per CTA).
+          const bool partial = (kv_len & (kPage - 1)) != 0 && jv == (kv_len - 1) / kBN;
+          uint64_t *land = partial ? &v_land : &v_full[vs];
+          if (lane == 0) mbar_arrive_expect_tx(land, kTileBytes);
           __syncwarp();
           if (lane < 8) {
             const uint32_t vdst = v_smem0 + vs * kTileBytes + lane * 2048;
-            tma_load_5d(vdst, &tmap_kv, 0, 0, 0, hk, page * 2 + 1, &v_full[vs]);
-            tma_load_5d(vdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2 + 1, &v_full[vs]);
+            tma_load_5d(vdst, &tmap_kv, 0, 0, 0, hk, page * 2 + 1, land);
+            tma_load_5d(vdst + kHalfBytes, &tmap_kv, 0, 0, 1, hk, page * 2 + 1, land);
+          }
+          if (partial) {
+            if (!wait_or_abort(&v_land, 0, abort_flag)) {
+              if (lane == 0 && !*abort_flag) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_PREFILL, blockIdx.x, 110);
+              if (lane == 0) atomicExch(&sh_abort, 1);
+              break;
+            }
+            const int first = kv_len - jv * kBN;
+            zero_v_rows(v_smem0 + vs * kTileBytes, first, min(kBN, (first + kPage - 1) / kPage * kPage), lane);
+            fence_proxy_async_smem();  // generic-proxy stores before the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&v_full[vs]);
           }
           ++jv;
           ++v_armed;

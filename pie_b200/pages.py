@@ -235,3 +235,80 @@ def build_csr(contexts: Sequence[KvPageList]) -> Tuple[np.ndarray, np.ndarray, n
         indices[s: s + len(c.pages)] = c.pages
     last = np.fromiter((c.last_page_len for c in contexts), dtype=np.int32, count=len(contexts))
     return indices, indptr, last
+
+
+class NativePageManager:
+    """The library's native (C++) page manager: id pool, reference counts, per-instance ownership, the
+    reference's out-of-memory policy (instances that started after the requester are terminated, newest
+    first; runtime/src/model/resource.rs:112-319) and export / import by name (resource.rs:356-451).
+    `IdPool` / `PagePool` above are the same id and reference-count rules in Python; this class is what a
+    runtime embeds."""
+
+    def __init__(self, num_pages: int) -> None:
+        import ctypes as C
+
+        from . import _lib
+        self._C, self._lib = C, _lib
+        self._h = _lib.lib.piekv_pages_create(int(num_pages))
+        if not self._h:
+            raise ValueError("piekv_pages_create failed")
+        self.num_pages = int(num_pages)
+
+    def close(self) -> None:
+        if self._h:
+            self._lib.lib.piekv_pages_destroy(self._h)
+            self._h = None
+
+    def __del__(self):  # pragma: no cover
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _arr(self, pages: Sequence[int]):
+        return (self._C.c_int32 * len(pages))(*[int(p) for p in pages])
+
+    def available(self) -> int:
+        return int(self._lib.lib.piekv_pages_available(self._h))
+
+    def refcount(self, page: int) -> int:
+        return int(self._lib.lib.piekv_pages_refcount(self._h, int(page)))
+
+    def owned(self, instance: int) -> int:
+        return int(self._lib.lib.piekv_pages_owned(self._h, int(instance)))
+
+    def alloc(self, instance: int, count: int) -> Tuple[List[int], List[int]]:
+        """(pages, instances terminated to make room).  Raises PoolExhausted when even that is not enough."""
+        out = (self._C.c_int32 * max(count, 1))()
+        rc = self._lib.lib.piekv_pages_alloc(self._h, int(instance), int(count), out)
+        if rc == self._lib.STATUS_OUT_OF_PAGES:
+            raise PoolExhausted(self._lib.lib.piekv_last_error_string().decode())
+        self._lib.check(rc, "pages_alloc")
+        vbuf = (self._C.c_uint64 * 64)()
+        nv = int(self._lib.lib.piekv_pages_last_victims(self._h, vbuf, 64))
+        return [int(out[i]) for i in range(count)], [int(vbuf[i]) for i in range(min(nv, 64))]
+
+    def free(self, instance: int, pages: Sequence[int]) -> None:
+        self._lib.check(self._lib.lib.piekv_pages_free(self._h, int(instance), self._arr(pages), len(pages)),
+                        "pages_free")
+
+    def share(self, instance: int, pages: Sequence[int]) -> None:
+        self._lib.check(self._lib.lib.piekv_pages_share(self._h, int(instance), self._arr(pages), len(pages)),
+                        "pages_share")
+
+    def cleanup(self, instance: int) -> None:
+        self._lib.check(self._lib.lib.piekv_pages_cleanup(self._h, int(instance)), "pages_cleanup")
+
+    def export(self, instance: int, pages: Sequence[int], name: str) -> None:
+        self._lib.check(self._lib.lib.piekv_pages_export(self._h, int(instance), self._arr(pages), len(pages),
+                                                         name.encode()), "pages_export")
+
+    def import_(self, name: str) -> List[int]:
+        out = (self._C.c_int32 * self.num_pages)()
+        n = int(self._lib.lib.piekv_pages_import(self._h, name.encode(), out, self.num_pages))
+        if n < 0:
+            raise KeyError(name)
+        return [int(out[i]) for i in range(n)]
+
+    def release_exported(self, name: str) -> None:
+        self._lib.check(self._lib.lib.piekv_pages_release_exported(self._h, name.encode()), "pages_release_exported")

@@ -411,3 +411,49 @@ def test_decode_with_programmatic_dependent_launch(mode):
     assert ops.device_error("cuda") is None
     assert torch.equal(results[0][0], results[mode][0])
     assert torch.equal(results[0][1], results[mode][1])
+
+
+@pytest.mark.parametrize("hq,hkv", [(4, 2), (3, 3)])   # two-head kernel / one-head kernel
+@pytest.mark.parametrize("causal", [True, False])
+def test_prefill_ignores_nan_in_stale_rows_and_unused_pages(hq, hkv, causal):
+    """A recycled page may hold anything beyond the request's last token (and pages outside every list
+    anything at all): probabilities there are zero, and zero times NaN must not reach the output."""
+    reqs = [(0, 300), (511, 130), (0, 5), (96, 1)]   # kv = 300, 641, 5, 97: partly filled last pages
+    sc = make_scenario(hq, hkv, 128, torch.bfloat16, reqs, seed=31, scale=0.5)
+    m = sc.meta
+    pool = sc.pool.clone()
+    used = np.zeros(sc.num_pages, dtype=bool)
+    for b in range(len(reqs)):
+        pages = m.kv_indices[m.kv_indptr[b]: m.kv_indptr[b + 1]]
+        used[pages] = True
+        last = int(m.kv_last_page_len[b])
+        if last < 16:
+            pool[int(pages[-1]), :, last:] = float("nan")
+    pool[torch.from_numpy(~used)] = float("nan")
+    ref = R.prefill_attention(sc.q, pool, m.qo_indptr, m.kv_indptr, m.kv_indices, m.kv_last_page_len, causal=causal)
+    w = ops.BatchPrefillWithPagedKVCacheWrapper(_workspace(), "NHD")
+    w.plan(dev(m.qo_indptr), dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), hq, hkv, 128, 16,
+           causal=causal, q_data_type=torch.bfloat16)
+    out = w.run(sc.q.cuda(), pool.cuda()).cpu()
+    assert ops.device_error("cuda") is None
+    assert torch.isfinite(out.float()).all()
+    assert (out.float() - ref.float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 2), (16, 1)])   # 1, 4 and 8 page slots per stage
+@pytest.mark.parametrize("ctx", [[40000], [20000, 17, 30000, 3], [5000, 5000, 5000]])
+def test_decode_two_level_merge_of_long_requests(hq, hkv, ctx):
+    """Requests cut over more than 16 CTAs are merged in two levels (groups of 16 partials fold on
+    different SMs, the last group folds the groups); 17..148 segments per request are all exercised by
+    these lengths, and the counters must come back to zero."""
+    sc = make_scenario(hq, hkv, 128, torch.bfloat16, [(c - 1, 1) for c in ctx], seed=9, scale=0.5)
+    m = sc.meta
+    ref, ref_lse = R.decode_attention(sc.q, sc.pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len, return_lse=True)
+    ws = _workspace()
+    out, lse = _run_decode(sc, ws, return_lse=True)
+    assert ops.device_error("cuda") is None
+    assert (out.cpu().float() - ref.float()).abs().max().item() <= 2e-2
+    assert (lse.cpu() - ref_lse).abs().max().item() <= 2e-2
+    assert int(ws[: ops.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
+    out2, _ = _run_decode(sc, ws, return_lse=True)
+    assert torch.equal(out, out2)

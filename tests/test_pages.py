@@ -98,3 +98,80 @@ def test_remove_page_and_csr():
     idx, ptr, last = build_csr([a, b, KvPageList(pool, 16)])
     assert ptr.tolist() == [0, 2, 3, 3] and last.tolist() == [8, 16, 0]
     assert idx.tolist() == a.pages + b.pages and idx.dtype == np.int32
+
+
+# ---- the native (C++) manager: same id rules as IdPool, plus the reference's ownership / OOM / export rules
+def test_native_manager_ids_follow_the_python_pool():
+    from pie_b200.pages import NativePageManager
+    rng = np.random.default_rng(0)
+    nat, py = NativePageManager(3000), PagePool(3000)
+    held = []
+    for step in range(400):
+        if held and rng.random() < 0.45:
+            k = int(rng.integers(1, min(len(held), 40) + 1))
+            idx = sorted(rng.choice(len(held), size=k, replace=False).tolist(), reverse=True)
+            drop = [held.pop(i) for i in idx]
+            nat.free(1, drop)
+            py.release(drop)
+        else:
+            k = int(rng.integers(1, 60))
+            if py.available() < k:
+                continue
+            a, victims = nat.alloc(1, k)
+            b = py.alloc(k)
+            assert a == b and victims == []
+            held += a
+        assert nat.available() == py.available()
+    # tail compaction: > 1000 free ids forming the tail fold back, the next id is the smallest again
+    nat.free(1, held)
+    py.release(held)
+    assert nat.available() == py.available() == 3000
+    assert nat.alloc(1, 3)[0] == py.alloc(3) == [0, 1, 2]
+    nat.close()
+
+
+def test_native_manager_oom_terminates_newer_instances_newest_first():
+    from pie_b200.pages import NativePageManager
+    m = NativePageManager(10)
+    old, _ = m.alloc(100, 4)      # instance 100 starts first
+    mid, _ = m.alloc(200, 3)
+    new, _ = m.alloc(300, 3)
+    assert m.available() == 0
+    # the oldest asks for 5 more: 300 (newest) goes first, then 200; 100 itself is never a victim
+    pages, victims = m.alloc(100, 5)
+    assert victims == [300, 200] and m.owned(300) == 0 and m.owned(200) == 0 and m.owned(100) == 9
+    assert sorted(pages) == sorted(new + mid)[:5]
+    # a newer instance cannot evict an older one (resource.rs:262-275): the request fails, nothing changes
+    m.alloc(400, 1)
+    with pytest.raises(PoolExhausted):
+        m.alloc(400, 5)
+    assert m.owned(100) == 9 and m.owned(400) == 1
+    # an instance without a start time cannot trigger the policy at all
+    with pytest.raises(PoolExhausted):
+        m.alloc(500, 3)
+    m.close()
+
+
+def test_native_manager_share_export_import():
+    from pie_b200.pages import NativePageManager
+    m = NativePageManager(8)
+    a, _ = m.alloc(1, 3)
+    m.share(2, a[:2])                       # a fork keeps the two full pages in common
+    assert [m.refcount(p) for p in a] == [2, 2, 1]
+    m.cleanup(1)                            # the parent goes away: shared pages stay, its private page returns
+    assert [m.refcount(p) for p in a] == [1, 1, 0] and m.available() == 6
+    m.export(2, a[:2], "prefix")
+    assert m.owned(2) == 0 and m.import_("prefix") == a[:2]
+    with pytest.raises(ValueError):
+        m.export(2, a[:1], "prefix")        # not held any more / name exists
+    with pytest.raises(KeyError):
+        m.import_("nope")
+    m.cleanup(2)
+    assert m.available() == 6               # exported pages survive their exporter
+    m.release_exported("prefix")
+    assert m.available() == 8
+    with pytest.raises(ValueError):
+        m.share(3, [7])                     # not allocated
+    with pytest.raises(ValueError):
+        m.free(3, [])                       # an instance that holds nothing (InstanceNotAllocated in the reference)
+    m.close()
