@@ -1,8 +1,9 @@
 """Generate the golden fixtures of tests/golden/ by running the REFERENCE's own host code.
 
-Run in a container that has the reference checkout (read-only) at /root/reference:
+Run where a checkout of the reference is available (read-only is enough) and name its Python source
+directory, the one that holds `pie_worker/`:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <reference checkout>/pie/src
 
 It imports `pie_worker.batching.Batch` (pie/src/pie_worker/batching.py) unmodified, feeds it batches in
 the wire form (uint32 / float32 byte strings, pie/src/pie_worker/batching.py:61-76) and stores the inputs
@@ -16,7 +17,9 @@ import sys
 
 import numpy as np
 
-REF = "/root/reference/pie/src"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PIE_REFERENCE_SRC", "")
+if not os.path.isdir(os.path.join(REF, "pie_worker")):
+    raise SystemExit("usage: make_golden.py <reference checkout>/pie/src")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 

@@ -70,3 +70,13 @@ def test_shard_arithmetic():
         pass
     else:
         raise AssertionError("expected ValueError")
+
+
+def test_peer_layout_is_aligned_and_disjoint():
+    from pie_b200.parallel import peer_layout
+    for batch, heads, d, es in ((1, 8, 128, 2), (256, 64, 128, 2), (37, 16, 128, 2)):
+        off0, off1, total = peer_layout(batch, heads, d, es)
+        need = batch * heads * d * es
+        assert off0 >= 8 * 4                      # the flag words of up to 8 ranks come first
+        assert off0 % 256 == 0 and off1 % 256 == 0 and total % 256 == 0
+        assert off1 - off0 >= need and total - off1 >= need
