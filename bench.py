@@ -127,7 +127,10 @@ class ClockSampler:
 def build_steps(rank: int, horizon: int, batch: int = 64, num_pages: int = 32768):
     from pie_b200 import workloads as W
 
-    reqs = W.config2_requests(batch=batch, seed=1 + rank, num_pages=num_pages)
+    # weak scaling: every GPU gets the SAME draw of context lengths (the workload's seed 1), so the work
+    # per GPU is fixed as N grows and the max over ranks compares like with like; the page tables
+    # (fragmentation) and the tensor contents differ per rank
+    reqs = W.config2_requests(batch=batch, seed=1, num_pages=num_pages, perm_seed=1 + rank)
     return W.decode_steps(reqs, horizon)
 
 

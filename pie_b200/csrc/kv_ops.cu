@@ -266,6 +266,140 @@ __global__ void rope_append_kernel(AppendArgs a, RopeDev rp) {
   }
 }
 
+// The same operation for the common case (16-byte vectors, non-interleaved pairs, head_dim <= 256),
+// laid out for bandwidth: a block takes kTokPerBlock tokens; their cos / sin values are computed once
+// (one pair per thread) and shared through shared memory instead of once per head, the page lookup of a
+// token (three dependent loads) is done by one thread while the others compute, and afterwards every
+// thread moves 16-byte pieces of a flat work list (token, head, chunk) so that all 256 threads carry
+// loads in flight whatever the head count.  Arithmetic and rounding are those of rotate_chunk.
+constexpr int kTokPerBlock = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256) rope_append_tokens_kernel(AppendArgs a, RopeDev rp) {
+  constexpr int VEC = 16 / sizeof(T);
+  __shared__ float sh_c[kTokPerBlock][kMaxHalfDim], sh_s[kTokPerBlock][kMaxHalfDim];
+  __shared__ T *sh_kdst[kTokPerBlock];
+  __shared__ int sh_rope_ok[kTokPerBlock];
+  const int tok0 = blockIdx.x * kTokPerBlock;
+  const int ntok = min(kTokPerBlock, a.nnz - tok0);
+  const int D = a.dim, half = D / 2;
+  const bool do_rope = rp.mode != PIEKV_ROPE_NONE;
+  const int tid = threadIdx.x;
+
+  if (tid < ntok) {  // destination rows in the pool
+    const int tok = tok0 + tid;
+    T *kdst = nullptr;
+    if (a.pool != nullptr) {
+      const int b = a.batch_indices[tok];
+      const int pos = a.positions[tok];
+      if (b < 0 || b >= a.batch) {
+        report_error(a.err, PIEKV_ERR_BATCH_INDEX, KID_APPEND, tok, b);
+      } else {
+        const int p0 = a.kv_indptr[b], p1 = a.kv_indptr[b + 1];
+        const int slot = pos >= 0 ? pos / a.page_size : -1;
+        if (slot < 0 || p0 + slot >= p1) {
+          report_error(a.err, PIEKV_ERR_PAGE_SLOT, KID_APPEND, tok, pos);
+        } else {
+          const int page = a.kv_indices[p0 + slot];
+          if (page < 0 || page >= a.num_pages) {
+            report_error(a.err, PIEKV_ERR_PAGE_ID, KID_APPEND, tok, page);
+          } else {
+            const size_t half_page = (size_t)a.page_size * a.hkv * D;
+            kdst = reinterpret_cast<T *>(a.pool) + (size_t)page * 2 * half_page + (size_t)(pos % a.page_size) * a.hkv * D;
+          }
+        }
+      }
+    }
+    sh_kdst[tid] = kdst;
+  }
+  if (do_rope) {
+    for (int x = tid; x < ntok * half; x += blockDim.x) {
+      const int t = x / half, pr = x - t * half;
+      const int pos_id = a.pos_ids[tok0 + t];
+      const bool ok = !(rp.mode == PIEKV_ROPE_TABLE && (pos_id < 0 || pos_id >= rp.table_len));
+      if (pr == 0) {
+        sh_rope_ok[t] = ok ? 1 : 0;  // out of the table: q / k stay un-rotated, k still lands in the pool
+        if (!ok) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_ROPE, tok0 + t, pos_id);
+      }
+      float c = 1.f, sn = 0.f;
+      if (ok) rope_cos_sin1(rp, pos_id, pr, half, c, sn);
+      sh_c[t][pr] = c;
+      sh_s[t][pr] = sn;
+    }
+  } else if (tid < ntok) {
+    sh_rope_ok[tid] = 0;
+  }
+  __syncthreads();
+
+  const int q_heads = a.q != nullptr ? a.hq : 0;
+  const int k_heads = a.k != nullptr ? a.hkv : 0;
+  const int rchunks = half / VEC;  // a rotation item covers VEC pairs: elements [i0, i0+VEC) and the same + half
+  // ---- rotations: q heads (in place or to q_out) and k heads (to the pool and / or in place)
+  const int rot_items = ntok * (q_heads + k_heads) * rchunks;
+  for (int x = tid; x < rot_items; x += blockDim.x) {
+    const int ch = x % rchunks;
+    const int h = (x / rchunks) % (q_heads + k_heads);
+    const int t = x / (rchunks * (q_heads + k_heads));
+    const int tok = tok0 + t;
+    const bool rot = sh_rope_ok[t] != 0;
+    const T *src;
+    T *dst0 = nullptr, *dst1 = nullptr;
+    if (h < q_heads) {
+      if (!rot) continue;  // nothing to do for q without a rotation
+      T *row = reinterpret_cast<T *>(a.q) + (size_t)tok * a.q_sn + (size_t)h * a.q_sh;
+      src = row;
+      dst0 = a.q_out ? reinterpret_cast<T *>(a.q_out) + ((size_t)tok * a.hq + h) * D : row;
+    } else {
+      const int hk = h - q_heads;
+      T *row = reinterpret_cast<T *>(a.k) + (size_t)tok * a.k_sn + (size_t)hk * a.k_sh;
+      src = row;
+      T *kd = sh_kdst[t];
+      if (kd != nullptr) {
+        dst0 = kd + (size_t)hk * D;
+        dst1 = (rot && a.rotate_k_in_place) ? row : nullptr;
+      } else if (rot && (a.pool == nullptr || a.rotate_k_in_place)) {
+        dst0 = row;
+      } else {
+        continue;
+      }
+    }
+    const int i0 = ch * VEC;
+    const Vec<T, VEC> lo = load_vec<T, VEC>(src + i0);
+    const Vec<T, VEC> hi = load_vec<T, VEC>(src + i0 + half);
+    Vec<T, VEC> olo = lo, ohi = hi;
+    if (rot) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) {
+        const float xv = Elem<T>::to_f32(lo.v[j]), yv = Elem<T>::to_f32(hi.v[j]);
+        const float c = sh_c[t][i0 + j], sn = sh_s[t][i0 + j];
+        olo.v[j] = Elem<T>::from_f32(__fsub_rn(__fmul_rn(xv, c), __fmul_rn(yv, sn)));
+        ohi.v[j] = Elem<T>::from_f32(__fadd_rn(__fmul_rn(xv, sn), __fmul_rn(yv, c)));
+      }
+    }
+    store_vec<T, VEC>(dst0 + i0, olo);
+    store_vec<T, VEC>(dst0 + i0 + half, ohi);
+    if (dst1 != nullptr) {
+      store_vec<T, VEC>(dst1 + i0, olo);
+      store_vec<T, VEC>(dst1 + i0 + half, ohi);
+    }
+  }
+  // ---- v rows into the pool
+  if (a.pool != nullptr && a.v != nullptr) {
+    const int vchunks = D / VEC;
+    const int v_items = ntok * a.hkv * vchunks;
+    const size_t half_page = (size_t)a.page_size * a.hkv * D;
+    for (int x = tid; x < v_items; x += blockDim.x) {
+      const int ch = x % vchunks;
+      const int h = (x / vchunks) % a.hkv;
+      const int t = x / (vchunks * a.hkv);
+      T *kd = sh_kdst[t];
+      if (kd == nullptr) continue;
+      const T *vrow = reinterpret_cast<const T *>(a.v) + (size_t)(tok0 + t) * a.v_sn + (size_t)h * a.v_sh;
+      store_vec<T, VEC>(kd + half_page + (size_t)h * D + ch * VEC, load_vec<T, VEC>(vrow + ch * VEC));
+    }
+  }
+}
+
 // Per-pair frequencies in double, rounded once to fp32.  Formula of
 // pie/src/flashinfer_metal/kernels/metal_rope.metal:66-89 with the low/high/old_context
 // parameters the reference passes at pie/src/pie_worker/model/llama3.py:660-669.
@@ -312,7 +446,9 @@ static int launch_rope_append_t(const AppendArgs &a, const RopeDev &rp, cudaStre
   if (a.v) vec_ok = vec_ok && aligned16(a.v) && stride_ok(a.v_sn) && stride_ok(a.v_sh);
   if (a.pool) vec_ok = vec_ok && aligned16(a.pool);
   if (a.nnz == 0) return 0;
-  if (vec_ok) {
+  if (vec_ok && !rp.interleave && a.dim <= 2 * kMaxHalfDim && (a.k != nullptr || a.pool == nullptr)) {
+    rope_append_tokens_kernel<T><<<(a.nnz + kTokPerBlock - 1) / kTokPerBlock, 256, 0, st>>>(a, rp);
+  } else if (vec_ok) {
     int tx = a.dim / VEC;  // chunks across a full row (V copy); rope uses half of them
     if (tx > 32) tx = 32;
     int heads = (a.q ? a.hq : 0) + a.hkv;

@@ -188,10 +188,12 @@ CONFIG2 = HeadConfig(32, 8, 128, torch.bfloat16, 32768)
 
 
 def config2_requests(batch: int = 64, lo: int = 512, hi: int = 4096, seed: int = 1,
-                     num_pages: int = 32768) -> PagedRequests:
+                     num_pages: int = 32768, perm_seed: Optional[int] = None) -> PagedRequests:
+    """Context lengths U{lo..hi} drawn with `seed`; pages dealt from a permutation seeded with
+    `perm_seed` (default: the same seed)."""
     g = torch.Generator().manual_seed(seed)
     ctx = torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
-    reqs = PagedRequests(seeded_perm(num_pages, seed))
+    reqs = PagedRequests(seeded_perm(num_pages, seed if perm_seed is None else perm_seed))
     for c in ctx:
         reqs.add(c)
     return reqs
