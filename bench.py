@@ -592,7 +592,7 @@ def run_decode70b(args):
     if world > 1 and args.join == "peer":
         peers = parallel.PeerOutputs(B, cfg.num_qo_heads, D, cfg.dtype, dev)
 
-    def step(i):
+    def step(i, counted=False):
         pl = plan[i]
         rf = pl["refill"]
         if rf is not None:
@@ -608,7 +608,7 @@ def run_decode70b(args):
         w.plan(pl["indptr"], pl["indices"], pl["last"], hq, hkv, D, 16, q_data_type=cfg.dtype)
         if peers is not None:
             launches[0] += 2  # the fused step and the flag wait
-            return w.run_fused_peer(q, k, v, pl["pos"], pool, peers, rope)
+            return w.run_fused_peer(q, k, v, pl["pos"], pool, peers, rope, counted=counted)
         o = w.run_fused(q, k, v, pl["pos"], pool, rope, out=out)
         launches[0] += 1
         return parallel.allgather_heads(o, gather_buffer=gather) if world > 1 else o
@@ -621,18 +621,51 @@ def run_decode70b(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for i in range(warmup):
-        step(i)
+    graph = None
+    launch_mode = "eager, one fused kernel per step"
+    side = torch.cuda.Stream(device=dev)
+    use_graph = args.graph and (peers is not None or world == 1)  # the NCCL join stays eager
+    if use_graph:
+        # all timed steps (and their refills) in ONE graph: the device paces itself, no host jitter between
+        # steps.  With the peer-store join the step number lives in device memory (counted mode).
+        with torch.cuda.stream(side):
+            for i in range(warmup):
+                step(i, counted=True)
+        side.synchronize()
+        barrier()
+        launches[0] = 0
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                step(warmup + i, counted=True)
+        with torch.cuda.stream(side):
+            graph.replay()  # one untimed replay: graph upload
+        if peers is not None:
+            peers.advance(steps)
+        side.synchronize()
+        launch_mode = "CUDA graph of all timed steps"
+    else:
+        for i in range(warmup):
+            step(i)
     barrier()
-    launches[0] = 0
+    if graph is None:
+        launches[0] = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     with sampler:
         barrier()
-        e0.record()
-        for i in range(steps):
-            step(warmup + i)
-        e1.record()
+        if graph is not None:
+            with torch.cuda.stream(side):
+                e0.record(side)
+                graph.replay()
+                e1.record(side)
+            if peers is not None:
+                peers.advance(steps)
+        else:
+            e0.record()
+            for i in range(steps):
+                step(warmup + i)
+            e1.record()
         barrier()
     ms = e0.elapsed_time(e1)
     if world > 1:
@@ -668,7 +701,7 @@ def run_decode70b(args):
                            "outputs stored to every GPU by the decode kernel (NVLink peer stores + flags)"
                            if peers is not None else "NCCL all-gather of attention outputs"),
                        "pool_pages": num_pages,
-                       "l2": "inputs larger than L2; no flush", "launch": "eager, one fused kernel per step"},
+                       "l2": "inputs larger than L2; no flush", "launch": launch_mode},
             "clocks": sampler.summary(), "gpu_launches": launches[0],
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only, per GPU)", "achieved": achieved,
                          "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
@@ -1003,6 +1036,9 @@ def main():
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
+    ap.add_argument("--graph", action="store_true",
+                    help="decode70b: capture all timed steps in one CUDA graph (peer-store join or one GPU; the "
+                         "NCCL join stays eager)")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="decode70b on several GPUs: how the head-sharded outputs are joined")
     ap.add_argument("--prefill-brle", action="store_true",

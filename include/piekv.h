@@ -279,6 +279,11 @@ typedef struct piekv_peer_outputs {
   int32_t world, rank;
   int32_t row_heads;               /* query heads per output row (>= world * num_qo_heads of the call)       */
   int32_t step;                    /* published in the flags; must grow from call to call                     */
+  /* Graph replays: when step_counter is not NULL the kernel reads the step number from that device
+   * word instead of `step`, and stores to out[r] on odd and out_alt[r] on even step numbers;
+   * piekv_peer_wait_counted increments the word when the step is complete.  Start it at 1. */
+  const int32_t *step_counter;
+  void *out_alt[PIEKV_MAX_PEERS];
 } piekv_peer_outputs;
 
 /* piekv_decode_step_fused with the results of this rank's heads written to columns
@@ -299,6 +304,11 @@ int piekv_decode_step_fused_peer(const void *q, const void *k, const void *v, in
  * gives up after 2 s with PIEKV_ERR_WAIT_TIMEOUT in the error word.  Work queued behind it on the
  * stream sees every rank's rows of that step. */
 int piekv_peer_wait(const int32_t *flags, int32_t world, int32_t step, int32_t *err, void *stream);
+/* The same wait with the step number taken from the device word `step_counter`, which is incremented
+ * afterwards: [piekv_decode_step_fused_peer with step_counter, piekv_peer_wait_counted] can be captured
+ * in a CUDA graph once and replayed for every step. */
+int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_counter, int32_t *err,
+                            void *stream);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */
 

@@ -58,6 +58,8 @@ class PeerOutputsC(C.Structure):
         ("rank", C.c_int32),
         ("row_heads", C.c_int32),
         ("step", C.c_int32),
+        ("step_counter", C.c_void_p),
+        ("out_alt", C.c_void_p * MAX_PEERS),
     ]
 
 
@@ -109,6 +111,7 @@ SIGNATURES = {
          _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p],
     ),
     "piekv_peer_wait": (C.c_int, [_p, _i32, _i32, _p, _p]),
+    "piekv_peer_wait_counted": (C.c_int, [_p, _i32, _p, _p, _p]),
     "piekv_pages_create": (C.c_void_p, [_i32]),
     "piekv_pages_destroy": (None, [_p]),
     "piekv_pages_available": (_i32, [_p]),

@@ -26,6 +26,8 @@ struct AttnArgs {
 // (own GPU included), mapped into this process; `flag[d]` is this GPU's word in GPU d's flag array.
 struct PeerOut {
   void *dst[8];
+  void *dst_alt[8];     // used for even step numbers when the step is read from `step_ptr`
+  const int *step_ptr;  // nullable: device word holding the step number (graph replays), else `step`
   int *flag[8];
   int n;          // 0: not used
   int row_heads;  // query heads per output row at the destinations (all GPUs' heads)

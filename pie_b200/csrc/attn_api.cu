@@ -184,7 +184,13 @@ extern "C" int piekv_decode_step_fused_peer(const void *q, const void *k, const 
   po.row_heads = peers->row_heads;
   po.head_off = peers->rank * num_qo_heads;
   po.step = peers->step;
+  po.step_ptr = peers->step_counter;
   for (int d = 0; d < peers->world; ++d) {
+    if (peers->step_counter != nullptr) {
+      PIEKV_REQUIRE(peers->out_alt[d] != nullptr && (reinterpret_cast<uintptr_t>(peers->out_alt[d]) & 15) == 0,
+                    "decode_step_fused_peer: out_alt of rank %d is null or not 16-byte aligned", d);
+      po.dst_alt[d] = peers->out_alt[d];
+    }
     PIEKV_REQUIRE(peers->out[d] != nullptr && peers->flags[d] != nullptr, "decode_step_fused_peer: null pointer for rank %d", d);
     PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(peers->out[d]) & 15) == 0, "decode_step_fused_peer: output of rank %d not 16-byte aligned", d);
     po.dst[d] = peers->out[d];

@@ -148,6 +148,15 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint64
   }
 }
 
+// One 32-bit word of global memory that another kernel (or GPU) may just have written.  Always an
+// explicit .global load inside the caller's own branch: folding "pointer or kernel parameter" into
+// one generic volatile load would read parameter space through a generic address, which faults.
+__device__ __forceinline__ int ld_global_relaxed_sys(const int *p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

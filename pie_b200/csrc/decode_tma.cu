@@ -212,9 +212,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_dst = p.peer.n > 0 ? p.peer.n : 1;
   const int row_heads = p.peer.n > 0 ? p.peer.row_heads : a.hq;
   const int head_off = p.peer.n > 0 ? p.peer.head_off : 0;
+  // The step number either came with the launch or sits in device memory, where the wait that closes
+  // a step bumps it: a captured graph can then be replayed step after step.  Odd steps use dst, even
+  // steps dst_alt.  Read once per thread here: every input of this kernel is final by now (the
+  // programmatic-dependent-launch waits are above).
+  int peer_step = p.peer.step;
+  if (p.peer.n > 0 && p.peer.step_ptr != nullptr) peer_step = ld_global_relaxed_sys(p.peer.step_ptr);
+  const bool use_alt = p.peer.n > 0 && p.peer.step_ptr != nullptr && (peer_step & 1) == 0;
   auto dst_row = [&](int d, int b_, int qh) -> T * {
-    T *base = reinterpret_cast<T *>(p.peer.n > 0 ? p.peer.dst[d] : a.out);
-    return base + ((size_t)b_ * row_heads + head_off + qh) * kDim;
+    void *pb = a.out;
+    if (p.peer.n > 0) pb = use_alt ? p.peer.dst_alt[d] : p.peer.dst[d];
+    return reinterpret_cast<T *>(pb) + ((size_t)b_ * row_heads + head_off + qh) * kDim;
   };
   // Every CTA passes here exactly once after its last result store.  The CTA that arrives last
   // publishes this step's number in every GPU's flag array: all stores of this launch, fenced at
@@ -230,7 +238,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         atomicExch(p.peer.done, 0);  // ready for the next launch
         __threadfence_system();
         for (int d = 0; d < p.peer.n; ++d)
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(p.peer.step) : "memory");
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(peer_step) : "memory");
       }
     }
   };

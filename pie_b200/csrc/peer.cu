@@ -6,20 +6,29 @@
 namespace piekv {
 namespace {
 
-__global__ void peer_wait_kernel(const int32_t *flags, int world, int step, int32_t *err) {
+// step_ptr != nullptr: the step number is read from device memory and, once every flag has reached it,
+// incremented for the next launch (so that a captured graph of [decode step, wait] can be replayed).
+__global__ void peer_wait_kernel(const int32_t *flags, int world, int step_arg, int32_t *step_ptr, int32_t *err) {
   const int r = threadIdx.x;
-  if (r >= world) return;
-  const uint64_t t0 = global_timer_ns();
-  for (;;) {
-    int32_t v;
-    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
-    if (v - step >= 0) return;  // step numbers only grow (wrap-safe comparison)
-    if (global_timer_ns() - t0 > 2000000000ull) {
-      report_error(err, PIEKV_ERR_WAIT_TIMEOUT, KID_PEER, r, v);
-      return;
+  int step = step_arg;
+  if (step_ptr != nullptr) step = ld_global_relaxed_sys(step_ptr);
+  __syncwarp();  // every lane has read the counter before lane 0 rewrites it below
+  if (r < world) {
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+      int32_t v;
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      if (v - step >= 0) break;  // step numbers only grow (wrap-safe comparison)
+      if (global_timer_ns() - t0 > 2000000000ull) {
+        report_error(err, PIEKV_ERR_WAIT_TIMEOUT, KID_PEER, r, v);
+        break;
+      }
+      __nanosleep(200);
     }
-    __nanosleep(200);
   }
+  __syncwarp();
+  if (r == 0 && step_ptr != nullptr)
+    asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(step_ptr), "r"(step + 1) : "memory");
 }
 
 }  // namespace
@@ -67,7 +76,16 @@ extern "C" int piekv_peer_free(void *ptr) {
 
 extern "C" int piekv_peer_wait(const int32_t *flags, int32_t world, int32_t step, int32_t *err, void *stream) {
   PIEKV_REQUIRE(flags != nullptr && world >= 1 && world <= PIEKV_MAX_PEERS, "peer_wait: bad arguments");
-  piekv::peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, step, err);
+  piekv::peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, step, nullptr, err);
+  PIEKV_LAUNCH_CHECK("peer_wait_kernel");
+  return 0;
+}
+
+extern "C" int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_counter, int32_t *err,
+                                       void *stream) {
+  PIEKV_REQUIRE(flags != nullptr && step_counter != nullptr && world >= 1 && world <= PIEKV_MAX_PEERS,
+                "peer_wait_counted: bad arguments");
+  piekv::peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, world, 0, step_counter, err);
   PIEKV_LAUNCH_CHECK("peer_wait_kernel");
   return 0;
 }

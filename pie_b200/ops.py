@@ -504,12 +504,18 @@ class BatchDecodeWithPagedKVCacheWrapper:
         return (out, lse) if return_lse else out
 
     def run_fused_peer(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
-                       paged_kv_cache: torch.Tensor, peers, rope: Optional["RopeConfig"] = None) -> torch.Tensor:
+                       paged_kv_cache: torch.Tensor, peers, rope: Optional["RopeConfig"] = None,
+                       counted: bool = False) -> torch.Tensor:
         """`run_fused` for head-sharded ranks (the reference's tensor parallelism,
         pie/src/pie_worker/model/llama3.py:607-610): this rank's heads are stored into the output rows of
         every rank by the kernel itself (`peers`: a `pie_b200.parallel.PeerOutputs`), the wait for the
         other ranks' rows is queued on the stream, and the full [batch, all heads, head_dim] tensor of
-        this rank is returned.  Takes the place of attention followed by an NCCL collective."""
+        this rank is returned.  Takes the place of attention followed by an NCCL collective.
+
+        `counted=True` takes the step number from the device-side counter of `peers` instead of a launch
+        argument, which makes the two launches capturable in a CUDA graph that is replayed step after step;
+        call `peers.advance(n)` after every replay of a graph that holds n such steps (an eager counted
+        call advances by itself).  Do not mix counted and uncounted steps on one `PeerOutputs`."""
         if self._plan is None:
             raise RuntimeError("Must call plan() before run()")
         pl = self._plan
@@ -530,7 +536,7 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError("peer buffers are too small for this plan")
         rp = (rope if rope is not None else RopeConfig()).to_c(d)
         ws = self.workspace_buffer
-        desc = peers.begin_step()
+        desc = peers.counted_descriptor() if counted else peers.begin_step()
         check(lib.piekv_decode_step_fused_peer(q.data_ptr(), k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1],
                                                vs[0], vs[1], pos_ids.data_ptr(), paged_kv_cache.data_ptr(),
                                                C.byref(desc), pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
@@ -539,7 +545,12 @@ class BatchDecodeWithPagedKVCacheWrapper:
                                                C.byref(rp), pl["sm_scale"], ws.data_ptr(), ws.numel(),
                                                _err_word(q.device).data_ptr(), _stream(q.device)),
               "BatchDecode.run_fused_peer")
-        peers.wait()
+        if counted:
+            peers.wait_counted()
+            if not torch.cuda.is_current_stream_capturing():
+                peers.advance()
+        else:
+            peers.wait()
         return peers.full(b)
 
 

@@ -111,6 +111,9 @@ class PeerOutputs:
                 self._base.append(int(q.value))
         self._local = torch.as_tensor(_RawCuda(self._own, self.nbytes), device=self.device)
         self.step = 0
+        self._counter_off = 128  # device-side step counter (graph replays), after the flag words
+        self._local[self._counter_off: self._counter_off + 4].view(torch.int32).fill_(1)
+        torch.cuda.synchronize(self.device)
         dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores
 
     def begin_step(self):
@@ -123,6 +126,31 @@ class PeerOutputs:
             d.flags[r] = self._base[r]
         d.world, d.rank, d.row_heads, d.step = self.world, self.rank, self.row_heads, self.step
         return d
+
+    def counted_descriptor(self):
+        """Descriptor for launches that take the step number from the device-side counter (odd steps use
+        the first output buffer, even steps the second), i.e. for launches captured in a CUDA graph.
+        Every captured or eager use must be followed by `wait_counted()` and `advance()`."""
+        d = self._lib.PeerOutputsC()
+        for r in range(self.world):
+            d.out[r] = self._base[r] + self._off0
+            d.out_alt[r] = self._base[r] + self._off1
+            d.flags[r] = self._base[r]
+        d.world, d.rank, d.row_heads, d.step = self.world, self.rank, self.row_heads, 0
+        d.step_counter = self._own + self._counter_off
+        return d
+
+    def wait_counted(self) -> None:
+        """Queue the wait for the step the device counter names; it increments the counter afterwards."""
+        from .ops import _err_word, _stream
+        self._lib.check(self._lib.lib.piekv_peer_wait_counted(self._own, self.world, self._own + self._counter_off,
+                                                              _err_word(self.device).data_ptr(),
+                                                              _stream(self.device)), "peer_wait_counted")
+
+    def advance(self, steps: int = 1) -> None:
+        """Tell the host mirror that `steps` counted steps have been queued (once per graph replay of that
+        many steps), so that `full()` names the buffer of the latest one."""
+        self.step += int(steps)
 
     def wait(self) -> None:
         """Queue, on the current stream, the wait for every rank's flag of the current step."""

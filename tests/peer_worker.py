@@ -38,6 +38,7 @@ def main() -> None:
     pool_r = pool[:, :, :, ks, :].contiguous()
     pool_full = pool.clone()
     peers = PeerOutputs(batch, hq, 128, dt, dev)
+    peers_counted = PeerOutputs(batch, hq, 128, dt, dev)   # a second set: counted and uncounted steps do not mix
     w_full = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
     w_full.plan(ptr, idx, last, hq, hkv, 128, 16, q_data_type=dt)
     ws_r = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
@@ -58,6 +59,36 @@ def main() -> None:
         sums = [None] * world
         dist.all_gather_object(sums, int(got.view(torch.int16).to(torch.int64).sum().item()))
         assert len(set(sums)) == 1, sums
+    # the same two launches captured once and replayed: the step number then lives in device memory
+    pc = peers_counted
+    q = W.randn((batch, hq, 128), 99, dt, 0.5, device=dev)
+    k = W.randn((batch, hkv, 128), 98, dt, 0.5, device=dev)
+    v = W.randn((batch, hkv, 128), 97, dt, 0.5, device=dev)
+    q_r, k_r, v_r = q[:, qs].contiguous(), k[:, ks].contiguous(), v[:, ks].contiguous()
+    want = w_full.run_fused(q, k, v, pos, pool_full, rope=rope).clone()
+    side = torch.cuda.Stream(device=dev)
+    torch.cuda.synchronize(dev)
+    with torch.cuda.stream(side):
+        w_r.run_fused_peer(q_r, k_r, v_r, pos, pool_r, pc, rope=rope, counted=True)  # eager: advances by itself
+    side.synchronize()
+    assert pc.step == 1
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for _ in range(3):
+            w_r.run_fused_peer(q_r, k_r, v_r, pos, pool_r, pc, rope=rope, counted=True)
+    for rep in range(4):
+        g.replay()
+        pc.advance(3)
+        torch.cuda.synchronize(dev)
+        assert ops.device_error(dev) is None
+        got = pc.full(batch)
+        diff = (got.float() - want.float()).abs().max().item()
+        assert diff <= 4e-3, f"rank {rank} graph replay {rep}: max diff {diff}"
+    assert pc.step == 1 + 12
+    dist.barrier()
+    flags = pc._local[: 4 * world].view(torch.int32).tolist()
+    assert flags == [pc.step] * world, flags
+    pc.close()
     peers.close()
     print("PEER-OK", rank, flush=True)
     dist.destroy_process_group()
