@@ -310,6 +310,10 @@ int piekv_peer_wait(const int32_t *flags, int32_t world, int32_t step, int32_t *
 int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_counter, int32_t *err,
                             void *stream);
 
+/* sizeof of the structs that cross this boundary, for bindings to check their mirrors against:
+ * which = 0: piekv_rope_params, 1: piekv_peer_outputs; anything else: -1. */
+int32_t piekv_abi_sizeof(int32_t which);
+
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */
 
 /* For every pair j and every layer l: pool_l[dst[j], :, :valid_j] = pool_l[src[j], :, :valid_j]

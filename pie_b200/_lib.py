@@ -125,6 +125,7 @@ SIGNATURES = {
     "piekv_pages_export": (C.c_int, [_p, C.c_uint64, _p, _i32, C.c_char_p]),
     "piekv_pages_import": (_i32, [_p, C.c_char_p, _p, _i32]),
     "piekv_pages_release_exported": (C.c_int, [_p, C.c_char_p]),
+    "piekv_abi_sizeof": (_i32, [_i32]),
     "piekv_prefill_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32, _i32, _i64]),
     "piekv_prefill_plan": (
         C.c_int,

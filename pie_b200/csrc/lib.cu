@@ -48,4 +48,10 @@ extern "C" int piekv_set_option(int32_t key, int32_t value) {
 
 extern "C" int piekv_version(void) { return PIEKV_VERSION; }
 
+extern "C" int32_t piekv_abi_sizeof(int32_t which) {
+  if (which == 0) return (int32_t)sizeof(piekv_rope_params);
+  if (which == 1) return (int32_t)sizeof(piekv_peer_outputs);
+  return -1;
+}
+
 extern "C" const char *piekv_last_error_string(void) { return piekv::g_err; }

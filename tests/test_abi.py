@@ -76,3 +76,12 @@ def test_ops_reject_cpu_tensors_like_the_reference_facade():
         ops.apply_rope_pos_ids_inplace(q, q, i[:2])
     with pytest.raises(ValueError, match="NHD"):
         ops.append_paged_kv_cache(q, q, i, i, torch.zeros(1, 2, 16, 4, 64), i, i, i, kv_layout="HND")
+
+
+def test_struct_mirrors_have_the_size_the_library_reports():
+    import ctypes as C
+
+    from pie_b200 import _lib
+    assert _lib.lib.piekv_abi_sizeof(0) == C.sizeof(_lib.RopeParams)
+    assert _lib.lib.piekv_abi_sizeof(1) == C.sizeof(_lib.PeerOutputsC)
+    assert _lib.lib.piekv_abi_sizeof(99) == -1
