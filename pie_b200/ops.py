@@ -401,7 +401,8 @@ class BatchDecodeWithPagedKVCacheWrapper:
         if pos_encoding_mode != "NONE":
             raise ValueError("pos_encoding_mode other than 'NONE' is not supported; apply RoPE before the append")
         if window_left != -1 or (logits_soft_cap not in (None, 0.0)):
-            raise ValueError("window_left / logits_soft_cap are not supported")
+            raise ValueError("window_left / logits_soft_cap are not supported by the decode wrapper "
+                             "(a sliding window is available through BatchPrefillWithPagedKVCacheWrapper)")
         if num_qo_heads % num_kv_heads != 0:
             raise ValueError(f"num_qo_heads {num_qo_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if kv_data_type is not None and kv_data_type != q_data_type:
@@ -461,14 +462,8 @@ class BatchDecodeWithPagedKVCacheWrapper:
 
     forward = run
 
-    def run_fused(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
-                  paged_kv_cache: torch.Tensor, rope: Optional["RopeConfig"] = None,
-                  out: Optional[torch.Tensor] = None, return_lse: bool = False):
-        """One decode step in a single launch: RoPE of q and of the new k at `pos_ids`, append of k / v
-        into the last slot of every request's last page, attention over all pages.  Equivalent to the
-        reference's per-layer sequence at pie/src/pie_worker/model/llama3.py:660-689, except that q and
-        k are read only (not rotated in place).  The planned page table must already include the new
-        token, as it does in the reference."""
+    def _fused_inputs(self, q, k, v, pos_ids, paged_kv_cache):
+        """Checks shared by the fused entry points; returns (plan, num_pages, d, batch, q / k / v row strides)."""
         if self._plan is None:
             raise RuntimeError("Must call plan() before run()")
         pl = self._plan
@@ -483,6 +478,17 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError(f"q {tuple(q.shape)} / k {tuple(k.shape)} / v {tuple(v.shape)} differ from the plan")
         if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
             raise ValueError("paged_kv_cache shape differs from the plan")
+        return pl, num_pages, d, b, qs, ks, vs
+
+    def run_fused(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
+                  paged_kv_cache: torch.Tensor, rope: Optional["RopeConfig"] = None,
+                  out: Optional[torch.Tensor] = None, return_lse: bool = False):
+        """One decode step in a single launch: RoPE of q and of the new k at `pos_ids`, append of k / v
+        into the last slot of every request's last page, attention over all pages.  Equivalent to the
+        reference's per-layer sequence at pie/src/pie_worker/model/llama3.py:660-689, except that q and
+        k are read only (not rotated in place).  The planned page table must already include the new
+        token, as it does in the reference."""
+        pl, num_pages, d, b, qs, ks, vs = self._fused_inputs(q, k, v, pos_ids, paged_kv_cache)
         if not (q.dtype == k.dtype == v.dtype == paged_kv_cache.dtype):
             raise ValueError("q, k, v and the cache must share one dtype")
         if out is None:
@@ -516,20 +522,7 @@ class BatchDecodeWithPagedKVCacheWrapper:
         argument, which makes the two launches capturable in a CUDA graph that is replayed step after step;
         call `peers.advance(n)` after every replay of a graph that holds n such steps (an eager counted
         call advances by itself).  Do not mix counted and uncounted steps on one `PeerOutputs`."""
-        if self._plan is None:
-            raise RuntimeError("Must call plan() before run()")
-        pl = self._plan
-        for t, name in ((q, "q"), (k, "k"), (v, "v")):
-            _require_cuda(t, name)
-        _require_i32(pos_ids, "pos_ids")
-        num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
-        qs, ks, vs = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
-        b = pl["batch"]
-        if tuple(q.shape) != (b, pl["hq"], pl["d"]) or tuple(k.shape) != (b, pl["hkv"], pl["d"]) \
-                or tuple(v.shape) != tuple(k.shape) or pos_ids.shape[0] < b:
-            raise ValueError(f"q {tuple(q.shape)} / k {tuple(k.shape)} / v {tuple(v.shape)} differ from the plan")
-        if (page_size, hkv, d) != (pl["page_size"], pl["hkv"], pl["d"]):
-            raise ValueError("paged_kv_cache shape differs from the plan")
+        pl, num_pages, d, b, qs, ks, vs = self._fused_inputs(q, k, v, pos_ids, paged_kv_cache)
         if not (q.dtype == k.dtype == v.dtype == paged_kv_cache.dtype == peers.dtype):
             raise ValueError("q, k, v, the cache and the peer buffers must share one dtype")
         if b > peers.batch_max or d != peers.head_dim or pl["hq"] * peers.world > peers.row_heads:
@@ -587,8 +580,10 @@ class BatchPrefillWithPagedKVCacheWrapper:
         _require_i32(paged_kv_last_page_len, "paged_kv_last_page_len")
         if pos_encoding_mode != "NONE":
             raise ValueError("pos_encoding_mode other than 'NONE' is not supported; apply RoPE before the append")
-        if window_left != -1 or (logits_soft_cap not in (None, 0.0)):
-            raise ValueError("window_left / logits_soft_cap are not supported")
+        if logits_soft_cap not in (None, 0.0):
+            raise ValueError("logits_soft_cap is not supported")
+        if window_left < -1:
+            raise ValueError("window_left must be -1 (no window) or >= 0")
         if packed_custom_mask is not None:
             raise ValueError("packed_custom_mask is not supported; pass the boolean custom_mask")
         if head_dim_vo is not None and head_dim_vo != head_dim_qk:
@@ -620,6 +615,27 @@ class BatchPrefillWithPagedKVCacheWrapper:
             if run_indptr.shape[0] < 1:
                 raise ValueError("brle indptr must have nnz + 1 entries")
             brle = (runs, run_indptr, int(mask_bits))
+            causal = False
+        if window_left >= 0:
+            # Sliding window (query at position p sees keys p - window_left .. p; the other model families of
+            # the reference plan their wrappers this way, e.g. pie/src/pie_worker/model/olmo3.py:979-1012):
+            # expressed as three runs per query token - attend 0, skip `start`, attend the window - built
+            # with a few device ops, then expanded to the packed mask by the library.  kv tiles outside every
+            # window of a query tile are skipped by the kernel through the mask summary.
+            if custom_mask is not None or brle_mask is not None:
+                raise ValueError("window_left cannot be combined with an explicit mask")
+            if page_size != 16 or head_dim_qk != 128 or q_data_type not in (torch.float16, torch.bfloat16):
+                raise ValueError("window_left needs the tensor-core prefill path (fp16/bf16, head_dim 128, page size 16)")
+            counts = (qo_indptr[1:] - qo_indptr[:-1]).to(torch.int64)
+            seq = get_seq_lens(paged_kv_indptr, paged_kv_last_page_len, page_size).to(torch.int64)
+            n_tok = int(qo_indptr[-1].item())  # plan() is a host-synchronous call in the reference as well
+            req = torch.repeat_interleave(torch.arange(counts.numel(), device=counts.device), counts, output_size=n_tok)
+            j = torch.arange(n_tok, device=counts.device) - qo_indptr[:-1].to(torch.int64)[req]
+            pos = seq[req] - counts[req] + j
+            start = torch.clamp(pos - int(window_left), min=0)
+            runs = torch.stack([torch.zeros_like(start), start, pos + 1 - start], dim=1).to(torch.int32).contiguous()
+            run_indptr = (torch.arange(n_tok + 1, device=counts.device, dtype=torch.int64) * 3).to(torch.int32)
+            brle = (runs.view(-1), run_indptr, int((counts * seq).sum().item()))
             causal = False
         batch = qo_indptr.shape[0] - 1
         self._plan = dict(qo_indptr=qo_indptr, indptr=paged_kv_indptr, indices=paged_kv_indices,
