@@ -288,7 +288,8 @@ typedef struct piekv_peer_outputs {
 
 /* piekv_decode_step_fused with the results of this rank's heads written to columns
  * [rank * num_qo_heads, (rank + 1) * num_qo_heads) of out[r] for every r, then flags[r][rank] = step.
- * Use two alternating output buffers: a rank may start step s + 1 while another still reads step s. */
+ * Use two alternating output buffers: a rank may start step s + 1 while another still reads step s.
+ * batch == 0 launches nothing and raises no flag: do not consume a step number or wait for it. */
 int piekv_decode_step_fused_peer(const void *q, const void *k, const void *v, int64_t q_stride_n,
                                  int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
                                  int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids,

@@ -31,6 +31,21 @@ int cuda_status(cudaError_t e, const char *what);  // 0 or -(int)e, records text
   } while (0)
 
 int sm_count();  // multiprocessors of the current device (cached per device)
+int current_device_slot();  // ordinal of the current device if it is in [0, kMaxDevices), else -1
+constexpr int kMaxDevices = 64;
+
+// The dynamic-shared-memory opt-in of a kernel belongs to one device (context), so it is made once per
+// device ordinal, not once per process.  `done` is the caller's static table for that kernel
+// instantiation; atomic byte accesses keep two host threads from tearing a flag (a doubled opt-in is harmless).
+template <typename Kernel>
+int opt_in_dynamic_smem(Kernel kernel, int bytes, unsigned char *done, const char *what) {
+  const int dev = current_device_slot();
+  if (dev >= 0 && __atomic_load_n(&done[dev], __ATOMIC_ACQUIRE)) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return ::piekv::cuda_status(e, what);
+  if (dev >= 0) __atomic_store_n(&done[dev], (unsigned char)1, __ATOMIC_RELEASE);
+  return 0;
+}
 int get_option(int key);  // library options set through piekv_set_option
 
 inline int dtype_size(int dtype) { return dtype == PIEKV_F32 ? 4 : 2; }

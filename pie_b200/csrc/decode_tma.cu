@@ -660,14 +660,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 
 template <typename T, int HKV, bool FUSED>
 int launch_t(const CUtensorMap &tm, const DecodeParams &p, const FusedArgs &f, cudaStream_t st) {
-  static bool configured = false;  // per instantiation
+  static unsigned char configured[kMaxDevices] = {0};  // per instantiation and device
   const int smem = kStages * kStageBytes + 1024;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_tma_kernel<T, HKV, FUSED>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return cuda_status(e, "decode: cudaFuncSetAttribute");
-    configured = true;
-  }
+  if (int rc = opt_in_dynamic_smem(decode_tma_kernel<T, HKV, FUSED>, smem, configured, "decode: cudaFuncSetAttribute"))
+    return rc;
   if (p.pdl == 0) {
     decode_tma_kernel<T, HKV, FUSED><<<sm_count(), kThreads, smem, st>>>(tm, p, f);
     PIEKV_LAUNCH_CHECK("decode_tma_kernel");
@@ -860,12 +856,14 @@ extern "C" int piekv_decode_run_noalloc(const void *q, int64_t q_stride_n, int64
   a.sm_scale = sm_scale;
   a.err = err;
   cudaStream_t st = (cudaStream_t)stream;
-  if (!decode_tma_supported(a, dtype)) return launch_attn_generic(a, dtype, st);  // that kernel needs no scratch
+  // The size limit is checked before a kernel is chosen, so that which sizes are accepted does not depend
+  // on the dtype or alignment of a call (the general kernel below happens to need no scratch).
   const int64_t need = decode_tma_workspace_bytes(batch, num_qo_heads, num_kv_heads);
   PIEKV_REQUIRE(need <= kStaticScratchBytes,
                 "decode_run_noalloc: batch %d with %d query heads needs %lld bytes of scratch, the built-in "
                 "scratch holds %lld; use piekv_decode_run with a caller workspace",
                 batch, num_qo_heads, (long long)need, (long long)kStaticScratchBytes);
+  if (!decode_tma_supported(a, dtype)) return launch_attn_generic(a, dtype, st);
   void *scratch = nullptr;
   if (int rc = static_scratch_ptr(&scratch)) return rc;
   // the arrival counters must be zero when the kernel starts, whatever an earlier call left behind

@@ -21,6 +21,12 @@ int cuda_status(cudaError_t e, const char *what) {
   return -(int)e;
 }
 
+int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
 int sm_count() {
   static int cached[64] = {0};
   int dev = 0;

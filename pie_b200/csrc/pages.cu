@@ -218,6 +218,12 @@ extern "C" int piekv_pages_export(piekv_page_manager *m, uint64_t instance, cons
     PIEKV_REQUIRE(pages[i] >= 0 && it->second.pages.count((uint32_t)pages[i]),
                   "pages_export: page %d is not allocated to instance %llu", pages[i], (unsigned long long)instance);
   PIEKV_REQUIRE(!m->exported.count(name), "pages_export: export name '%s' exists", name);
+  {
+    // A page listed twice would be released twice later and take a co-holder's reference with it.
+    std::unordered_set<uint32_t> seen;
+    for (int32_t i = 0; i < count; ++i)
+      PIEKV_REQUIRE(seen.insert((uint32_t)pages[i]).second, "pages_export: page %d is listed twice", pages[i]);
+  }
   std::vector<uint32_t> v;
   for (int32_t i = 0; i < count; ++i) {
     it->second.pages.erase((uint32_t)pages[i]);  // ownership (and the reference) moves to the name

@@ -767,13 +767,9 @@ int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, 
 template <typename T>
 static int launch_prefill_t(const AttnArgs &a, const CUtensorMap &tq, const CUtensorMap &tkv, const PrefillParams &p,
                             int max_tiles, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(prefill_tc_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-    if (e != cudaSuccess) return cuda_status(e, "prefill: cudaFuncSetAttribute");
-    configured = true;
-  }
+  static unsigned char configured[kMaxDevices] = {0};
+  if (int rc = opt_in_dynamic_smem(prefill_tc_kernel<T>, kSmemBytes, configured, "prefill: cudaFuncSetAttribute"))
+    return rc;
   const long long blocks = (long long)max_tiles * a.hq;
   PIEKV_REQUIRE(blocks < (1ll << 31), "prefill: too many tiles");
   prefill_tc_kernel<T><<<(unsigned)blocks, kThreads, kSmemBytes, st>>>(tq, tkv, p);

@@ -486,13 +486,10 @@ __global__ void __launch_bounds__(k2Threads, 1)
 template <typename T>
 int launch_t(const AttnArgs &a, const CUtensorMap &tq, const CUtensorMap &tkv, const PrefillParams &p, int max_tiles,
              cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e =
-        cudaFuncSetAttribute(prefill_tc2_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, k2SmemBytes);
-    if (e != cudaSuccess) return cuda_status(e, "prefill (two heads): cudaFuncSetAttribute");
-    configured = true;
-  }
+  static unsigned char configured[kMaxDevices] = {0};
+  if (int rc = opt_in_dynamic_smem(prefill_tc2_kernel<T>, k2SmemBytes, configured,
+                                   "prefill (two heads): cudaFuncSetAttribute"))
+    return rc;
   const long long blocks = (long long)max_tiles * (a.hq / 2);
   PIEKV_REQUIRE(blocks < (1ll << 31), "prefill: too many tiles");
   prefill_tc2_kernel<T><<<(unsigned)blocks, k2Threads, k2SmemBytes, st>>>(tq, tkv, p);

@@ -76,6 +76,15 @@ def _dtype_code(dt: torch.dtype, name: str) -> int:
 
 
 def _stream(device: torch.device) -> int:
+    """Stream handle for a launch on `device`.  The library launches on the CURRENT CUDA device (and looks
+    its SM count and built-in scratch up for that device), so tensors of another GPU are refused instead of
+    being paired with a foreign stream.  The reference worker pins one device per process
+    (pie/src/pie_worker/model/llama3.py:732-733)."""
+    cur = torch.cuda.current_device()
+    idx = device.index if device.index is not None else cur
+    if idx != cur:
+        raise ValueError(f"tensors live on cuda:{idx} but the current CUDA device is cuda:{cur}; "
+                         f"call torch.cuda.set_device({idx}) (or use `with torch.cuda.device({idx})`) first")
     return torch.cuda.current_stream(device).cuda_stream
 
 
@@ -527,6 +536,10 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError("q, k, v, the cache and the peer buffers must share one dtype")
         if b > peers.batch_max or d != peers.head_dim or pl["hq"] * peers.world > peers.row_heads:
             raise ValueError("peer buffers are too small for this plan")
+        if b == 0:
+            # Nothing would be launched, so no flag would be raised: every rank (they share the page tables)
+            # skips the step number and the wait instead of spinning until the wait's time limit.
+            return peers.full(0)
         rp = (rope if rope is not None else RopeConfig()).to_c(d)
         ws = self.workspace_buffer
         desc = peers.counted_descriptor() if counted else peers.begin_step()

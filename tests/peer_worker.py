@@ -13,6 +13,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from pie_b200 import ops  # noqa: E402
 from pie_b200 import workloads as W  # noqa: E402
 from pie_b200.parallel import PeerOutputs, shard_heads  # noqa: E402
+from tests.util import oracle_decode_after_append  # noqa: E402
 
 
 def main() -> None:
@@ -55,6 +56,10 @@ def main() -> None:
         assert ops.device_error(dev) is None
         diff = (got.float() - want.float()).abs().max().item()
         assert diff <= 4e-3, f"rank {rank} step {step}: max diff {diff}"
+        if step == 0:  # the gathered rows against the CPU oracle, once (it takes a second per rank)
+            ref = oracle_decode_after_append(q, pos, pool_full, ptr, idx, last)
+            odiff = (got.cpu().float() - ref.float()).abs().max().item()
+            assert odiff <= 2e-2, f"rank {rank}: max diff to the oracle {odiff}"
         # every rank holds the same bits: compare a checksum of the gathered rows across ranks
         sums = [None] * world
         dist.all_gather_object(sums, int(got.view(torch.int16).to(torch.int64).sum().item()))

@@ -85,3 +85,17 @@ def test_struct_mirrors_have_the_size_the_library_reports():
     assert _lib.lib.piekv_abi_sizeof(0) == C.sizeof(_lib.RopeParams)
     assert _lib.lib.piekv_abi_sizeof(1) == C.sizeof(_lib.PeerOutputsC)
     assert _lib.lib.piekv_abi_sizeof(99) == -1
+
+
+def test_ops_refuse_tensors_of_a_device_that_is_not_current(monkeypatch):
+    """The library launches on the current CUDA device; tensors of another GPU must raise instead of being
+    paired with a foreign stream.  Checked on the host with the two torch queries replaced."""
+    class FakeStream:
+        cuda_stream = 0
+
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda device=None: FakeStream())
+    assert ops._stream(torch.device("cuda", 0)) == 0
+    assert ops._stream(torch.device("cuda")) == 0
+    with pytest.raises(ValueError, match="current CUDA device"):
+        ops._stream(torch.device("cuda", 1))

@@ -128,3 +128,64 @@ def test_library_against_dependency_outputs(name):
     got = _t(name, "prefill_masked_out", sc.dtype, sc.q.shape)
     assert (out.cpu().float() - got.float()).abs().max().item() <= 2e-2
     assert ops.device_error("cuda") is None
+
+
+@pytest.mark.gpu
+def test_library_against_the_dependency_run_live():
+    """When the reference's CUDA dependency is importable on this machine, run the reference's call sequence
+    (pie/src/pie_worker/model/llama3.py:660-689,745-777) live on a config-2-shaped batch and compare this
+    library's results on the same inputs: metadata exact, appended pool bit-exact, decode outputs within 2e-2.
+    The dependency is only called, never read."""
+    try:
+        import flashinfer
+    except Exception as e:  # not installed, or not importable without its build tools
+        pytest.skip(f"flashinfer is not importable here: {type(e).__name__}")
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+
+    hq, hkv, d, batch, pages = 32, 8, 128, 64, 16384
+    dt = torch.bfloat16
+    reqs = W.config2_requests(batch=batch, lo=512, hi=2048, seed=1, num_pages=pages)
+    m = W.decode_steps(reqs, 1)[0]
+    pool = W.randn((pages, 2, 16, hkv, d), 61, dt, 0.5, device="cuda")
+    q = W.randn((batch, hq, d), 62, dt, 0.5, device="cuda")
+    k = W.randn((batch, hkv, d), 63, dt, 0.5, device="cuda")
+    v = W.randn((batch, hkv, d), 64, dt, 0.5, device="cuda")
+    indptr, indices, last, qo, pos_ids = dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), \
+        dev(m.qo_indptr), dev(m.pos_ids)
+    ws_f = torch.zeros(128 << 20, dtype=torch.uint8, device="cuda")
+    try:
+        fq, fk, fpool = q.clone(), k.clone(), pool.clone()
+        fseq = flashinfer.get_seq_lens(indptr, last, 16)
+        fbi, fkp = flashinfer.get_batch_indices_positions(qo, fseq, batch)
+        flashinfer.apply_llama31_rope_pos_ids_inplace(q=fq, k=fk, pos_ids=pos_ids, rope_scale=8.0, rope_theta=5e5,
+                                                      low_freq_factor=1.0, high_freq_factor=4.0, old_context_len=8192)
+        flashinfer.append_paged_kv_cache(append_key=fk, append_value=v, batch_indices=fbi, positions=fkp,
+                                         paged_kv_cache=fpool, kv_indices=indices, kv_indptr=indptr,
+                                         kv_last_page_len=last, kv_layout="NHD")
+        fw = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws_f, "NHD")
+        fw.plan(indptr=indptr, indices=indices, last_page_len=last, num_qo_heads=hq, num_kv_heads=hkv, head_dim=d,
+                page_size=16, pos_encoding_mode="NONE", q_data_type=dt)
+        fout = fw.run(fq, fpool)
+        torch.cuda.synchronize()
+    except Exception as e:  # e.g. no compiler for its kernels on this machine
+        pytest.skip(f"flashinfer could not run here: {type(e).__name__}: {str(e)[:120]}")
+    seq = ops.get_seq_lens(indptr, last, 16)
+    bi, kp = ops.get_batch_indices_positions(qo, seq, batch)
+    assert torch.equal(seq, fseq.to(seq.dtype)) and torch.equal(bi, fbi.to(bi.dtype)) and torch.equal(kp, fkp.to(kp.dtype))
+    mq, mk = q.clone(), k.clone()
+    ops.apply_llama31_rope_pos_ids_inplace(mq, mk, pos_ids)
+    _rope_close(mq.cpu(), fq.cpu(), q.cpu())
+    _rope_close(mk.cpu(), fk.cpu(), k.cpu())
+    mpool = pool.clone()
+    ops.append_paged_kv_cache(fk, v, bi, kp, mpool, indices, indptr, last)  # the dependency's k: data movement only
+    assert torch.equal(mpool.view(torch.int16), fpool.view(torch.int16))
+    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+    w.plan(indptr, indices, last, hq, hkv, d, 16, q_data_type=dt)
+    out = w.run(fq, fpool)
+    assert (out.float() - fout.float()).abs().max().item() <= 2e-2
+    # and the fused step against the dependency's three separate ops
+    fused = w.run_fused(q, k, v, pos_ids, pool.clone(), ops.RopeConfig())
+    assert (fused.float() - fout.float()).abs().max().item() <= 2e-2
+    assert ops.device_error("cuda") is None

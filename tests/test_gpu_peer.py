@@ -19,7 +19,7 @@ import torch
 from pie_b200 import _lib, ops
 from pie_b200 import workloads as W
 from pie_b200.parallel import peer_layout, shard_heads
-from tests.util import dev
+from tests.util import dev, oracle_decode_after_append
 
 pytestmark = pytest.mark.gpu
 
@@ -52,6 +52,8 @@ def test_peer_stores_emulated_ranks_equal_unsharded_step(world):
     w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
     w.plan(ptr, idx, last, hq, hkv, 128, 16, q_data_type=torch.bfloat16)
     want = w.run_fused(q, k, v, pos, pool_ref, rope=rope).clone()
+    ref = oracle_decode_after_append(q, pos, pool_ref, ptr, idx, last)   # the CPU oracle on the same step
+    assert (want.cpu().float() - ref.float()).abs().max().item() <= 2e-2
 
     off0, off1, nbytes = peer_layout(batch, hq, 128, 2)
     mem = [torch.zeros(nbytes, dtype=torch.uint8, device="cuda") for _ in range(world)]
@@ -85,6 +87,7 @@ def test_peer_stores_emulated_ranks_equal_unsharded_step(world):
             assert flags == [step] * world
             got = mem[t][off: off + batch * hq * 128 * 2].view(torch.bfloat16).view(batch, hq, 128)
             assert (got.float() - want.float()).abs().max().item() <= 4e-3, (step, t)
+            assert (got.cpu().float() - ref.float()).abs().max().item() <= 2e-2, (step, t)
             assert torch.equal(mem[t][off: off + batch * hq * 128 * 2], mem[0][off: off + batch * hq * 128 * 2])
     # the sharded pools received the same appended rows as the unsharded one
     for r in range(world):
@@ -104,6 +107,46 @@ def test_peer_wait_reports_a_flag_that_never_comes():
     e = err.tolist()
     assert e[0] == _lib.PIEKV_ERR_WAIT_TIMEOUT and e[2] == 1   # rank 1's flag
     assert int((flags + 1).sum().item()) == 64 + 5            # the device still answers
+
+
+def test_empty_batch_raises_no_flag_and_the_wrapper_skips_the_wait():
+    """batch == 0: nothing is launched and no flag is raised, so the Python wrapper must neither take a step
+    number nor queue a wait (which would spin to its time limit on every rank)."""
+    class NoStep:  # stands in for PeerOutputs: any call that would consume a step fails the test
+        dtype, batch_max, head_dim, world, row_heads = torch.bfloat16, 8, 128, 2, 16
+
+        def begin_step(self):
+            raise AssertionError("an empty batch must not take a step number")
+
+        counted_descriptor = wait = wait_counted = advance = begin_step
+
+        def full(self, batch):
+            return torch.empty((batch, self.row_heads, self.head_dim), dtype=self.dtype, device="cuda")
+
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
+    z = lambda *shape: torch.zeros(shape, dtype=torch.int32, device="cuda")
+    w.plan(z(1), z(1), z(1), 8, 4, 128, 16, q_data_type=torch.bfloat16)
+    pool = torch.zeros((4, 2, 16, 4, 128), dtype=torch.bfloat16, device="cuda")
+    e = lambda h: torch.empty((0, h, 128), dtype=torch.bfloat16, device="cuda")
+    for counted in (False, True):
+        out = w.run_fused_peer(e(8), e(4), e(4), z(1), pool, NoStep(), counted=counted)
+        assert tuple(out.shape) == (0, 16, 128)
+    # the C entry point itself: status 0, flags untouched
+    mem = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    d = _lib.PeerOutputsC()
+    for t in range(2):
+        d.out[t] = mem.data_ptr() + 256
+        d.flags[t] = mem.data_ptr()
+    d.world, d.rank, d.row_heads, d.step = 2, 0, 16, 1
+    rp = ops.RopeConfig().to_c(128)
+    rc = _lib.lib.piekv_decode_step_fused_peer(None, None, None, 1024, 128, 512, 128, 512, 128, None, pool.data_ptr(),
+                                               C.byref(d), None, None, None, 0, 8, 4, 128, 16, 4, _lib.PIEKV_BF16,
+                                               C.byref(rp), 0.1, ws.data_ptr(), ws.numel(), None,
+                                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(mem.view(torch.int32)[:2].abs().sum().item()) == 0
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")

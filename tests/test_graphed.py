@@ -27,6 +27,7 @@ def test_graphed_step_matches_eager_step():
     from pie_b200 import ops
     from pie_b200 import workloads as W
     from pie_b200.graphed import GraphedDecodeStep
+    from tests.util import oracle_decode_after_append
 
     hq, hkv, pages = 32, 8, 2048
     dt = torch.bfloat16
@@ -58,3 +59,6 @@ def test_graphed_step_matches_eager_step():
         assert (got.float() - want.float()).abs().max().item() <= 4e-3, (step, batch)
         # every real page received exactly the bytes of the eager step; only the scratch page may differ
         assert torch.equal(pool[:pages], ref_pool[:pages]), (step, batch)
+        # and the CPU oracle on the pool the replay left behind
+        ref = oracle_decode_after_append(q, pos, pool, ptr, idx, last)
+        assert (got.cpu().float() - ref.float()).abs().max().item() <= 2e-2, (step, batch)

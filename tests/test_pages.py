@@ -175,3 +175,22 @@ def test_native_manager_share_export_import():
     with pytest.raises(ValueError):
         m.free(3, [])                       # an instance that holds nothing (InstanceNotAllocated in the reference)
     m.close()
+
+
+def test_native_export_rejects_a_page_listed_twice():
+    """A duplicate in an export list would be released twice and drop a co-holder's reference."""
+    from pie_b200.pages import NativePageManager
+    m = NativePageManager(8)
+    a, _ = m.alloc(1, 2)
+    p = a[0]
+    m.share(2, [p])
+    assert m.refcount(p) == 2
+    with pytest.raises(ValueError):
+        m.export(1, [p, p], "dup")
+    assert m.refcount(p) == 2 and m.owned(1) == 2  # nothing moved
+    m.export(1, [p], "once")
+    m.release_exported("once")
+    assert m.refcount(p) == 1                     # instance 2 still holds it
+    got, _ = m.alloc(3, 6)
+    assert p not in got                           # and it is not handed out again
+    m.close()

@@ -16,6 +16,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import paged_kv_ref as R
 from pie_b200 import _lib
 from pie_b200 import workloads as W
 from tests.util import dev, make_scenario
@@ -58,12 +59,29 @@ def test_noalloc_matches_workspace_entry_point_twice():
         assert torch.isfinite(b).all()
         assert (a.float() - b.float()).abs().max().item() <= 2e-2  # the tolerance of the other decode tests
         assert torch.equal(a, b)  # same kernel, same partition: the same bits
+        # and both against the CPU oracle, so that a fault the two entry points share cannot hide
+        m = sc.meta
+        ref = R.decode_attention(sc.q, sc.pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len)
+        assert (b.cpu().float() - ref.float()).abs().max().item() <= 2e-2
 
 
 def test_noalloc_rejects_what_does_not_fit():
+    """A batch whose split-KV scratch exceeds the built-in array is refused before anything is launched.
+    Real (small) device buffers are passed, so that the outcome does not hinge on the order of the checks."""
     assert L.piekv_decode_noalloc_max_bytes() == 8 << 20
-    one = 256  # any non-null, aligned value: the size check happens before anything touches memory
-    rc = L.piekv_decode_run_noalloc(one, 4096, 128, one, one, None, one, one, one, 4096, 32, 8, 128, 16, 1 << 20,
-                                    _lib.PIEKV_BF16, 0.1, None, None)
-    assert rc > 0
-    assert b"scratch" in L.piekv_last_error_string()
+    batch = 4096
+    q = torch.zeros((batch, 32, 128), dtype=torch.bfloat16, device="cuda")
+    out = torch.empty_like(q)
+    pool = torch.zeros((4, 2, 16, 8, 128), dtype=torch.bfloat16, device="cuda")
+    indptr = torch.zeros(batch + 1, dtype=torch.int32, device="cuda")  # every request empty
+    indices = torch.zeros(1, dtype=torch.int32, device="cuda")
+    last = torch.ones(batch, dtype=torch.int32, device="cuda")
+    err = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for dtype_code in (_lib.PIEKV_BF16, _lib.PIEKV_F32):  # the tuned and the general kernel's dtypes alike
+        rc = L.piekv_decode_run_noalloc(q.data_ptr(), q.stride(0), q.stride(1), pool.data_ptr(), out.data_ptr(), None,
+                                        indptr.data_ptr(), indices.data_ptr(), last.data_ptr(), batch, 32, 8, 128, 16,
+                                        4, dtype_code, 0.1, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        assert rc > 0
+        assert b"scratch" in L.piekv_last_error_string()
+    torch.cuda.synchronize()
+    assert err.tolist() == [0, 0, 0, 0]

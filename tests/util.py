@@ -68,3 +68,20 @@ def ulp_diff_bf16(a: torch.Tensor, b: torch.Tensor) -> int:
         i = t.contiguous().view(torch.int16).to(torch.int32)
         return torch.where(i < 0, -(i & 0x7FFF), i)
     return int((key(a) - key(b)).abs().max().item()) if a.numel() else 0
+
+
+def oracle_decode_after_append(q, pos_ids, pool_after, indptr, indices, last, rope_mode="llama31", theta=500000.0,
+                               scale=8.0):
+    """CPU-oracle decode attention for a fused step whose append has already happened: rotate q on the CPU
+    (on-the-fly sin / cos, within one rounding step of the device's) and attend over `pool_after`, the pool
+    as the device left it.  All arguments may be device tensors or numpy arrays."""
+    from oracle import paged_kv_ref as R
+
+    def host(x):
+        return x.cpu().numpy() if isinstance(x, torch.Tensor) else np.asarray(x)
+
+    qc = q.detach().cpu()
+    inv = R.rope_inv_freq(qc.shape[-1], theta, rope_mode, scale)
+    c, s = R.rope_cos_sin(host(pos_ids), inv)
+    return R.decode_attention(R.apply_rope(qc, c, s), pool_after.detach().cpu(), host(indptr), host(indices),
+                              host(last))
