@@ -18,9 +18,14 @@ independent page pools and no data-path collective - every rank runs its own 64-
 
 Printed JSON line: metric = decode tokens/s (whole job), `value` with inputs resident in HBM, `e2e`
 through pie_b200.ops with pinned HOST buffers (H2D of the step's q/k/v + metadata and D2H of the
-attention output inside the timed region), `roofline` for the decode-attention kernel (algorithmic
-bytes / CUDA-event time against the measured HBM copy bandwidth), `cpu_baseline` = the CPU oracle on a
-bounded sample.  `--impl reference` times the CPU restatement of the reference path on the host cores.
+attention output inside the timed region), `roofline` for the fused kernel of the timed region (algorithmic
+bytes / CUDA-event time against the measured HBM copy bandwidth; the attention-only variant beside it),
+`cpu_baseline` = the CPU oracle on a bounded sample.  The same line carries sub-records of the secondary
+workloads, measured after the headline's timed region: `head_sharded` (70B-shaped decode, KV heads split
+over the N ranks and joined by the decode kernel's peer stores, with the NCCL all-gather and the one-GPU
+step beside it) at every N, and `prefill` (chunked-prefill mix, tensor-core roofline) and `beam` (beam
+search with shared pages) at N = 1.  `--impl reference` times the CPU restatement of the reference path
+on the host cores; `--impl flashinfer` times the reference's CUDA dependency as a black box.
 """
 from __future__ import annotations
 
@@ -154,6 +159,20 @@ def views(row: torch.Tensor, b: int):
 # ---------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------
+def headline_config(W, requests: int, n_gpus: int, num_pages: int, steps: int, warmup: int) -> dict:
+    """The `config` object of the headline line.  Both arms (this library and `--impl reference`) print
+    exactly this, computed from the same seeded metadata, so that their lines describe one workload."""
+    horizon = min(HORIZON, steps + warmup)
+    cfg = W.CONFIG2
+    metas = W.decode_steps(W.config2_requests(batch=requests, seed=1, num_pages=num_pages, perm_seed=1), horizon)
+    mid = metas[(warmup + steps // 2) % horizon]
+    return {"workload": WORKLOAD, "requests_per_gpu": requests, "global_requests": requests * n_gpus,
+            "pool_pages": num_pages,
+            "parallelism": f"request-sharded x{n_gpus}, independent page pools, no collective",
+            "l2": "inputs larger than L2 (0.6 GB of KV per step vs 126 MB); no flush",
+            "step_algorithmic_bytes": W.decode_step_bytes(mid, cfg)}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -188,9 +207,6 @@ def run_ours(args):
     qkv_host = W.randn((n_var, B, (HQ + 2 * HKV) * D), 200 + rank, cfg.dtype, cfg.value_scale).pin_memory()
     qkv = qkv_host.to(dev)
     out = torch.empty((B, HQ, D), dtype=cfg.dtype, device=dev)
-    seq_lens = torch.empty(B, dtype=torch.int32, device=dev)
-    bidx = torch.empty(B, dtype=torch.int32, device=dev)
-    kvpos = torch.empty(B, dtype=torch.int32, device=dev)
     ws = torch.zeros(64 << 20, dtype=torch.uint8, device=dev)
     err = torch.zeros(4, dtype=torch.int32, device=dev)
     rope = ops.RopeConfig(mode=cfg.rope_mode, theta=cfg.rope_theta, scale=cfg.rope_scale).to_c(D)
@@ -199,7 +215,7 @@ def run_ours(args):
     launches = [0]
     es = 2
 
-    ops.set_programmatic_dependent_launch(2)  # page tables are static inputs here: prologue overlaps the tail
+    ops.set_programmatic_dependent_launch(args.pdl)  # page tables are static inputs here: prologue overlaps the tail
 
     def qkv_views(t):
         q = t[:, : HQ * D].view(B, HQ, D)
@@ -227,7 +243,17 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     # ---- value: device-resident, CUDA graph of exactly `steps` steps -------------------------------
+    # The graph holds the driver's K steps.  It is replayed R times back to back inside ONE event pair so
+    # that the timed region lasts about a quarter of a second whatever K is (clock samples, power state);
+    # steps / ms_per_step stay per step, `timed_replays` = R.
     with torch.cuda.stream(stream):
         for i in range(warmup):
             step_device(i, stream.cuda_stream)
@@ -237,28 +263,33 @@ def run_ours(args):
     with torch.cuda.graph(graph, stream=stream):
         for i in range(steps):
             step_device(warmup + i, torch.cuda.current_stream(dev).cuda_stream)
-    timed_launches = launches[0]
+    graph_launches = launches[0]
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with torch.cuda.stream(stream):
         graph.replay()  # one untimed replay: graph upload + caches
+        p0.record(stream)
+        graph.replay()
+        p1.record(stream)
     barrier()
+    probe_ms = max_over_ranks(p0.elapsed_time(p1))
+    replays = 1 if args.min_timed_ms <= 0 else int(min(4096, max(1, math.ceil(args.min_timed_ms / max(probe_ms, 1e-3)))))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local)
     with sampler:
         barrier()
         with torch.cuda.stream(stream):
             e0.record(stream)
-            graph.replay()
+            for _ in range(replays):
+                graph.replay()
             e1.record(stream)
         barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    value = n_gpus * B * steps / (ms * 1e-3)
+    total_ms = max_over_ranks(e0.elapsed_time(e1))
+    ms_per_step = total_ms / (steps * replays)
+    value = n_gpus * B / (ms_per_step * 1e-3)
+    timed_launches = graph_launches * replays
     errw = err.cpu().tolist()
 
-    # ---- roofline: the decode-attention kernel alone ------------------------------------------------
+    # ---- roofline: the fused kernel is the timed region; the attention-only variant is timed beside it ---
     reps = args.kernel_reps
     mid = metas[(warmup + steps // 2) % horizon]
     mv = views(packed[(warmup + steps // 2) % horizon], B)
@@ -283,14 +314,17 @@ def run_ours(args):
     tokens = int(mid.seq_lens.astype(np.int64).sum())
     kern_bytes = tokens * 2 * HKV * D * es + B * 2 * HQ * D * es + 4 * (len(mid.kv_indices) + 2 * B + 1)
     peak, peak_kind = load_peaks()
-    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
+    attn_achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
     step_bytes = W.decode_step_bytes(mid, cfg)
+    step_achieved = step_bytes / (ms_per_step * 1e-3) / 1e9
 
     # ---- e2e: public Python API, host buffers, H2D + D2H inside the timed region ---------------------
-    # Three streams (upload, compute, download) and three buffer sets: the upload of step i+1 and the
-    # download of step i-1 overlap the kernel of step i; every step still uploads its own q/k/v and page
-    # tables from pinned host memory and downloads its own attention output.
-    e2e_steps = min(steps, 256)
+    # Throughput form: three streams (upload, compute, download) and three buffer sets: the upload of step
+    # i+1 and the download of step i-1 overlap the kernel of step i; every step still uploads its own q/k/v
+    # and page tables from pinned host memory and downloads its own attention output.  The steps are
+    # INDEPENDENT of one another here (a real decode loop feeds step i's output into step i+1's q and cannot
+    # overlap them); the un-pipelined per-step latency is reported beside it.
+    e2e_steps = max(steps, min(2048, int(args.min_timed_ms / 0.15) if args.min_timed_ms > 0 else steps))
     NB = 3
     out_host = [torch.empty((B, HQ, D), dtype=cfg.dtype).pin_memory() for _ in range(NB)]
     out_devs = [torch.empty((B, HQ, D), dtype=cfg.dtype, device=dev) for _ in range(NB)]
@@ -341,12 +375,50 @@ def run_ours(args):
         step_e2e(warmup + i)
     c1.record(s_out)
     barrier()
-    e2e_ms = c0.elapsed_time(c1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = max_over_ranks(c0.elapsed_time(c1))
     e2e_value = n_gpus * B * e2e_steps / (e2e_ms * 1e-3)
+
+    # latency form: one buffer set, one stream, the host waits for the output before it issues the next step
+    lat_steps = min(64, max(8, steps))
+    s_lat = torch.cuda.Stream(dev)
+
+    def step_latency(i: int):
+        with torch.cuda.stream(s_lat):
+            meta_devs[0].copy_(packed_host[i % horizon], non_blocking=True)
+            qkv_devs[0].copy_(qkv_host[i % n_var], non_blocking=True)
+            mv_ = views(meta_devs[0], B)
+            q_, k_, v_ = qkv_views(qkv_devs[0])
+            wrapper.plan(mv_["indptr"], mv_["indices"], mv_["last"], HQ, HKV, D, 16, pos_encoding_mode="NONE",
+                         q_data_type=cfg.dtype)
+            wrapper.run_fused(q_, k_, v_, mv_["pos"], pool, rope_cfg, out=out_devs[0])
+            out_host[0].copy_(out_devs[0], non_blocking=True)
+        s_lat.synchronize()
+
+    for i in range(3):
+        step_latency(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(lat_steps):
+        step_latency(warmup + i)
+    lat_us = max_over_ranks((time.perf_counter() - t0) / lat_steps * 1e6)
+
+    # free the headline's buffers before the secondary workloads allocate theirs
+    del graph, pool, qkv, out_devs, qkv_devs, meta_devs, wrapper
+    torch.cuda.empty_cache()
+
+    # ---- secondary workloads, reported inside the same line (they do not change metric / value) -------
+    sub = {}
+    if not args.no_sub:
+        try:
+            sub["head_sharded"] = measure_head_sharded(world, rank, dev, steps=48, warmup=4)
+        except Exception as e:  # a sub-record must never cost the headline its line
+            sub["head_sharded"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        if world == 1:
+            for name, fn in (("prefill", lambda: prefill_subrecord(dev)), ("beam", lambda: beam_subrecord(dev))):
+                try:
+                    sub[name] = fn()
+                except Exception as e:
+                    sub[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
 
     # ---- cpu baseline (rank 0, N=1 only): the CPU oracle on a bounded sample --------------------------
     cpu = None
@@ -354,30 +426,41 @@ def run_ours(args):
         cpu = cpu_baseline(sample_steps=args.cpu_steps)
 
     if rank == 0:
+        config = headline_config(W, B, n_gpus, cfg.num_pages, steps, warmup)
+        assert config["step_algorithmic_bytes"] == step_bytes  # rank 0 timed exactly the workload it names
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "requests_per_gpu": B, "global_requests": B * n_gpus, "pool_pages": cfg.num_pages,
-                       "parallelism": f"request-sharded x{n_gpus}, independent page pools, no collective",
-                       "l2": "inputs larger than L2 (0.6 GB of KV per step vs 126 MB); no flush",
-                       "launch": "CUDA graph of all timed steps, one fused kernel per step, programmatic dependent launch",
-                       "step_algorithmic_bytes": step_bytes},
+            "config": config,
+            "launch": f"CUDA graph of the {steps} timed steps, one fused kernel per step, programmatic dependent "
+                      f"launch mode {args.pdl}; the graph is replayed {replays}x inside one CUDA-event pair",
+            "timed_replays": replays, "timed_region_ms": total_ms,
             "clocks": sampler.summary(),
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
+                    "latency_us_per_step": lat_us, "latency_steps": lat_steps,
                     "how": "pie_b200.ops wrappers; per step H2D of q/k/v + page tables from pinned memory and D2H of the "
-                           "output, on upload / compute / download streams with 3 buffer sets"},
+                           "output. `value`: INDEPENDENT steps pipelined over upload / compute / download streams with "
+                           "3 buffer sets (throughput). `latency_us_per_step`: one buffer set, upload -> fused step -> "
+                           "download, host synchronised after every step (what a dependent decode loop pays)"},
             "gpu_launches": timed_launches,
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only; the fused step adds RoPE + append to it)", "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                         "traffic": int(kern_bytes * NCU_TRAFFIC_RATIO), "traffic_source": "ncu capture of a 32-request case, scaled by bytes streamed",
-                         "bytes_per_launch": kern_bytes,
-                         "us_per_launch": kern_ms * 1e3,
-                         "frac_of_nominal_8tbs": achieved / 8000.0,
-                         "step_frac": step_bytes / (ms / steps * 1e-3) / 1e9 / peak},
+            "roofline": {"bound": "hbm",
+                         "kernel": "decode_tma_kernel<bf16, 8 kv heads, fused RoPE + append + attention> (the timed region)",
+                         "achieved": step_achieved, "peak": peak, "unit": "GB/s", "frac": step_achieved / peak,
+                         "peak_source": peak_kind,
+                         "traffic": int(step_bytes * NCU_TRAFFIC_RATIO),
+                         "traffic_source": "ncu capture of a 32-request case, scaled by bytes streamed",
+                         "bytes_per_launch": step_bytes, "us_per_launch": ms_per_step * 1e3,
+                         "frac_of_nominal_8tbs": step_achieved / 8000.0,
+                         "attention_only": {"kernel": "decode_tma_kernel<bf16, 8 kv heads> via piekv_decode_run, "
+                                                      f"{reps} back-to-back launches", "achieved": attn_achieved,
+                                            "frac": attn_achieved / peak, "bytes_per_launch": kern_bytes,
+                                            "us_per_launch": kern_ms * 1e3,
+                                            "frac_of_nominal_8tbs": attn_achieved / 8000.0}},
             "device_error_word": errw,
         }
+        line.update(sub)
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
@@ -388,7 +471,7 @@ def run_ours(args):
 # ---------------------------------------------------------------------------------------------
 # secondary workload: chunked prefill mix (tensor-core bound); `--workload prefill`
 # ---------------------------------------------------------------------------------------------
-def run_prefill(args):
+def prefill_leg(args):
     """8 new prompts of 2048 tokens + 8 chunks of 512 tokens on 6144 cached tokens, causal, 32q/8kv
     heads, D128, bf16, page 16.  A step = RoPE + append of all 20480 tokens, then paged prefill attention.
     Reports causal-exact TFLOP/s (4*D*Hq*allowed pairs) of the attention kernel against the measured
@@ -525,37 +608,46 @@ def run_prefill(args):
         "mask_plan": mask_plan,
         "device_error_word": ops.device_error(dev),
     }
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def run_prefill(args):
+    print(json.dumps(prefill_leg(args)), flush=True)
+
+
+def prefill_subrecord(dev):
+    """The `prefill` sub-record of the headline line: the chunked-prefill mix with the native causal flag, in a
+    loop long enough (about half a second of attention launches) for the sustained-clock regime the
+    tensor-core peak is quoted in."""
+    import types
+
+    a = types.SimpleNamespace(prefill_scale=1.0, pages=32768, prefill_mask=False, prefill_brle=False, warmup=10,
+                              steps=500)
+    line = prefill_leg(a)
+    return {"workload": line["config"]["workload"], "tokens_per_s": line["value"], "ms_per_step": line["ms_per_step"],
+            "ms_per_launch": line["roofline"]["ms_per_launch"], "launches_timed": a.steps,
+            "roofline": line["roofline"], "clocks": line["clocks"], "device_error_word": line["device_error_word"]}
 
 
 # ---------------------------------------------------------------------------------------------
 # secondary workload: 70B-shaped decode with eviction churn, KV heads sharded over the ranks
 # ---------------------------------------------------------------------------------------------
-def run_decode70b(args):
-    """64 q / 8 kv heads, D128, bf16, 256 requests with lognormal contexts (median 2048, clipped to
-    [128, 32768]); every 32 steps 20 % of the requests are evicted, their pages recycled and the slots
-    refilled with 1024-token contexts written through the RoPE + append kernel.  With G ranks every rank
-    holds 8/G KV heads (and 64/G query heads) of every request with identical page tables.  The ranks are
-    joined either by the decode kernel itself, which stores its heads into every rank's output buffer
-    over NVLink and raises a flag (`--join peer`, default), or by an NCCL all-gather after the attention
-    (`--join nccl`)."""
+def decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=False, batch=256, num_pages=None,
+                  group_world=None):
+    """One timed leg of the 70B-shaped workload.  `world` ranks share the heads (world == 1: all heads on this
+    GPU, no join).  Returns a dict of raw figures; every rank of the group must call it together when
+    world > 1.  64 q / 8 kv heads, D128, bf16, `batch` requests with lognormal contexts; every 32 steps 20 % of
+    the requests are evicted, their pages recycled and the slots refilled with 1024-token contexts written
+    through the RoPE + append kernel."""
     import torch.distributed as dist
 
     from pie_b200 import ops, parallel
     from pie_b200 import workloads as W
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    dev = torch.device("cuda", local)
-    torch.cuda.set_device(dev)
     cfg = W.CONFIG5
-    B, D = args.requests if args.requests != 64 else 256, cfg.head_dim
+    B, D = batch, cfg.head_dim
     hq, hkv = cfg.num_qo_heads // world, cfg.num_kv_heads // world
-    num_pages = args.pages if args.pages != 32768 else cfg.num_pages
-    steps, warmup = args.steps, args.warmup
+    num_pages = num_pages or cfg.num_pages
     reqs = W.config5_requests(B, 5, num_pages)
 
     def t(x):
@@ -589,7 +681,7 @@ def run_decode70b(args):
     w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
     launches = [0]
     peers = None
-    if world > 1 and args.join == "peer":
+    if world > 1 and join == "peer":
         peers = parallel.PeerOutputs(B, cfg.num_qo_heads, D, cfg.dtype, dev)
 
     def step(i, counted=False):
@@ -621,10 +713,10 @@ def run_decode70b(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    graph = None
+    g = None
     launch_mode = "eager, one fused kernel per step"
     side = torch.cuda.Stream(device=dev)
-    use_graph = args.graph and (peers is not None or world == 1)  # the NCCL join stays eager
+    use_graph = graph and (peers is not None or world == 1)  # the NCCL join stays eager
     if use_graph:
         # all timed steps (and their refills) in ONE graph: the device paces itself, no host jitter between
         # steps.  With the peer-store join the step number lives in device memory (counted mode).
@@ -634,12 +726,12 @@ def run_decode70b(args):
         side.synchronize()
         barrier()
         launches[0] = 0
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
             for i in range(steps):
                 step(warmup + i, counted=True)
         with torch.cuda.stream(side):
-            graph.replay()  # one untimed replay: graph upload
+            g.replay()  # one untimed replay: graph upload
         if peers is not None:
             peers.advance(steps)
         side.synchronize()
@@ -648,16 +740,16 @@ def run_decode70b(args):
         for i in range(warmup):
             step(i)
     barrier()
-    if graph is None:
+    if g is None:
         launches[0] = 0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(dev.index or 0)
     with sampler:
         barrier()
-        if graph is not None:
+        if g is not None:
             with torch.cuda.stream(side):
                 e0.record(side)
-                graph.replay()
+                g.replay()
                 e1.record(side)
             if peers is not None:
                 peers.advance(steps)
@@ -688,28 +780,101 @@ def run_decode70b(args):
     kern_ms = k0.elapsed_time(k1) / 20
     tokens = int(mid["meta"].seq_lens.astype(np.int64).sum())
     kern_bytes = tokens * 2 * hkv * D * 2 + B * 2 * hq * D * 2 + 4 * (len(mid["meta"].kv_indices) + 2 * B + 1)
-    peak, peak_kind = load_peaks()
-    achieved = kern_bytes / (kern_ms * 1e-3) / 1e9
-    if rank == 0:
-        print(json.dumps({
-            "metric": METRIC, "value": B * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, "
-                                   f"{B} requests, lognormal ctx, 20% evicted+refilled every 32 steps",
-                       "parallelism": f"KV heads sharded x{world} ({hkv} kv / {hq} q heads per GPU), " + (
-                           "outputs stored to every GPU by the decode kernel (NVLink peer stores + flags)"
-                           if peers is not None else "NCCL all-gather of attention outputs"),
-                       "pool_pages": num_pages,
-                       "l2": "inputs larger than L2; no flush", "launch": launch_mode},
-            "clocks": sampler.summary(), "gpu_launches": launches[0],
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only, per GPU)", "achieved": achieved,
-                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
-                         "traffic": None, "bytes_per_launch": kern_bytes, "us_per_launch": kern_ms * 1e3,
-                         "cached_tokens": tokens},
-            "device_error_word": ops.device_error(dev)}), flush=True)
+    errw = ops.device_error(dev)
     if peers is not None:
         peers.close()
+    del pool, qkv, kv_refill, ws, w
+    torch.cuda.empty_cache()
+    return dict(B=B, hq=hq, hkv=hkv, num_pages=num_pages, ms=ms, steps=steps, warmup=warmup, kern_ms=kern_ms,
+                kern_bytes=kern_bytes, tokens=tokens, launches=launches[0], launch_mode=launch_mode,
+                clocks=sampler.summary(), err=errw, peer=peers is not None)
+
+
+def measure_head_sharded(world, rank, dev, steps=48, warmup=4):
+    """The `head_sharded` sub-record of the headline line: the 70B-shaped decode step with the KV heads split
+    over all `world` ranks, joined by the decode kernel's own peer stores and, for comparison, by an NCCL
+    all-gather; plus the same step unsharded on rank 0's GPU alone, which is what strong scaling is quoted
+    against.  At world == 1 it is the unsharded step."""
+    import torch.distributed as dist
+
+    peak, peak_kind = load_peaks()
+
+    def roof(r):
+        ach = r["kern_bytes"] / (r["kern_ms"] * 1e-3) / 1e9
+        return {"bound": "hbm", "kernel": f"decode_tma_kernel<bf16, {r['hkv']} kv heads> (attention only, per GPU)",
+                "achieved": ach, "peak": peak, "unit": "GB/s", "frac": ach / peak, "peak_source": peak_kind,
+                "bytes_per_launch": r["kern_bytes"], "us_per_launch": r["kern_ms"] * 1e3}
+
+    rec = {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, 256 requests, "
+                       "lognormal ctx (median 2048), 20% evicted + refilled every 32 steps", "steps": steps,
+           "warmup": warmup, "scaling": "strong"}
+    if world == 1:
+        r = decode70b_leg(1, 0, dev, steps, warmup)
+        rec.update({"n_gpus": 1, "join": "none (all heads on one GPU)", "tokens_per_s": r["B"] * steps / (r["ms"] * 1e-3),
+                    "ms_per_step": r["ms"] / steps, "per_gpu_kernel_us": r["kern_ms"] * 1e3, "roofline": roof(r),
+                    "strong_scaling_vs_1gpu": 1.0, "launch": r["launch_mode"], "device_error_word": r["err"]})
+        return rec
+    peer = decode70b_leg(world, rank, dev, steps, warmup, join="peer")
+    peer_graph = decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=True)
+    nccl = decode70b_leg(world, rank, dev, steps, warmup, join="nccl")
+    # the unsharded step on rank 0 alone (the other ranks wait at the barrier with an idle GPU)
+    one = None
+    if rank == 0:
+        one = decode70b_leg(1, 0, dev, steps, warmup)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    if rank != 0:
+        return None
+    best = min(peer["ms"], peer_graph["ms"])
+    tps = peer["B"] * steps / (best * 1e-3)
+    tps1 = one["B"] * steps / (one["ms"] * 1e-3)
+    rec.update({"n_gpus": world, "join": "peer (decode kernel stores its heads to every GPU over NVLink, flag + bounded wait)",
+                "tokens_per_s": tps, "ms_per_step": best / steps,
+                "eager_ms_per_step": peer["ms"] / steps, "graph_ms_per_step": peer_graph["ms"] / steps,
+                "nccl_ms_per_step": nccl["ms"] / steps, "peer_vs_nccl": nccl["ms"] / best,
+                "per_gpu_kernel_us": peer["kern_ms"] * 1e3, "roofline": roof(peer),
+                "one_gpu_tokens_per_s": tps1, "one_gpu_ms_per_step": one["ms"] / steps,
+                "strong_scaling_vs_1gpu": tps / tps1, "strong_scaling_efficiency": tps / tps1 / world,
+                "kv_heads_per_gpu": peer["hkv"], "clocks": peer["clocks"],
+                "device_error_word": peer["err"] or nccl["err"] or one["err"]})
+    return rec
+
+
+def run_decode70b(args):
+    """`--workload decode70b`: one leg of the head-sharded workload as a line of its own (`--join peer|nccl`,
+    `--graph`)."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    B = args.requests if args.requests != 64 else 256
+    r = decode70b_leg(world, rank, dev, args.steps, args.warmup, join=args.join, graph=args.graph, batch=B,
+                      num_pages=args.pages if args.pages != 32768 else None)
+    peak, peak_kind = load_peaks()
+    achieved = r["kern_bytes"] / (r["kern_ms"] * 1e-3) / 1e9
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": B * r["steps"] / (r["ms"] * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms"] / r["steps"], "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, "
+                                   f"{B} requests, lognormal ctx, 20% evicted+refilled every 32 steps",
+                       "parallelism": f"KV heads sharded x{world} ({r['hkv']} kv / {r['hq']} q heads per GPU), " + (
+                           "outputs stored to every GPU by the decode kernel (NVLink peer stores + flags)"
+                           if r["peer"] else "NCCL all-gather of attention outputs"),
+                       "pool_pages": r["num_pages"],
+                       "l2": "inputs larger than L2; no flush", "launch": r["launch_mode"]},
+            "clocks": r["clocks"], "gpu_launches": r["launches"],
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (attention only, per GPU)", "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_kind,
+                         "traffic": None, "bytes_per_launch": r["kern_bytes"], "us_per_launch": r["kern_ms"] * 1e3,
+                         "cached_tokens": r["tokens"]},
+            "device_error_word": r["err"]}), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -717,7 +882,7 @@ def run_decode70b(args):
 # ---------------------------------------------------------------------------------------------
 # secondary workload: beam search with shared prefix pages and copy-on-write of the partial page
 # ---------------------------------------------------------------------------------------------
-def run_beam(args):
+def beam_leg():
     """16 prefixes of 1024 tokens, each forked into 4 beams that share the prefix pages; 64 decode steps;
     every 8 steps the 2 best beams of a group (seeded random score) survive and fork again: full pages are
     shared by reference count, a partially filled last page is copied (copy_pages_kernel), losers' private
@@ -823,7 +988,7 @@ def run_beam(args):
     torch.cuda.synchronize(dev)
     wall_ms = (time.perf_counter() - t0) * 1e3
     ms = e0.elapsed_time(e1)
-    print(json.dumps({
+    return {
         "metric": METRIC, "value": B * steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": 8,
         "ms_per_step": ms / steps, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "beam search page sharing: 16 prefixes x 1024 tokens x 4 beams, fork top-2 every 8 "
@@ -833,20 +998,50 @@ def run_beam(args):
         "page_copies": stats["copies"], "page_copy_bytes": stats["copy_bytes"], "pages_recycled": stats["freed"],
         "logical_kv_bytes_per_step": stats["logical_tokens"] * 4096 // steps,
         "unique_page_kv_bytes_per_step": stats["unique_tokens"] * 4096 // steps,
-        "device_error_word": ops.device_error(dev)}), flush=True)
+        "device_error_word": ops.device_error(dev)}
+
+
+def run_beam(args):
+    print(json.dumps(beam_leg()), flush=True)
+
+
+def beam_subrecord(dev):
+    """The `beam` sub-record of the headline line (beam search with shared prefix pages)."""
+    line = beam_leg()
+    keep = ("ms_per_step", "wall_ms_per_step", "page_copies", "page_copy_bytes", "pages_recycled",
+            "logical_kv_bytes_per_step", "unique_page_kv_bytes_per_step", "device_error_word")
+    rec = {"workload": line["config"]["workload"], "tokens_per_s": line["value"], "steps": line["steps"]}
+    rec.update({k: line[k] for k in keep})
+    rec["host"] = line["config"]["host"]
+    return rec
 
 
 # ---------------------------------------------------------------------------------------------
 # CPU arms
 # ---------------------------------------------------------------------------------------------
+def load_workloads_standalone():
+    """pie_b200/workloads.py loaded by file path: it needs only numpy and torch, and importing it through the
+    package would map libpiekv.so into a process whose job is to time the CPU path."""
+    import importlib.util
+
+    name = "_piekv_workloads_standalone"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(name, os.path.join(ROOT, "pie_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
 class CpuPath:
     """The reference path on host cores: the CPU oracle in the reference's op order
     (RoPE -> append -> decode attention, pie/src/pie_worker/model/llama3.py:654-689)."""
 
     def __init__(self, num_pages: int = 32768, seed: int = 1):
         from oracle import paged_kv_ref as R
-        from pie_b200 import workloads as W
 
+        W = load_workloads_standalone()
         self.R, self.W = R, W
         self.cfg = W.CONFIG2
         torch.set_num_threads(os.cpu_count() or 1)
@@ -928,7 +1123,8 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": dt / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "requests_per_gpu": 64, "sample": sample},
+        "config": headline_config(path.W, 64, world, 32768, steps, warmup),
+        "sample": sample,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": path.cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -1041,6 +1237,12 @@ def main():
                          "NCCL join stays eager)")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="decode70b on several GPUs: how the head-sharded outputs are joined")
+    ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
+                    help="decode: programmatic dependent launch mode of the timed steps (see PIEKV_OPT_PDL)")
+    ap.add_argument("--min-timed-ms", type=float, default=250.0,
+                    help="decode: replay the captured graph of --steps steps until the timed region lasts this long")
+    ap.add_argument("--no-sub", action="store_true",
+                    help="decode: skip the secondary workloads' sub-records (head_sharded, prefill, beam)")
     ap.add_argument("--prefill-brle", action="store_true",
                     help="prefill: pass the mask as BRLE runs (wire form), expanded to bits on the device")
     args = ap.parse_args()

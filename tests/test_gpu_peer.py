@@ -123,7 +123,7 @@ def test_empty_batch_raises_no_flag_and_the_wrapper_skips_the_wait():
         def full(self, batch):
             return torch.empty((batch, self.row_heads, self.head_dim), dtype=self.dtype, device="cuda")
 
-    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")
+    ws = torch.zeros(8 << 20, dtype=torch.uint8, device="cuda")
     w = ops.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD")
     z = lambda *shape: torch.zeros(shape, dtype=torch.int32, device="cuda")
     w.plan(z(1), z(1), z(1), 8, 4, 128, 16, q_data_type=torch.bfloat16)
