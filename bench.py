@@ -1217,6 +1217,58 @@ def run_flashinfer(args):
                      "us_per_launch": kern_ms * 1e3, "bytes_per_launch": kern_bytes}}), flush=True)
 
 
+def run_flashinfer_prefill(args):
+    """Black-box comparator for the chunked-prefill mix: FlashInfer's BatchPrefillWithPagedKVCacheWrapper with its
+    native causal flag on the same metadata and tensor shapes (called and timed only)."""
+    import flashinfer
+
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG3
+    HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    num_pages = 8192
+    meta = W.config3_meta(num_pages=num_pages)
+    n = meta.nnz
+
+    def t(x):
+        return torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+
+    pool = W.randn((num_pages, 2, 16, HKV, D), 300, cfg.dtype, 0.5, device=dev)
+    q = W.randn((n, HQ, D), 301, cfg.dtype, 0.5, device=dev)
+    ws = torch.zeros(256 << 20, dtype=torch.uint8, device=dev)
+    w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws, "NHD")
+    w.plan(qo_indptr=t(meta.qo_indptr), paged_kv_indptr=t(meta.kv_indptr), paged_kv_indices=t(meta.kv_indices),
+           paged_kv_last_page_len=t(meta.kv_last_page_len), num_qo_heads=HQ, num_kv_heads=HKV, head_dim_qk=D,
+           page_size=16, causal=True, q_data_type=cfg.dtype)
+    for _ in range(args.warmup):
+        w.run(q, pool)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        w.run(q, pool)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * D * HQ * W.causal_pairs(meta)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak = float(json.load(f)["bf16_tflops_sustained"])
+    except Exception:
+        peak = 1400.0
+    tf = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({"impl": "flashinfer", "version": flashinfer.__version__, "metric": "prefill_tokens_per_s",
+                      "value": n / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+                      "warmup": args.warmup, "ms_per_step": ms, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": f"chunked prefill mix: {meta.batch} requests, {n} query tokens, native "
+                                             "causal flag, attention only (no RoPE / append)"},
+                      "roofline": {"bound": "tensor", "kernel": "BatchPrefillWithPagedKVCacheWrapper.run",
+                                   "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                                   "flops_causal_exact": flops, "ms_per_launch": ms}}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1250,7 +1302,10 @@ def main():
     if args.impl == "reference":
         run_reference(args)
     elif args.impl == "flashinfer":
-        run_flashinfer(args)
+        if args.workload == "prefill":
+            run_flashinfer_prefill(args)
+        else:
+            run_flashinfer(args)
     elif args.workload == "prefill":
         run_prefill(args)
     elif args.workload == "decode70b":
