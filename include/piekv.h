@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define PIEKV_VERSION 100
+#define PIEKV_VERSION 101
 
 /* element types */
 #define PIEKV_F32 0
@@ -251,6 +251,69 @@ int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, con
                       int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
                       int32_t *err, void *stream);
 
+/* ---- sliding window and attention sinks ----------------------------------------------------------
+ *
+ * Other model families of the reference plan their wrappers with `window_left` (a different one per
+ * layer: pie/src/pie_worker/model/olmo3.py:976-1013, decode and prefill, the prefill together with
+ * `custom_mask`) or run a wrapper that takes per-head attention sinks
+ * (BatchAttentionWithAttentionSinkWrapper.run(q, kv, sinks, scaling),
+ * pie/src/pie_worker/model/gpt_oss.py:418-439,693-697,840-870).  The `_opt` entry points are the plain
+ * ones with this block appended; `opt == NULL` is exactly the plain call.
+ *
+ *   window_left  -1: none.  >= 0: the query at kv position p (= kv_len - qo_len + index of the query in
+ *                its request; for decode p = kv_len - 1) sees keys p - window_left .. only, on top of
+ *                whatever the causal flag or the mask allows.  The decode kernel then streams only the
+ *                pages that hold such keys.
+ *   sinks        nullable device fp32 [num_qo_heads]: softmax is taken over the scaled scores AND the
+ *                head's sink logit (not scaled); the sink has no value row, so it only takes
+ *                probability mass: out = sum_t exp(s_t) v_t / (sum_t exp(s_t) + exp(sink_h)).
+ *                `lse` then includes the sink term.  A query without any visible key gives zeros. */
+typedef struct piekv_attn_options {
+  int32_t window_left;
+  int32_t reserved; /* 0 */
+  const float *sinks;
+} piekv_attn_options;
+
+int piekv_decode_run_opt(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                         void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                         const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                         int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                         int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
+                         int32_t *err, void *stream, const piekv_attn_options *opt);
+
+int piekv_decode_step_fused_opt(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
+                                void *out, float *lse, const int32_t *kv_indptr,
+                                const int32_t *kv_indices, const int32_t *kv_last_page_len, int32_t batch,
+                                int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
+                                int32_t page_size, int32_t num_pages, int32_t dtype,
+                                const piekv_rope_params *rope, float sm_scale, void *workspace,
+                                int64_t workspace_bytes, int32_t *err, void *stream,
+                                const piekv_attn_options *opt);
+
+/* piekv_prefill_plan and piekv_prefill_plan_brle in one call, plus the window: the mask comes as bytes
+ * (`custom_mask`), as run lengths (`brle_runs` / `brle_indptr`) or not at all, and `window_left` >= 0 is
+ * ANDed into it on the device; a window without a mask is turned into one (causal or not, as `causal`
+ * says).  `mask_entries` = sum over requests of qo_len_b * kv_len_b whenever a mask or a window is
+ * given (it sizes the packed mask; also the `mask_bytes` of piekv_prefill_workspace_bytes and of the
+ * run call).  Run with piekv_prefill_run_opt(planned = 2 for run lengths, else 1) and the same window. */
+int piekv_prefill_plan_opt(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                           const int32_t *kv_last_page_len, const uint8_t *custom_mask,
+                           const uint32_t *brle_runs, const int32_t *brle_indptr, int64_t mask_entries,
+                           int32_t causal, int32_t window_left, int32_t batch, int32_t nnz,
+                           int32_t page_size, int32_t num_pages, void *workspace, int64_t workspace_bytes,
+                           int32_t *err, void *stream);
+
+int piekv_prefill_run_opt(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                          void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
+                          const int32_t *kv_indices, const int32_t *kv_last_page_len,
+                          const uint8_t *custom_mask, int64_t mask_bytes, int32_t causal,
+                          int32_t planned, int32_t batch, int32_t nnz, int32_t num_qo_heads,
+                          int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                          int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
+                          int32_t *err, void *stream, const piekv_attn_options *opt);
+
 /* ---- head-sharded decode over the GPUs of one node: results stored straight to every GPU ----
  *
  * The reference's tensor parallelism (llama3.py:607-610,963-965) gives every GPU Hkv/G kv heads and
@@ -312,7 +375,7 @@ int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_c
                             void *stream);
 
 /* sizeof of the structs that cross this boundary, for bindings to check their mirrors against:
- * which = 0: piekv_rope_params, 1: piekv_peer_outputs; anything else: -1. */
+ * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options; anything else: -1. */
 int32_t piekv_abi_sizeof(int32_t which);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */

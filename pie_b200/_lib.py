@@ -44,6 +44,12 @@ class RopeParams(C.Structure):
     ]
 
 
+class AttnOptions(C.Structure):
+    """Mirror of `piekv_attn_options`."""
+
+    _fields_ = [("window_left", C.c_int32), ("reserved", C.c_int32), ("sinks", C.c_void_p)]
+
+
 MAX_PEERS = 8
 PEER_HANDLE_BYTES = 64
 
@@ -90,6 +96,26 @@ SIGNATURES = {
     "piekv_decode_run": (
         C.c_int,
         [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p],
+    ),
+    "piekv_decode_run_opt": (
+        C.c_int,
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _p, _i64, _p, _p,
+         C.POINTER(AttnOptions)],
+    ),
+    "piekv_decode_step_fused_opt": (
+        C.c_int,
+        [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
+         _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _f32, _p, _i64, _p, _p,
+         C.POINTER(AttnOptions)],
+    ),
+    "piekv_prefill_plan_opt": (
+        C.c_int,
+        [_p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _p, _i64, _p, _p],
+    ),
+    "piekv_prefill_run_opt": (
+        C.c_int,
+        [_p, _i64, _i64, _p, _p, _p, _p, _p, _p, _p, _p, _i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+         _i32, _i32, _f32, _p, _i64, _p, _p, C.POINTER(AttnOptions)],
     ),
     "piekv_decode_noalloc_max_bytes": (_i64, []),
     "piekv_decode_run_noalloc": (

@@ -20,6 +20,13 @@ struct AttnArgs {
   int batch, nnz, hq, hkv, dim, page_size, num_pages;
   float sm_scale;
   int32_t *err;
+  // Sliding window: the query at kv position p (= kv_len - qo_len + row index) sees keys p - window_left .. ;
+  // -1: no window.  The decode and generic kernels apply it themselves; the tensor-core prefill kernels
+  // get it through the packed mask their plan builds.
+  int window_left = -1;
+  // Attention sinks: nullable fp32 [Hq].  The head's sink logit joins the softmax normaliser (it takes
+  // probability mass) but has no value row.
+  const float *sinks = nullptr;
 };
 
 // Destinations of a head-sharded decode step on several GPUs: the same output buffer on every GPU
@@ -49,6 +56,8 @@ bool prefill_tc_supported(const AttnArgs &a, int dtype);
 int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t mask_bytes);
 // brle_runs / brle_indptr (both or neither): build the packed mask from per-token run lengths
 // instead of a.mask
+// a.window_left >= 0 is ANDed into whichever mask form is given; without any mask it becomes one
+// (mask_bytes must then still name sum qo_len * kv_len, which sizes the packed mask)
 int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
                         cudaStream_t st, const uint32_t *brle_runs = nullptr, const int32_t *brle_indptr = nullptr);
 int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,

@@ -52,12 +52,20 @@ extern "C" int64_t piekv_decode_workspace_bytes(int32_t batch, int32_t num_qo_he
   return a > b ? a : b;
 }
 
-extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
-                                float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
-                                const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
-                                int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
-                                int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes, int32_t *err,
-                                void *stream) {
+static int apply_options(AttnArgs &a, const piekv_attn_options *opt, const char *who) {
+  if (opt == nullptr) return 0;
+  PIEKV_REQUIRE(opt->window_left >= -1, "%s: window_left %d (use -1 for no window)", who, opt->window_left);
+  a.window_left = opt->window_left;
+  a.sinks = opt->sinks;
+  return 0;
+}
+
+extern "C" int piekv_decode_run_opt(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                                    void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                    const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                    int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                                    int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
+                                    int32_t *err, void *stream, const piekv_attn_options *opt) {
   AttnArgs a{};
   a.q = q;
   a.q_sn = q_stride_n;
@@ -81,9 +89,21 @@ extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_str
   a.sm_scale = sm_scale;
   a.err = err;
   if (int rc = check_common(a, dtype, "decode_run")) return rc;
+  if (int rc = apply_options(a, opt, "decode_run")) return rc;
   if (batch == 0) return 0;
   if (decode_tma_supported(a, dtype)) return launch_decode_tma(a, dtype, workspace, workspace_bytes, (cudaStream_t)stream);
   return launch_attn_generic(a, dtype, (cudaStream_t)stream);
+}
+
+extern "C" int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
+                                float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                int32_t num_kv_heads, int32_t head_dim, int32_t page_size, int32_t num_pages,
+                                int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes, int32_t *err,
+                                void *stream) {
+  return piekv_decode_run_opt(q, q_stride_n, q_stride_h, pool, out, lse, kv_indptr, kv_indices, kv_last_page_len, batch,
+                              num_qo_heads, num_kv_heads, head_dim, page_size, num_pages, dtype, sm_scale, workspace,
+                              workspace_bytes, err, stream, nullptr);
 }
 
 static int decode_step_fused_impl(const void *q, const void *k, const void *v, int64_t q_stride_n, int64_t q_stride_h,
@@ -93,7 +113,7 @@ static int decode_step_fused_impl(const void *q, const void *k, const void *v, i
                                   int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
                                   int32_t num_pages, int32_t dtype, const piekv_rope_params *rope, float sm_scale,
                                   void *workspace, int64_t workspace_bytes, int32_t *err, void *stream,
-                                  const piekv::PeerOut *peer) {
+                                  const piekv::PeerOut *peer, const piekv_attn_options *opt = nullptr) {
   AttnArgs a{};
   a.q = q;
   a.q_sn = q_stride_n;
@@ -114,6 +134,7 @@ static int decode_step_fused_impl(const void *q, const void *k, const void *v, i
   a.sm_scale = sm_scale;
   a.err = err;
   if (int rc = check_common(a, dtype, "decode_step_fused")) return rc;
+  if (int rc = apply_options(a, opt, "decode_step_fused")) return rc;
   if (int rc = check_rope(rope, head_dim, "decode_step_fused")) return rc;
   if (batch == 0) return 0;
   PIEKV_REQUIRE(k && v, "decode_step_fused: null k / v");
@@ -163,6 +184,21 @@ extern "C" int piekv_decode_step_fused(const void *q, const void *k, const void 
                                 pos_ids, pool, out, lse, kv_indptr, kv_indices, kv_last_page_len, batch, num_qo_heads,
                                 num_kv_heads, head_dim, page_size, num_pages, dtype, rope, sm_scale, workspace,
                                 workspace_bytes, err, stream, nullptr);
+}
+
+extern "C" int piekv_decode_step_fused_opt(const void *q, const void *k, const void *v, int64_t q_stride_n,
+                                           int64_t q_stride_h, int64_t k_stride_n, int64_t k_stride_h,
+                                           int64_t v_stride_n, int64_t v_stride_h, const int32_t *pos_ids, void *pool,
+                                           void *out, float *lse, const int32_t *kv_indptr, const int32_t *kv_indices,
+                                           const int32_t *kv_last_page_len, int32_t batch, int32_t num_qo_heads,
+                                           int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
+                                           int32_t num_pages, int32_t dtype, const piekv_rope_params *rope,
+                                           float sm_scale, void *workspace, int64_t workspace_bytes, int32_t *err,
+                                           void *stream, const piekv_attn_options *opt) {
+  return decode_step_fused_impl(q, k, v, q_stride_n, q_stride_h, k_stride_n, k_stride_h, v_stride_n, v_stride_h,
+                                pos_ids, pool, out, lse, kv_indptr, kv_indices, kv_last_page_len, batch, num_qo_heads,
+                                num_kv_heads, head_dim, page_size, num_pages, dtype, rope, sm_scale, workspace,
+                                workspace_bytes, err, stream, nullptr, opt);
 }
 
 extern "C" int piekv_decode_step_fused_peer(const void *q, const void *k, const void *v, int64_t q_stride_n,
@@ -268,6 +304,31 @@ extern "C" int piekv_prefill_plan_brle(const int32_t *qo_indptr, const int32_t *
   return launch_prefill_plan(a, mask_bits, workspace, workspace_bytes, (cudaStream_t)stream, brle_runs, brle_indptr);
 }
 
+extern "C" int piekv_prefill_plan_opt(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                                      const int32_t *kv_last_page_len, const uint8_t *custom_mask,
+                                      const uint32_t *brle_runs, const int32_t *brle_indptr, int64_t mask_entries,
+                                      int32_t causal, int32_t window_left, int32_t batch, int32_t nnz,
+                                      int32_t page_size, int32_t num_pages, void *workspace, int64_t workspace_bytes,
+                                      int32_t *err, void *stream) {
+  PIEKV_REQUIRE(batch >= 0 && nnz >= 0 && page_size > 0 && num_pages > 0 && mask_entries >= 0,
+                "prefill_plan_opt: bad sizes");
+  PIEKV_REQUIRE(window_left >= -1, "prefill_plan_opt: window_left %d (use -1 for no window)", window_left);
+  PIEKV_REQUIRE(nnz == 0 || (qo_indptr && kv_indptr && kv_last_page_len), "prefill_plan_opt: null pointer");
+  const bool brle = brle_runs != nullptr || brle_indptr != nullptr;
+  PIEKV_REQUIRE(!(brle && custom_mask), "prefill_plan_opt: pass the mask either as bytes or as run lengths");
+  PIEKV_REQUIRE(!brle || brle_indptr != nullptr, "prefill_plan_opt: brle_indptr is null");
+  if (page_size != 16) {
+    PIEKV_REQUIRE(!brle, "prefill_plan_opt: page size %d (a run-length mask needs the tensor-core path: 16)", page_size);
+    return 0;  // the general kernel needs no plan; it applies the window itself
+  }
+  AttnArgs a{};
+  fill_prefill_args(a, nullptr, 0, 0, nullptr, nullptr, nullptr, qo_indptr, kv_indptr, nullptr, kv_last_page_len,
+                    custom_mask, (custom_mask || brle) ? 0 : causal, batch, nnz, 1, 1, 128, page_size, num_pages, 1.f,
+                    err);
+  a.window_left = window_left;
+  return launch_prefill_plan(a, mask_entries, workspace, workspace_bytes, (cudaStream_t)stream, brle_runs, brle_indptr);
+}
+
 extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool, void *out,
                                  float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
                                  const int32_t *kv_indices, const int32_t *kv_last_page_len,
@@ -275,11 +336,26 @@ extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_st
                                  int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t num_kv_heads,
                                  int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype, float sm_scale,
                                  void *workspace, int64_t workspace_bytes, int32_t *err, void *stream) {
+  return piekv_prefill_run_opt(q, q_stride_n, q_stride_h, pool, out, lse, qo_indptr, kv_indptr, kv_indices,
+                               kv_last_page_len, custom_mask, mask_bytes, causal, planned, batch, nnz, num_qo_heads,
+                               num_kv_heads, head_dim, page_size, num_pages, dtype, sm_scale, workspace, workspace_bytes,
+                               err, stream, nullptr);
+}
+
+extern "C" int piekv_prefill_run_opt(const void *q, int64_t q_stride_n, int64_t q_stride_h, const void *pool,
+                                     void *out, float *lse, const int32_t *qo_indptr, const int32_t *kv_indptr,
+                                     const int32_t *kv_indices, const int32_t *kv_last_page_len,
+                                     const uint8_t *custom_mask, int64_t mask_bytes, int32_t causal, int32_t planned,
+                                     int32_t batch, int32_t nnz, int32_t num_qo_heads, int32_t num_kv_heads,
+                                     int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype,
+                                     float sm_scale, void *workspace, int64_t workspace_bytes, int32_t *err,
+                                     void *stream, const piekv_attn_options *opt) {
   AttnArgs a{};
   fill_prefill_args(a, q, q_stride_n, q_stride_h, pool, out, lse, qo_indptr, kv_indptr, kv_indices, kv_last_page_len,
                     custom_mask, causal, batch, nnz, num_qo_heads, num_kv_heads, head_dim, page_size, num_pages,
                     sm_scale, err);
   if (int rc = check_common(a, dtype, "prefill_run")) return rc;
+  if (int rc = apply_options(a, opt, "prefill_run")) return rc;
   PIEKV_REQUIRE(nnz == 0 || qo_indptr != nullptr, "prefill_run: qo_indptr is null");
   if (batch == 0 || nnz == 0) return 0;
   if (planned == 2) {
@@ -292,6 +368,8 @@ extern "C" int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_st
     if (!planned) {
       if (int rc = launch_prefill_plan(a, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream)) return rc;
     }
+    // with a window the plan holds a packed mask even when the caller passed none
+    if (a.window_left >= 0 && a.mask == nullptr && mask_bytes > 0) a.mask = reinterpret_cast<const uint8_t *>(workspace);
     return launch_prefill_tc(a, dtype, mask_bytes, workspace, workspace_bytes, (cudaStream_t)stream);
   }
   return launch_attn_generic(a, dtype, (cudaStream_t)stream);

@@ -1,8 +1,8 @@
 // General paged attention: any element type, any head_dim <= 256, any page size, GQA,
-// optional causal offset and optional flat boolean mask.  One warp per (query row, query
+// optional causal offset, optional flat boolean mask, optional sliding window and attention sinks.
+// One warp per (query row, query
 // head); lanes own head_dim elements d = lane, lane+32, ...; fp32 online softmax.
-// It is the path for shapes the tuned kernels do not cover (fp32, odd head sizes) and for
-// arbitrary custom masks.  Math follows the decode statement in
+// It is the path for shapes the tuned kernels do not cover (fp32, odd head sizes, other page sizes).  Math follows the decode statement in
 // pie/src/flashinfer_metal/kernels/metal_attention_simdgroup_opt.metal:1235-1330
 // (scale 1/sqrt(D), kv_head = q_head / (Hq/Hkv), fp32 running max / sum).
 #include "attn.cuh"
@@ -57,6 +57,12 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(AttnArgs a) {
     int c = kv_len - qo_len + j + 1;
     limit = c < limit ? c : limit;
   }
+  // sliding window: keys before (position of this query) - window_left are not seen
+  int t_first = 0;
+  if (a.window_left >= 0) {
+    const int first = kv_len - qo_len + j - a.window_left;
+    t_first = first > 0 ? first : 0;
+  }
 
   const uint8_t *mrow = nullptr;
   if (a.mask != nullptr) {
@@ -86,7 +92,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(AttnArgs a) {
   const size_t half_page = (size_t)a.page_size * row_elems;
   const T *pool = reinterpret_cast<const T *>(a.pool);
 
-  for (int t = 0; t < limit; ++t) {
+  for (int t = t_first; t < limit; ++t) {
     if (mrow != nullptr && mrow[t] == 0) continue;
     int page = a.kv_indices[p0 + t / a.page_size];
     if (page < 0 || page >= a.num_pages) {
@@ -117,6 +123,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(AttnArgs a) {
   }
 
   T *orow = reinterpret_cast<T *>(a.out) + ((size_t)i * a.hq + h) * D;
+  l = add_sink(l, m, a.sinks, h);
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int e = 0; e < kMaxEpl; ++e) {

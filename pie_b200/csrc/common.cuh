@@ -214,4 +214,12 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Softmax normaliser with an attention sink.  `l` is the running sum of exp2(score - m_log2); the sink's
+// logit (natural units, not multiplied by sm_scale) adds exp(sink) in the same units.  A row without any
+// key keeps l = 0 (its output is zero either way).
+__device__ __forceinline__ float add_sink(float l, float m_log2, const float *sinks, int head) {
+  if (sinks == nullptr || !(l > 0.f)) return l;
+  return l + fast_exp2(fmaf(__ldg(sinks + head), 1.4426950408889634f, -m_log2));
+}
+
 }  // namespace piekv

@@ -49,6 +49,13 @@ struct DecodeParams {
   int *counters;    // [batch], zero between launches
   int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets
   PeerOut peer;     // n == 0: results go to a.out only
+  // Sliding window (a.window_left >= 0): the kernel streams only the pages that hold keys inside each
+  // request's window.  win_indptr [B+1] is the prefix sum of those page counts (it takes kv_indptr's place
+  // in the work partition), win_meta[b] = (shift, first): flat windowed page g of request b is
+  // kv_indices[g + shift], and tokens before `first` of the request's first streamed page are outside
+  // the window.  Both are written by decode_window_kernel just before the launch; nullptr: no window.
+  const int32_t *win_indptr;
+  const int2 *win_meta;
 };
 
 // Extra inputs of the fused step (RoPE + append + attention in one launch): the new token's
@@ -91,6 +98,62 @@ __device__ __forceinline__ int request_of_page(const int32_t *indptr, int batch,
   return lo;
 }
 
+// Windowed page ranges of a decode batch.  One block; a request keeps the pages from the one that holds
+// key (seq_len - 1 - window_left) to its last.
+__global__ void __launch_bounds__(1024) decode_window_kernel(const int32_t *__restrict__ kv_indptr,
+                                                             const int32_t *__restrict__ last_page_len, int batch,
+                                                             int window_left, int32_t *win_indptr, int2 *win_meta) {
+  __shared__ int sh[32];
+  __shared__ int carry;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < batch; base += 1024) {
+    const int b = base + threadIdx.x;
+    int eff = 0, skip = 0, first = 0, p0 = 0;
+    if (b < batch) {
+      p0 = kv_indptr[b];
+      const int np = kv_indptr[b + 1] - p0;
+      if (np > 0) {
+        int last = last_page_len[b];
+        last = last < 1 ? 1 : (last > kPage ? kPage : last);  // the attention kernel reports a bad value
+        const int seq = (np - 1) * kPage + last;
+        const int first_tok = max(0, seq - 1 - window_left);
+        skip = first_tok / kPage;
+        first = first_tok % kPage;
+        eff = np - skip;
+      }
+    }
+    int x = eff;  // inclusive scan over the block
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    if (lane == 31) sh[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = sh[lane];
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, d);
+        if (lane >= d) w += y;
+      }
+      sh[lane] = w;
+    }
+    __syncthreads();
+    const int excl = carry + (warp > 0 ? sh[warp - 1] : 0) + x - eff;
+    if (b < batch) {
+      win_indptr[b] = excl;
+      win_meta[b] = make_int2(p0 + skip - excl, first);
+    }
+    __syncthreads();
+    if (threadIdx.x == 1023) carry = excl + eff;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) win_indptr[batch] = carry;
+}
+
 template <typename T, int HKV, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
     decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ DecodeParams p,
@@ -119,9 +182,11 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (p.pdl == 1) asm volatile("griddepcontrol.wait;" ::: "memory");
   // one coalesced read of the page-table offsets instead of a chain of dependent searches in L2
-  const int32_t *ip = a.kv_indptr;
+  const bool windowed = p.win_indptr != nullptr;
+  const int32_t *ip = windowed ? p.win_indptr : a.kv_indptr;  // the windowed prefix takes the offsets' place
   if (B <= kSmemBatch) {
-    for (int x = threadIdx.x; x <= B; x += kThreads) sh_indptr[x] = __ldg(a.kv_indptr + x);
+    const int32_t *src = ip;
+    for (int x = threadIdx.x; x <= B; x += kThreads) sh_indptr[x] = __ldg(src + x);
     ip = sh_indptr;
   }
   if (threadIdx.x == 0) {
@@ -158,10 +223,11 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) atomicExch(&sh_abort, 1);
           break;
         }
+        const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
         while (g < seg_end) {
           const int npg = min(PG, seg_end - g);
           // page ids first, so the load is in flight while we wait for the stage
-          int page = lane < npg ? __ldg(a.kv_indices + g + lane) : 0;
+          int page = lane < npg ? __ldg(a.kv_indices + g + shift + lane) : 0;
           const int s = armed % kStages;
           const uint32_t ph = (armed / kStages) & 1;
           if (*(volatile int *)&sh_abort) {
@@ -295,6 +361,12 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
       last_len = last_len < 1 ? 1 : kPage;
     }
+    int shift = 0, win_first = 0;
+    if (windowed) {
+      const int2 wm = __ldg(p.win_meta + b);
+      shift = wm.x;
+      win_first = wm.y;
+    }
     int rope_pos = 0;
     int last_phys = -1;  // physical id of the request's last page when this segment contains it
     if (FUSED) {
@@ -303,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
         rope_pos = 0;
       }
-      if (seg_end == req_end) last_phys = __ldg(a.kv_indices + req_end - 1);
+      if (seg_end == req_end) last_phys = __ldg(a.kv_indices + req_end - 1 + shift);
       // rotate the query fragments in registers (one rounding to T, as the in-place op does)
       if (f.rope.mode != PIEKV_ROPE_NONE) {
         if (!f.rope.interleave) {
@@ -365,6 +437,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (!aborted && pslot < npg) {
         const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
+        const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
         const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
         const uint32_t ktile = page_base + h * 4096;
         const uint32_t vtile = page_base + HKV * 4096 + h * 4096;
@@ -458,7 +531,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int tok = nt * 8 + qlane * 2 + e;
-            const bool ok = tok < valid;
+            const bool ok = tok < valid && tok >= tok_lo;
             sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
             sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
             mx0 = fmaxf(mx0, sc[nt][e]);
@@ -539,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int row = quad + half * 8;
         if (row < group) {
           const int qh = h * group + row;
-          const float lsum = half ? ls1 : ls0;
+          const float lsum = add_sink(half ? ls1 : ls0, half ? m1 : m0, a.sinks, qh);
           const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
           if (p.peer.n == 0) {  // the usual case keeps its own straight-line stores
             uint32_t *orow = reinterpret_cast<uint32_t *>(out + ((size_t)b * a.hq + qh) * kDim);
@@ -609,6 +682,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           if ((tid & 31) == 0) p.part_ml[idx] = make_float2(M, L);
           continue;
         }
+        L = add_sink(L, M, a.sinks, qh);
         const float inv = L > 0.f ? 1.f / L : 0.f;
         uint2 pk;
         pk.x = pack2<T>(acc.x * inv, acc.y * inv);
@@ -718,11 +792,12 @@ bool decode_tma_supported(const AttnArgs &a, int dtype) {
 int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
   const int pg = (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8) ? 8 / hkv : 1;
   const int64_t slots = (int64_t)sm_count() + batch;
-  return kCounterBytes + slots * pg * hq * (kDim * 4 + 8) + 256;
+  const int64_t window_meta = (((int64_t)batch + 1) * 12 + 255) / 256 * 256;  // win_indptr + win_meta
+  return kCounterBytes + slots * pg * hq * (kDim * 4 + 8) + 512 + window_meta;
 }
 
 static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, DecodeParams *p,
-                   CUtensorMap *tm) {
+                   CUtensorMap *tm, cudaStream_t st) {
   const int pg = 8 / a.hkv;
   const int64_t slots = (int64_t)sm_count() + a.batch;
   const int64_t need = decode_tma_workspace_bytes(a.batch, a.hq, a.hkv);
@@ -738,6 +813,19 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
   p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
   const int64_t ml_bytes = ((slots * pg * a.hq * 8 + 255) / 256) * 256;
   p->part_o = reinterpret_cast<float *>(ws + kCounterBytes + ml_bytes);
+  p->win_indptr = nullptr;
+  p->win_meta = nullptr;
+  if (a.window_left >= 0) {
+    // windowed page ranges, computed on the device right before the launch (stream-ordered, no host work)
+    const int64_t o_bytes = ((slots * pg * a.hq * kDim * 4 + 255) / 256) * 256;
+    int32_t *wi = reinterpret_cast<int32_t *>(ws + kCounterBytes + ml_bytes + o_bytes);
+    int2 *wm = reinterpret_cast<int2 *>(wi + ((a.batch + 1 + 1) & ~1));  // 8-byte aligned
+    decode_window_kernel<<<1, 1024, 0, st>>>(a.kv_indptr, a.kv_last_page_len, a.batch, a.window_left, wi, wm);
+    PIEKV_LAUNCH_CHECK("decode_window_kernel");
+    p->win_indptr = wi;
+    p->win_meta = wm;
+    if (p->pdl > 1) p->pdl = 1;  // the offsets the kernel partitions by were written by the launch before it
+  }
   return make_page_tensor_map(tm, a.pool, a.num_pages, a.hkv, dtype, /*box_halves=*/2, /*box_heads=*/a.hkv,
                               /*box_kv=*/2);
 }
@@ -746,7 +834,7 @@ int launch_decode_tma(const AttnArgs &a, int dtype, void *workspace, int64_t wor
   if (a.batch == 0) return 0;
   DecodeParams p;
   CUtensorMap tm;
-  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
+  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm, st)) return rc;
   FusedArgs f{};
   if (dtype == PIEKV_BF16) return launch_h<__nv_bfloat16, false>(tm, p, f, st);
   return launch_h<__half, false>(tm, p, f, st);
@@ -766,7 +854,7 @@ int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const v
   if (a.batch == 0) return 0;
   DecodeParams p;
   CUtensorMap tm;
-  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm)) return rc;
+  if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm, st)) return rc;
   if (peer != nullptr && peer->n > 0) {
     p.peer = *peer;
     p.peer.done = p.counters + (kCounterBytes / 4 - 1);  // last word of the counter block

@@ -57,6 +57,7 @@ extern "C" int piekv_version(void) { return PIEKV_VERSION; }
 extern "C" int32_t piekv_abi_sizeof(int32_t which) {
   if (which == 0) return (int32_t)sizeof(piekv_rope_params);
   if (which == 1) return (int32_t)sizeof(piekv_peer_outputs);
+  if (which == 2) return (int32_t)sizeof(piekv_attn_options);
   return -1;
 }
 

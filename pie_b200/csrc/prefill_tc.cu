@@ -137,7 +137,7 @@ __global__ void prefill_pack_mask_kernel(const uint8_t *__restrict__ mask, const
                                          const int32_t *__restrict__ kv_indptr, const int32_t *__restrict__ last,
                                          int batch, int nnz, int page_size, const int32_t *__restrict__ tile_base,
                                          const long long *__restrict__ poff, const long long *__restrict__ moff,
-                                         uint4 *packed, uint32_t *summary, int sw) {
+                                         uint4 *packed, uint32_t *summary, int sw, int window_left) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= nnz) return;
@@ -153,6 +153,8 @@ __global__ void prefill_pack_mask_kernel(const uint8_t *__restrict__ mask, const
   const int j = i - qo_indptr[b];
   const int kv = kv_len_of(kv_indptr, last, b, page_size);
   const int groups = (kv + 127) / 128;
+  // a sliding window is ANDed into the mask: keys before (position of the query) - window_left are dropped
+  const int t_first = window_left >= 0 ? max(0, kv - (qo_indptr[b + 1] - qo_indptr[b]) + j - window_left) : 0;
   const uint8_t *src = mask + moff[b] + (long long)j * kv;
   uint32_t *dst = reinterpret_cast<uint32_t *>(packed + poff[b] + (long long)j * groups);
   uint32_t *srow = summary + (size_t)(tile_base[b] + j / kBM) * sw;
@@ -161,7 +163,7 @@ __global__ void prefill_pack_mask_kernel(const uint8_t *__restrict__ mask, const
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const int t = g * 128 + w * 32 + lane;
-      const uint32_t word = __ballot_sync(0xffffffffu, t < kv && src[t] != 0);
+      const uint32_t word = __ballot_sync(0xffffffffu, t < kv && t >= t_first && src[t] != 0);
       if (lane == w) dst[g * 4 + w] = word;
       any |= word;
     }
@@ -184,7 +186,7 @@ __global__ void prefill_brle_mask_kernel(const uint32_t *__restrict__ runs, cons
                                          const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
                                          const int32_t *__restrict__ last, int batch, int nnz, int page_size,
                                          const int32_t *__restrict__ tile_base, const long long *__restrict__ poff,
-                                         uint4 *packed, uint32_t *summary, int sw) {
+                                         uint4 *packed, uint32_t *summary, int sw, int window_left) {
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (i >= nnz) return;
@@ -203,6 +205,8 @@ __global__ void prefill_brle_mask_kernel(const uint32_t *__restrict__ runs, cons
   const int groups = (kv + 127) / 128;
   const int words = groups * 4;
   const long long valid = max(0, min(kv, kv - qo + j + 1));
+  // a sliding window clips every attend run from below
+  const long long t_first = window_left >= 0 ? max(0, kv - qo + j - window_left) : 0;
   uint32_t *dst = reinterpret_cast<uint32_t *>(packed + poff[b] + (long long)j * groups);
   for (int w = lane; w < words; w += 32) dst[w] = 0;
   const int r0 = run_indptr[i], r1 = run_indptr[i + 1];
@@ -225,6 +229,7 @@ __global__ void prefill_brle_mask_kernel(const uint32_t *__restrict__ runs, cons
       long long e = __shfl_sync(0xffffffffu, end, src_lane);
       if (s >= valid) break;
       e = min(e, valid);
+      s = max(s, t_first);
       if (e <= s) continue;
       const int w_first = (int)(s >> 5), w_last = (int)((e - 1) >> 5);
       // lane's first owned word at or after w_first
@@ -243,6 +248,52 @@ __global__ void prefill_brle_mask_kernel(const uint32_t *__restrict__ runs, cons
   for (int g = lane; g < groups; g += 32) {
     const uint4 v = reinterpret_cast<const uint4 *>(dst)[g];
     if ((v.x | v.y | v.z | v.w) != 0) {
+      uint32_t *sp = srow + (g >> 5);
+      const uint32_t bit = 1u << (g & 31);
+      if ((*(volatile uint32_t *)sp & bit) == 0) atomicOr(sp, bit);
+    }
+  }
+}
+
+// A sliding window without any other mask, in the same packed form: the query at position
+// p = kv_len - qo_len + j sees keys [max(0, p - window_left), causal ? p : kv_len - 1].  One warp per
+// query row; lane w writes words w, w + 32, ... of the row.
+__global__ void prefill_window_mask_kernel(const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
+                                           const int32_t *__restrict__ last, int batch, int nnz, int page_size,
+                                           const int32_t *__restrict__ tile_base, const long long *__restrict__ poff,
+                                           uint4 *packed, uint32_t *summary, int sw, int window_left, int causal) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= nnz) return;
+  int lo = 0, hi = batch;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (qo_indptr[mid + 1] > i)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  const int b = lo < batch ? lo : batch - 1;
+  const int j = i - qo_indptr[b];
+  const int qo = qo_indptr[b + 1] - qo_indptr[b];
+  const int kv = kv_len_of(kv_indptr, last, b, page_size);
+  const int groups = (kv + 127) / 128;
+  const int pos = kv - qo + j;
+  const long long s = max(0, pos - window_left);
+  const long long e = causal ? max(0, min(kv, pos + 1)) : kv;  // exclusive
+  uint32_t *dst = reinterpret_cast<uint32_t *>(packed + poff[b] + (long long)j * groups);
+  uint32_t *srow = summary + (size_t)(tile_base[b] + j / kBM) * sw;
+  for (int w = lane; w < groups * 4; w += 32) {
+    const long long wb = (long long)w << 5;
+    uint32_t bits = 0;
+    if (e > s && wb < e && wb + 32 > s) {
+      const uint32_t lo_mask = s > wb ? 0xffffffffu << (int)(s - wb) : 0xffffffffu;
+      const uint32_t hi_mask = e < wb + 32 ? 0xffffffffu >> (int)(wb + 32 - e) : 0xffffffffu;
+      bits = lo_mask & hi_mask;
+    }
+    dst[w] = bits;
+    if (bits != 0) {
+      const int g = w >> 2;
       uint32_t *sp = srow + (g >> 5);
       const uint32_t bit = 1u << (g & 31);
       if ((*(volatile uint32_t *)sp & bit) == 0) atomicOr(sp, bit);
@@ -674,7 +725,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (ok) ok = pair_sync();
     if (ok) {
       tc::fence_after_sync();
-      const float lsum = l + xch_sum[hh ^ 1][row];
+      const float lsum = add_sink(l + xch_sum[hh ^ 1][row], m_ref, a.sinks, h);
       const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
       T *orow = out + ((size_t)(q0 + r0 + row) * a.hq + h) * kDim + hh * 64;
       const uint32_t o_addr = tmem + lane_base + kColO + hh * 64;
@@ -735,7 +786,8 @@ int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, 
                         cudaStream_t st, const uint32_t *brle_runs, const int32_t *brle_indptr) {
   if (a.nnz == 0 || a.batch == 0) return 0;
   const bool brle = brle_runs != nullptr || brle_indptr != nullptr;
-  const bool masked = a.mask != nullptr || brle;
+  const bool window_only = a.window_left >= 0 && a.mask == nullptr && !brle && mask_bytes > 0;
+  const bool masked = a.mask != nullptr || brle || window_only;
   const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, masked ? mask_bytes : 0);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= v.bytes, "prefill: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)v.bytes);
@@ -750,13 +802,19 @@ int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, 
   if (brle) {
     prefill_brle_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(brle_runs, brle_indptr, a.qo_indptr, a.kv_indptr,
                                                                a.kv_last_page_len, a.batch, a.nnz, a.page_size,
-                                                               v.tile_base, v.poff, v.packed, v.summary, v.sw);
+                                                               v.tile_base, v.poff, v.packed, v.summary, v.sw,
+                                                               a.window_left);
     PIEKV_LAUNCH_CHECK("prefill_brle_mask_kernel");
   } else if (a.mask != nullptr) {
     prefill_pack_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(a.mask, a.qo_indptr, a.kv_indptr, a.kv_last_page_len,
                                                                a.batch, a.nnz, a.page_size, v.tile_base, v.poff, v.moff,
-                                                               v.packed, v.summary, v.sw);
+                                                               v.packed, v.summary, v.sw, a.window_left);
     PIEKV_LAUNCH_CHECK("prefill_pack_mask_kernel");
+  } else if (window_only) {
+    prefill_window_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch,
+                                                                 a.nnz, a.page_size, v.tile_base, v.poff, v.packed,
+                                                                 v.summary, v.sw, a.window_left, a.causal);
+    PIEKV_LAUNCH_CHECK("prefill_window_mask_kernel");
   }
   prefill_plan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size, a.causal,
                                           v.tile_base, v.summary, v.sw, masked ? 1 : 0, v.tiles, v.ntiles, v.max_tiles);

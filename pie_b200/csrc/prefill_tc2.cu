@@ -447,6 +447,7 @@ __global__ void __launch_bounds__(k2Threads, 1)
     if (ok) ok = wait_or_abort(&o_done[x], 0, abort_flag);  // committed once, after the last tile
     if (ok) {
       tc::fence_after_sync();
+      l = add_sink(l, m_ref, a.sinks, h0 + x);
       const float inv = l > 0.f ? 1.f / l : 0.f;
       T *orow = out + ((size_t)(q0 + r0 + row) * a.hq + h0 + x) * kDim;
 #pragma unroll

@@ -33,7 +33,9 @@ from ._lib import RopeParams, check, lib
 __all__ = [
     "BatchPrefillWithPagedKVCacheWrapper",
     "BatchDecodeWithPagedKVCacheWrapper",
+    "BatchAttentionWithAttentionSinkWrapper",
     "apply_rope_pos_ids_inplace",
+    "apply_rope_with_cos_sin_cache_inplace",
     "apply_llama31_rope_pos_ids_inplace",
     "append_paged_kv_cache",
     "get_seq_lens",
@@ -264,6 +266,44 @@ def apply_llama31_rope_pos_ids_inplace(q: torch.Tensor, k: torch.Tensor, pos_ids
     _rope_inplace(q, k, pos_ids, cfg, "apply_llama31_rope_pos_ids_inplace")
 
 
+def apply_rope_with_cos_sin_cache_inplace(positions: torch.Tensor, query: torch.Tensor, key: torch.Tensor,
+                                          head_size: int, cos_sin_cache: torch.Tensor, is_neox: bool = True) -> None:
+    """Rotary embedding in place from a precomputed table, as the YaRN-scaled model families call it
+    (pie/src/pie_worker/model/gpt_oss.py:671-678, mistral3.py:838-845, olmo3.py:797-804).
+
+    `cos_sin_cache` is float32 [max_position, rotary_dim]: cos in the first half of a row, sin in the second
+    (any attention-temperature factor already multiplied in, gpt_oss.py:540-547).  `query` / `key` are
+    [n, heads, head_size] or flattened [n, heads * head_size]; `is_neox=True` pairs element i with
+    i + head_size / 2, False pairs (2i, 2i + 1).  Positions may be int32 or int64."""
+    _require_cuda(query, "query")
+    _require_cuda(key, "key")
+    _require_cuda(positions, "positions")
+    _require_cuda(cos_sin_cache, "cos_sin_cache")
+    if positions.dtype not in (torch.int32, torch.int64):
+        raise ValueError(f"positions must be int32 or int64, got {positions.dtype}")
+    pos = positions if positions.dtype == torch.int32 else positions.to(torch.int32)
+    pos = pos.contiguous()
+    if cos_sin_cache.dtype != torch.float32 or cos_sin_cache.dim() != 2:
+        raise ValueError("cos_sin_cache must be float32 [max_position, rotary_dim]")
+    if cos_sin_cache.shape[1] != head_size:
+        raise ValueError(f"rotary_dim {cos_sin_cache.shape[1]} smaller than head_size {head_size} is not supported")
+
+    def heads(t, name):
+        if t.dim() == 3:
+            if t.shape[2] != head_size:
+                raise ValueError(f"{name}: last axis {t.shape[2]} differs from head_size {head_size}")
+            return t
+        if t.dim() != 2 or t.shape[1] % head_size != 0:
+            raise ValueError(f"{name} must be [n, heads, head_size] or [n, heads * head_size], got {tuple(t.shape)}")
+        if t.shape[1] > 1 and t.stride(1) != 1:
+            raise ValueError(f"{name}: the flattened head axis must be contiguous")
+        return t.as_strided((t.shape[0], t.shape[1] // head_size, head_size), (t.stride(0), head_size, 1),
+                            t.storage_offset())
+
+    cfg = RopeConfig(mode="table", cos_sin_table=cos_sin_cache.contiguous(), interleave=not is_neox)
+    _rope_inplace(heads(query, "query"), heads(key, "key"), pos, cfg, "apply_rope_with_cos_sin_cache_inplace")
+
+
 def _append(q, k, v, pos_ids, batch_indices, positions, pool, kv_indices, kv_indptr, kv_last_page_len,
             cfg: Optional[RopeConfig], rotate_k_in_place: bool, who: str) -> None:
     _require_cuda(k, "append_key")
@@ -368,6 +408,24 @@ def _check_workspace(ws: torch.Tensor) -> None:
         raise ValueError(f"workspace_buffer must hold at least {COUNTER_BYTES} bytes")
 
 
+def _attn_options(window_left: int, sinks: Optional[torch.Tensor], num_qo_heads: int):
+    """ctypes `piekv_attn_options` (or None when there is neither a window nor sinks)."""
+    if window_left < 0 and sinks is None:
+        return None
+    o = _lib.AttnOptions()
+    o.window_left = int(window_left) if window_left >= 0 else -1
+    o.reserved = 0
+    o.sinks = None
+    if sinks is not None:
+        _require_cuda(sinks, "sinks")
+        if sinks.dtype != torch.float32 or sinks.dim() != 1 or sinks.shape[0] != num_qo_heads or \
+                not sinks.is_contiguous():
+            raise ValueError(f"sinks must be a contiguous float32 tensor of {num_qo_heads} entries (one per query "
+                             f"head), got {tuple(sinks.shape)} {sinks.dtype}")
+        o.sinks = sinks.data_ptr()
+    return o
+
+
 class BatchDecodeWithPagedKVCacheWrapper:
     """One query token per request against its paged K/V.
 
@@ -409,9 +467,10 @@ class BatchDecodeWithPagedKVCacheWrapper:
         _require_i32(last_page_len, "last_page_len")
         if pos_encoding_mode != "NONE":
             raise ValueError("pos_encoding_mode other than 'NONE' is not supported; apply RoPE before the append")
-        if window_left != -1 or (logits_soft_cap not in (None, 0.0)):
-            raise ValueError("window_left / logits_soft_cap are not supported by the decode wrapper "
-                             "(a sliding window is available through BatchPrefillWithPagedKVCacheWrapper)")
+        if logits_soft_cap not in (None, 0.0):
+            raise ValueError("logits_soft_cap is not supported")
+        if window_left is None or window_left < -1:
+            raise ValueError("window_left must be -1 (no window) or >= 0")
         if num_qo_heads % num_kv_heads != 0:
             raise ValueError(f"num_qo_heads {num_qo_heads} is not a multiple of num_kv_heads {num_kv_heads}")
         if kv_data_type is not None and kv_data_type != q_data_type:
@@ -437,11 +496,13 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError(f"workspace_buffer too small: {self.workspace_buffer.numel()} < {need} bytes")
         self._plan = dict(indptr=indptr, indices=indices, last_page_len=last_page_len, batch=batch,
                           hq=int(num_qo_heads), hkv=int(num_kv_heads), d=int(head_dim), page_size=int(page_size),
-                          dtype=q_data_type,
+                          dtype=q_data_type, window_left=int(window_left),
                           sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim))
 
     def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, out: Optional[torch.Tensor] = None,
-            return_lse: bool = False):
+            return_lse: bool = False, sinks: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None):
+        """`sinks` (float32 [num_qo_heads]) and `sm_scale` are extensions: per-head attention-sink logits and
+        a scale that overrides the planned one (the sink wrapper of the reference passes both at run time)."""
         if self._plan is None:
             raise RuntimeError("Must call plan() before run()")
         pl = self._plan
@@ -461,12 +522,15 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError("out must be a contiguous tensor shaped and typed like q")
         lse = torch.empty((pl["batch"], pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
         ws = self.workspace_buffer
-        check(lib.piekv_decode_run(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
-                                   lse.data_ptr() if lse is not None else None, pl["indptr"].data_ptr(),
-                                   pl["indices"].data_ptr(), pl["last_page_len"].data_ptr(), pl["batch"], pl["hq"],
-                                   pl["hkv"], pl["d"], pl["page_size"], num_pages,
-                                   _dtype_code(q.dtype, "decode run"), pl["sm_scale"], ws.data_ptr(), ws.numel(),
-                                   _err_word(q.device).data_ptr(), _stream(q.device)), "BatchDecode.run")
+        opt = _attn_options(pl["window_left"], sinks, pl["hq"])
+        check(lib.piekv_decode_run_opt(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
+                                       lse.data_ptr() if lse is not None else None, pl["indptr"].data_ptr(),
+                                       pl["indices"].data_ptr(), pl["last_page_len"].data_ptr(), pl["batch"],
+                                       pl["hq"], pl["hkv"], pl["d"], pl["page_size"], num_pages,
+                                       _dtype_code(q.dtype, "decode run"),
+                                       float(sm_scale) if sm_scale is not None else pl["sm_scale"], ws.data_ptr(),
+                                       ws.numel(), _err_word(q.device).data_ptr(), _stream(q.device),
+                                       C.byref(opt) if opt is not None else None), "BatchDecode.run")
         return (out, lse) if return_lse else out
 
     forward = run
@@ -491,7 +555,8 @@ class BatchDecodeWithPagedKVCacheWrapper:
 
     def run_fused(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos_ids: torch.Tensor,
                   paged_kv_cache: torch.Tensor, rope: Optional["RopeConfig"] = None,
-                  out: Optional[torch.Tensor] = None, return_lse: bool = False):
+                  out: Optional[torch.Tensor] = None, return_lse: bool = False,
+                  sinks: Optional[torch.Tensor] = None):
         """One decode step in a single launch: RoPE of q and of the new k at `pos_ids`, append of k / v
         into the last slot of every request's last page, attention over all pages.  Equivalent to the
         reference's per-layer sequence at pie/src/pie_worker/model/llama3.py:660-689, except that q and
@@ -507,14 +572,16 @@ class BatchDecodeWithPagedKVCacheWrapper:
         lse = torch.empty((b, pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
         rp = (rope if rope is not None else RopeConfig()).to_c(d)
         ws = self.workspace_buffer
-        check(lib.piekv_decode_step_fused(q.data_ptr(), k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1],
-                                          vs[0], vs[1], pos_ids.data_ptr(), paged_kv_cache.data_ptr(),
-                                          out.data_ptr(), lse.data_ptr() if lse is not None else None,
-                                          pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
-                                          pl["last_page_len"].data_ptr(), b, pl["hq"], pl["hkv"], pl["d"],
-                                          pl["page_size"], num_pages, _dtype_code(q.dtype, "fused decode"),
-                                          C.byref(rp), pl["sm_scale"], ws.data_ptr(), ws.numel(),
-                                          _err_word(q.device).data_ptr(), _stream(q.device)),
+        opt = _attn_options(pl["window_left"], sinks, pl["hq"])
+        check(lib.piekv_decode_step_fused_opt(q.data_ptr(), k.data_ptr(), v.data_ptr(), qs[0], qs[1], ks[0], ks[1],
+                                              vs[0], vs[1], pos_ids.data_ptr(), paged_kv_cache.data_ptr(),
+                                              out.data_ptr(), lse.data_ptr() if lse is not None else None,
+                                              pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
+                                              pl["last_page_len"].data_ptr(), b, pl["hq"], pl["hkv"], pl["d"],
+                                              pl["page_size"], num_pages, _dtype_code(q.dtype, "fused decode"),
+                                              C.byref(rp), pl["sm_scale"], ws.data_ptr(), ws.numel(),
+                                              _err_word(q.device).data_ptr(), _stream(q.device),
+                                              C.byref(opt) if opt is not None else None),
               "BatchDecode.run_fused")
         return (out, lse) if return_lse else out
 
@@ -536,6 +603,8 @@ class BatchDecodeWithPagedKVCacheWrapper:
             raise ValueError("q, k, v, the cache and the peer buffers must share one dtype")
         if b > peers.batch_max or d != peers.head_dim or pl["hq"] * peers.world > peers.row_heads:
             raise ValueError("peer buffers are too small for this plan")
+        if pl["window_left"] >= 0:
+            raise ValueError("run_fused_peer does not take a sliding window")
         if b == 0:
             # Nothing would be launched, so no flag would be raised: every rank (they share the page tables)
             # skips the step number and the wait instead of spinning until the wait's time limit.
@@ -629,33 +698,23 @@ class BatchPrefillWithPagedKVCacheWrapper:
                 raise ValueError("brle indptr must have nnz + 1 entries")
             brle = (runs, run_indptr, int(mask_bits))
             causal = False
-        if window_left >= 0:
-            # Sliding window (query at position p sees keys p - window_left .. p; the other model families of
-            # the reference plan their wrappers this way, e.g. pie/src/pie_worker/model/olmo3.py:979-1012):
-            # expressed as three runs per query token - attend 0, skip `start`, attend the window - built
-            # with a few device ops, then expanded to the packed mask by the library.  kv tiles outside every
-            # window of a query tile are skipped by the kernel through the mask summary.
-            if custom_mask is not None or brle_mask is not None:
-                raise ValueError("window_left cannot be combined with an explicit mask")
-            if page_size != 16 or head_dim_qk != 128 or q_data_type not in (torch.float16, torch.bfloat16):
-                raise ValueError("window_left needs the tensor-core prefill path (fp16/bf16, head_dim 128, page size 16)")
-            counts = (qo_indptr[1:] - qo_indptr[:-1]).to(torch.int64)
-            seq = get_seq_lens(paged_kv_indptr, paged_kv_last_page_len, page_size).to(torch.int64)
-            n_tok = int(qo_indptr[-1].item())  # plan() is a host-synchronous call in the reference as well
-            req = torch.repeat_interleave(torch.arange(counts.numel(), device=counts.device), counts, output_size=n_tok)
-            j = torch.arange(n_tok, device=counts.device) - qo_indptr[:-1].to(torch.int64)[req]
-            pos = seq[req] - counts[req] + j
-            start = torch.clamp(pos - int(window_left), min=0)
-            runs = torch.stack([torch.zeros_like(start), start, pos + 1 - start], dim=1).to(torch.int32).contiguous()
-            run_indptr = (torch.arange(n_tok + 1, device=counts.device, dtype=torch.int64) * 3).to(torch.int32)
-            brle = (runs.view(-1), run_indptr, int((counts * seq).sum().item()))
-            causal = False
+        window_entries = 0
+        if window_left >= 0 and custom_mask is None and brle is None:
+            # A window without a mask becomes a packed mask on the device (the query at position p sees keys
+            # p - window_left .. p, or .. kv_len - 1 when not causal); kv tiles outside every window of a query
+            # tile are then skipped through the mask summary.  Its size needs sum(qo_len * kv_len): one small
+            # device reduction read back here (plan() is a host-synchronous call in the reference as well).
+            if page_size == 16 and head_dim_qk == 128 and q_data_type in (torch.float16, torch.bfloat16):
+                counts = (qo_indptr[1:] - qo_indptr[:-1]).to(torch.int64)
+                seq = get_seq_lens(paged_kv_indptr, paged_kv_last_page_len, page_size).to(torch.int64)
+                window_entries = int((counts * seq).sum().item())
         batch = qo_indptr.shape[0] - 1
         self._plan = dict(qo_indptr=qo_indptr, indptr=paged_kv_indptr, indices=paged_kv_indices,
                           last_page_len=paged_kv_last_page_len, batch=batch, hq=int(num_qo_heads),
                           hkv=int(num_kv_heads), d=int(head_dim_qk), page_size=int(page_size), mask=mask,
-                          mask_bytes=int(mask.numel()) if mask is not None else (brle[2] if brle else 0),
+                          mask_bytes=int(mask.numel()) if mask is not None else (brle[2] if brle else window_entries),
                           brle=brle, causal=bool(causal), dtype=q_data_type, planned_for=None,
+                          window_left=int(window_left),
                           sm_scale=float(sm_scale) if sm_scale is not None else 1.0 / math.sqrt(head_dim_qk))
 
     def _device_plan(self, n: int, num_pages: int) -> None:
@@ -670,27 +729,23 @@ class BatchPrefillWithPagedKVCacheWrapper:
         if ws.numel() < need:
             raise ValueError(f"workspace_buffer too small: {ws.numel()} < {need} bytes")
         dev = pl["qo_indptr"].device
+        runs_ptr = rptr_ptr = None
         if pl["brle"] is not None:
-            runs, run_indptr, mask_bits = pl["brle"]
+            runs, run_indptr, _ = pl["brle"]
             if run_indptr.shape[0] != n + 1:
                 raise ValueError(f"brle indptr has {run_indptr.shape[0]} entries for {n} query tokens")
-            check(lib.piekv_prefill_plan_brle(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
-                                              pl["last_page_len"].data_ptr(), runs.data_ptr(), run_indptr.data_ptr(),
-                                              mask_bits, pl["batch"], n, pl["page_size"], num_pages, ws.data_ptr(),
-                                              ws.numel(), _err_word(dev).data_ptr(), _stream(dev)),
-                  "BatchPrefill.plan (BRLE)")
-            pl["planned_for"] = key
-            return
-        check(lib.piekv_prefill_plan(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
-                                     pl["last_page_len"].data_ptr(),
-                                     pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
-                                     1 if pl["causal"] else 0, pl["batch"], n, pl["page_size"], num_pages,
-                                     ws.data_ptr(), ws.numel(), _err_word(dev).data_ptr(), _stream(dev)),
-              "BatchPrefill.plan")
+            runs_ptr, rptr_ptr = runs.data_ptr(), run_indptr.data_ptr()
+        check(lib.piekv_prefill_plan_opt(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
+                                         pl["last_page_len"].data_ptr(),
+                                         pl["mask"].data_ptr() if pl["mask"] is not None else None, runs_ptr, rptr_ptr,
+                                         pl["mask_bytes"], 1 if pl["causal"] else 0, pl["window_left"], pl["batch"], n,
+                                         pl["page_size"], num_pages, ws.data_ptr(), ws.numel(),
+                                         _err_word(dev).data_ptr(), _stream(dev)), "BatchPrefill.plan")
         pl["planned_for"] = key
 
     def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, out: Optional[torch.Tensor] = None,
-            return_lse: bool = False):
+            return_lse: bool = False, sinks: Optional[torch.Tensor] = None, sm_scale: Optional[float] = None):
+        """`sinks` (float32 [num_qo_heads]) and `sm_scale` are extensions, see the decode wrapper's run()."""
         if self._plan is None:
             raise RuntimeError("Must call plan() before run()")
         pl = self._plan
@@ -711,16 +766,57 @@ class BatchPrefillWithPagedKVCacheWrapper:
         lse = torch.empty((n, pl["hq"]), dtype=torch.float32, device=q.device) if return_lse else None
         ws = self.workspace_buffer
         self._device_plan(n, num_pages)
-        check(lib.piekv_prefill_run(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
-                                    lse.data_ptr() if lse is not None else None, pl["qo_indptr"].data_ptr(),
-                                    pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
-                                    pl["last_page_len"].data_ptr(),
-                                    pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
-                                    1 if pl["causal"] else 0, 2 if pl["brle"] is not None else 1, pl["batch"], n,
-                                    pl["hq"], pl["hkv"], pl["d"],
-                                    pl["page_size"], num_pages, _dtype_code(q.dtype, "prefill run"),
-                                    pl["sm_scale"], ws.data_ptr(), ws.numel(), _err_word(q.device).data_ptr(),
-                                    _stream(q.device)), "BatchPrefill.run")
+        opt = _attn_options(pl["window_left"], sinks, pl["hq"])
+        check(lib.piekv_prefill_run_opt(q.data_ptr(), qs[0], qs[1], paged_kv_cache.data_ptr(), out.data_ptr(),
+                                        lse.data_ptr() if lse is not None else None, pl["qo_indptr"].data_ptr(),
+                                        pl["indptr"].data_ptr(), pl["indices"].data_ptr(),
+                                        pl["last_page_len"].data_ptr(),
+                                        pl["mask"].data_ptr() if pl["mask"] is not None else None, pl["mask_bytes"],
+                                        1 if pl["causal"] else 0, 2 if pl["brle"] is not None else 1, pl["batch"], n,
+                                        pl["hq"], pl["hkv"], pl["d"],
+                                        pl["page_size"], num_pages, _dtype_code(q.dtype, "prefill run"),
+                                        float(sm_scale) if sm_scale is not None else pl["sm_scale"], ws.data_ptr(),
+                                        ws.numel(), _err_word(q.device).data_ptr(), _stream(q.device),
+                                        C.byref(opt) if opt is not None else None), "BatchPrefill.run")
         return (out, lse) if return_lse else out
+
+    forward = run
+
+
+class BatchAttentionWithAttentionSinkWrapper(BatchPrefillWithPagedKVCacheWrapper):
+    """Paged attention with per-head attention sinks and an optional sliding window fixed at construction.
+
+    Reference construction and use: pie/src/pie_worker/model/gpt_oss.py:418-439 (two wrappers, one with
+    `window_left = sliding_window - 1`, one without), plan 840-870 (the prefill wrapper's positional
+    arguments with `causal=True` and the same window), run 693-697: `run(q, kv_cache_layer, sinks, scaling)`.
+    The head's sink logit joins the softmax normaliser only.  Decode batches (one query token per request)
+    go through the same planned call."""
+
+    def __init__(self, float_workspace_buffer: torch.Tensor, kv_layout: str = "NHD", window_left: int = -1,
+                 q_data_type: Optional[torch.dtype] = None, kv_data_type: Optional[torch.dtype] = None,
+                 head_dim_qk: Optional[int] = None, head_dim_vo: Optional[int] = None, **_ignored) -> None:
+        super().__init__(float_workspace_buffer, kv_layout)
+        if head_dim_qk is not None and head_dim_vo is not None and head_dim_qk != head_dim_vo:
+            raise ValueError("head_dim_vo must equal head_dim_qk")
+        if kv_data_type is not None and q_data_type is not None and kv_data_type != q_data_type:
+            raise ValueError("kv_data_type must equal q_data_type")
+        self._window_left = int(window_left)
+        self._q_data_type = q_data_type
+
+    def plan(self, qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, num_kv_heads,
+             head_dim_qk, page_size, causal: bool = False, window_left: Optional[int] = None,
+             q_data_type: Optional[torch.dtype] = None, kv_data_type: Optional[torch.dtype] = None,
+             non_blocking: bool = True, **kw) -> None:
+        wl = self._window_left if window_left is None else int(window_left)
+        dt = q_data_type or self._q_data_type or torch.float16
+        super().plan(qo_indptr, paged_kv_indptr, paged_kv_indices, paged_kv_last_page_len, num_qo_heads, num_kv_heads,
+                     head_dim_qk, page_size, causal=causal, window_left=wl, q_data_type=dt, kv_data_type=kv_data_type,
+                     **kw)
+
+    def run(self, q: torch.Tensor, paged_kv_cache: torch.Tensor, sinks: Optional[torch.Tensor] = None,
+            sm_scale: Optional[float] = None, out: Optional[torch.Tensor] = None, return_lse: bool = False):
+        if sinks is not None and sinks.dtype != torch.float32:
+            sinks = sinks.to(torch.float32)
+        return super().run(q, paged_kv_cache, out=out, return_lse=return_lse, sinks=sinks, sm_scale=sm_scale)
 
     forward = run

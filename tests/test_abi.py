@@ -28,7 +28,7 @@ def test_header_and_bindings_agree():
 
 
 def test_version_and_error_text():
-    assert _lib.lib.piekv_version() == 100
+    assert _lib.lib.piekv_version() == 101
     rc = _lib.lib.piekv_get_seq_lens(None, None, 4, 16, None, None)
     assert rc > 0
     assert b"null" in _lib.lib.piekv_last_error_string()
@@ -84,6 +84,7 @@ def test_struct_mirrors_have_the_size_the_library_reports():
     from pie_b200 import _lib
     assert _lib.lib.piekv_abi_sizeof(0) == C.sizeof(_lib.RopeParams)
     assert _lib.lib.piekv_abi_sizeof(1) == C.sizeof(_lib.PeerOutputsC)
+    assert _lib.lib.piekv_abi_sizeof(2) == C.sizeof(_lib.AttnOptions)
     assert _lib.lib.piekv_abi_sizeof(99) == -1
 
 

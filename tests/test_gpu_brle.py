@@ -135,30 +135,3 @@ def test_brle_plan_rejects_what_it_cannot_serve():
     with pytest.raises(ValueError):   # both mask forms at once
         w.plan(i32(0, 1), i32(0, 1), i32(0), i32(3), 4, 2, 128, 16, brle_mask=brle,
                custom_mask=torch.ones(3, dtype=torch.bool, device="cuda"), q_data_type=torch.bfloat16)
-
-
-@pytest.mark.parametrize("window", [0, 7, 100, 5000])
-def test_sliding_window_through_the_run_length_mask(window):
-    """plan(window_left=W): query at position p sees keys p-W .. p (and nothing after p)."""
-    from tests.util import make_scenario
-    reqs = [(0, 300), (511, 130), (96, 1)]
-    sc = make_scenario(4, 2, 128, torch.bfloat16, reqs, seed=41, scale=0.5)
-    m = sc.meta
-    mask = []
-    for ctx, new in reqs:
-        kv = ctx + new
-        for j in range(new):
-            p = ctx + j
-            row = np.zeros(kv, dtype=bool)
-            row[max(0, p - window): p + 1] = True
-            mask.append(row)
-    flat = np.concatenate(mask)
-    ref = R.prefill_attention(sc.q, sc.pool, m.qo_indptr, m.kv_indptr, m.kv_indices, m.kv_last_page_len,
-                              custom_mask=flat, causal=False)
-    ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
-    w = ops.BatchPrefillWithPagedKVCacheWrapper(ws, "NHD")
-    w.plan(dev(m.qo_indptr), dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), 4, 2, 128, 16,
-           window_left=window, q_data_type=torch.bfloat16)
-    out = w.run(sc.q.cuda(), sc.pool.cuda()).cpu()
-    assert ops.device_error("cuda") is None
-    assert (out.float() - ref.float()).abs().max().item() <= 2e-2

@@ -154,3 +154,39 @@ def test_append_skips_out_of_range_and_copy_pages():
     assert pool.abs().sum() == k[0].abs().sum() * 2 + k[2].abs().sum() * 2
     R.copy_pages([pool], [2], [0], [2])
     assert torch.equal(pool[0, :, :2], pool[2, :, :2]) and pool[0, :, 2:].abs().sum() == 0
+
+
+def test_oracle_window_and_sinks_against_a_dense_float64_softmax():
+    """Window: only keys p - W .. p (decode: p = kv_len - 1).  Sinks: softmax over [scores, sink], value of the
+    sink dropped.  Both against a direct float64 evaluation."""
+    import math
+    from tests.util import make_scenario
+    sc = make_scenario(4, 2, 64, torch.float32, [(36, 1), (99, 1)], seed=5)
+    m = sc.meta
+    sinks = torch.tensor([0.3, -1.0, 2.0, 0.0])
+    W_ = 10
+    out, lse = R.decode_attention(sc.q, sc.pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len, return_lse=True,
+                                  window_left=W_, sinks=sinks)
+    scale = 1.0 / math.sqrt(64)
+    for b in range(2):
+        k, v = R.gather_kv(sc.pool, m.kv_indices, m.kv_indptr, m.kv_last_page_len, b)
+        k, v = k[-(W_ + 1):].double(), v[-(W_ + 1):].double()
+        for h in range(4):
+            s = (k[:, h // 2] @ sc.q[b, h].double()) * scale
+            z = torch.cat([s, sinks[h: h + 1].double()])
+            p = torch.softmax(z, dim=0)[:-1]
+            want = p @ v[:, h // 2]
+            assert (out[b, h].double() - want).abs().max().item() < 1e-5
+            assert abs(lse[b, h].item() - torch.logsumexp(z, 0).item()) < 1e-4
+    # prefill: a window ANDed with a mask
+    sc = make_scenario(2, 1, 64, torch.float32, [(20, 6)], seed=6)
+    m = sc.meta
+    mask = np.ones(6 * 26, dtype=bool)
+    out = R.prefill_attention(sc.q, sc.pool, m.qo_indptr, m.kv_indptr, m.kv_indices, m.kv_last_page_len,
+                              custom_mask=mask, window_left=3)
+    k, v = R.gather_kv(sc.pool, m.kv_indices, m.kv_indptr, m.kv_last_page_len, 0)
+    for j in range(6):
+        lo = 20 + j - 3
+        s = (k[lo:, 0].double() @ sc.q[j, 1].double()) * (1.0 / math.sqrt(64))  # the all-true mask does not bound above
+        want = torch.softmax(s, 0) @ v[lo:, 0].double()
+        assert (out[j, 1].double() - want).abs().max().item() < 1e-5
