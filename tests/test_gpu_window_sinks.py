@@ -180,7 +180,8 @@ def test_prefill_window_together_with_a_custom_mask(window, form):
     assert (out.float() - ref.float()).abs().max().item() <= TOL16
     no_window = R.prefill_attention(sc.q, sc.pool, m.qo_indptr, m.kv_indptr, m.kv_indices, m.kv_last_page_len,
                                     custom_mask=flat)
-    assert (no_window.float() - ref.float()).abs().max().item() > 1e-2  # the window did cut something
+    if window < 400:  # (the largest one spans every context here: the same result as without it)
+        assert (no_window.float() - ref.float()).abs().max().item() > 1e-2  # the window did cut something
 
 
 def test_prefill_window_general_kernel_fp32():
