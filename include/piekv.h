@@ -55,6 +55,9 @@ extern "C" {
 #define PIEKV_ERR_WAIT_TIMEOUT 5  /* a bounded on-chip wait ran out                         */
 #define PIEKV_ERR_TABLE_RANGE 6   /* RoPE table position outside [0,table_len)              */
 #define PIEKV_ERR_INDPTR 7        /* non-monotone indptr                                    */
+#define PIEKV_ERR_NO_FREE_PAGE 8  /* device page table: fewer free pages than the call needs */
+#define PIEKV_ERR_PAGE_CAPACITY 9 /* device page table: a request outgrew its row, or too many pages in one call */
+#define PIEKV_ERR_SLOT 10         /* device page table: bad request slot / fork into a used slot */
 
 /* RoPE parameters.  Reference arguments: apply_llama31_rope_pos_ids_inplace(q, k,
  * pos_ids, rope_scale, rope_theta, low_freq_factor, high_freq_factor, old_context_len)
@@ -389,6 +392,51 @@ int piekv_copy_pages(void *const *pools, int32_t num_layers, const int32_t *src_
                      const int32_t *dst_pages, const int32_t *valid_len, int32_t count,
                      int32_t page_size, int32_t num_kv_heads, int32_t head_dim, int32_t num_pages,
                      int32_t dtype, int32_t *err, void *stream);
+
+/* ---- page tables, reference counts and the free list on the device -------------------------------
+ *
+ * The reference keeps page ownership on the host: an id pool that hands out the smallest free id
+ * (runtime/src/utils.rs:42-158), contexts that grow by whole pages as tokens arrive (adjust_kv_pages,
+ * sdk/rust/inferlet/src/context.rs:356-399), forks that share full pages (context.rs:147-225) and pages
+ * that return to the pool with their last holder (sdk/rust/inferlet/src/forward.rs:28-55); every step
+ * the page tables are rebuilt and uploaded (pie/src/pie_worker/batching.py:196-239).  These entry points
+ * keep the same bookkeeping in device memory, advanced by small stream-ordered kernels, so a decode loop
+ * or a beam search runs (and can be captured in a CUDA graph) without host page tables.
+ *
+ * `state` is a caller-owned device buffer of piekv_pagestate_bytes() bytes holding, for `max_requests`
+ * request slots of up to `pages_per_request` pages each: page rows, page counts, last-page fill, one
+ * reference count per physical page and the free bitmap.  The four size arguments must be the same in
+ * every call on one state.  Slot lists are DEVICE int32 arrays; a slot appears at most once per call.
+ * Requests are served in list order and the i-th page a call needs is the i-th smallest free id - what
+ * a host loop over the same list does with the reference's id pool.  Problems (no free page, a row
+ * that is full, a bad slot) are reported through the error word and the call changes nothing further.
+ * No counterpart in the reference as device code. */
+int64_t piekv_pagestate_bytes(int32_t num_pages, int32_t max_requests, int32_t pages_per_request);
+/* every page free, every slot empty */
+int piekv_pagestate_init(void *state, int64_t state_bytes, int32_t num_pages, int32_t max_requests,
+                         int32_t pages_per_request, int32_t page_size, void *stream);
+/* Grow (delta > 0) or shrink (delta < 0) the listed requests by deltas[i] tokens, or by delta_all when
+ * deltas == NULL (a decode step: 1); shrinks release their pages before any page is handed out.
+ * At most 1024 requests and 4096 new pages per call.  Optional outputs (NULL: skip), the CSR page table
+ * of exactly this batch as the attention entry points take it: kv_indptr [count + 1], kv_indices
+ * [kv_indptr[count]], kv_last_page_len [count], and pos_ids [count] = tokens held before the call
+ * (the RoPE position of the first new token). */
+int piekv_pagestate_adjust(void *state, int32_t num_pages, int32_t max_requests, int32_t pages_per_request,
+                           int32_t page_size, const int32_t *slots, const int32_t *deltas,
+                           int32_t delta_all, int32_t count, int32_t *kv_indptr, int32_t *kv_indices,
+                           int32_t *kv_last_page_len, int32_t *pos_ids, int32_t *err, void *stream);
+/* The listed requests let go of all their pages; pages without a holder return to the free list. */
+int piekv_pagestate_release(void *state, int32_t num_pages, int32_t max_requests, int32_t pages_per_request,
+                            int32_t page_size, const int32_t *slots, int32_t count, int32_t *err,
+                            void *stream);
+/* children[i] (an empty slot, not a parent of this call) becomes a copy-on-write fork of parents[i]:
+ * full pages shared by reference count, a partly filled last page replaced by a fresh page.  Outputs
+ * (device, [count]): the page copies that complete the forks, to be passed to piekv_copy_pages with the
+ * same `count` (entries with nothing to copy have valid 0 and src == dst).  At most 1024 forks per call. */
+int piekv_pagestate_fork(void *state, int32_t num_pages, int32_t max_requests, int32_t pages_per_request,
+                         int32_t page_size, const int32_t *parents, const int32_t *children, int32_t count,
+                         int32_t *copy_src, int32_t *copy_dst, int32_t *copy_valid, int32_t *err,
+                         void *stream);
 
 /* ---- page bookkeeping on the host (no GPU work) ---------------------------------------------
  *

@@ -25,6 +25,9 @@ ERR_NAMES = {
     5: "bounded on-chip wait timed out",
     6: "RoPE table position out of range",
     7: "non-monotone indptr",
+    8: "device page table: not enough free pages",
+    9: "device page table: request row full / too many pages in one call",
+    10: "device page table: bad slot",
 }
 
 
@@ -138,6 +141,11 @@ SIGNATURES = {
     ),
     "piekv_peer_wait": (C.c_int, [_p, _i32, _i32, _p, _p]),
     "piekv_peer_wait_counted": (C.c_int, [_p, _i32, _p, _p, _p]),
+    "piekv_pagestate_bytes": (_i64, [_i32, _i32, _i32]),
+    "piekv_pagestate_init": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32, _p]),
+    "piekv_pagestate_adjust": (C.c_int, [_p, _i32, _i32, _i32, _i32, _p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p]),
+    "piekv_pagestate_release": (C.c_int, [_p, _i32, _i32, _i32, _i32, _p, _i32, _p, _p]),
+    "piekv_pagestate_fork": (C.c_int, [_p, _i32, _i32, _i32, _i32, _p, _p, _i32, _p, _p, _p, _p, _p]),
     "piekv_pages_create": (C.c_void_p, [_i32]),
     "piekv_pages_destroy": (None, [_p]),
     "piekv_pages_available": (_i32, [_p]),

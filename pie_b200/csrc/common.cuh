@@ -60,6 +60,7 @@ enum KernelId : int {
   KID_DECODE = 6,
   KID_PREFILL = 7,
   KID_PEER = 8,
+  KID_PAGES = 9,
 };
 
 // ---- device side -------------------------------------------------------------------

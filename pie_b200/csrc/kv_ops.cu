@@ -487,25 +487,28 @@ struct PoolPtrs {
   void *p[kMaxLayersPerLaunch];
 };
 
-// grid (pair, K|V, layer).  The first `valid` rows of a page half are one contiguous run of
-// valid * Hkv * D elements, so the copy is a flat 16-byte-vector memcpy.
+// grid (pair * parts, K|V, layer).  The first `valid` rows of a page half are one contiguous run of
+// valid * Hkv * D elements, so the copy is a flat 16-byte-vector memcpy; a half is cut into `parts`
+// slices, one CTA each, so that a handful of pairs (a beam fork copies a few dozen pages) still
+// spreads over all SMs.  Every thread keeps four 16-byte loads in flight.
 __global__ void copy_pages_kernel(PoolPtrs pools, const int32_t *__restrict__ src, const int32_t *__restrict__ dst,
                                   const int32_t *__restrict__ valid_len, int page_size, size_t row_bytes,
-                                  int num_pages, int32_t *err) {
-  const int j = blockIdx.x;
+                                  int num_pages, int parts, int32_t *err) {
+  const int j = blockIdx.x / parts;
+  const int part = blockIdx.x % parts;
   const int kv = blockIdx.y;
   char *base = reinterpret_cast<char *>(pools.p[blockIdx.z]);
   int s = src[j], d = dst[j];
   int valid = valid_len != nullptr ? valid_len[j] : page_size;
   if (s < 0 || s >= num_pages || d < 0 || d >= num_pages) {
-    if (threadIdx.x == 0) report_error(err, PIEKV_ERR_PAGE_ID, KID_COPY, j, s < 0 || s >= num_pages ? s : d);
+    if (threadIdx.x == 0 && part == 0) report_error(err, PIEKV_ERR_PAGE_ID, KID_COPY, j, s < 0 || s >= num_pages ? s : d);
     return;
   }
   if (valid < 0 || valid > page_size) {
-    if (threadIdx.x == 0) report_error(err, PIEKV_ERR_LAST_PAGE_LEN, KID_COPY, j, valid);
+    if (threadIdx.x == 0 && part == 0) report_error(err, PIEKV_ERR_LAST_PAGE_LEN, KID_COPY, j, valid);
     return;
   }
-  if (s == d) return;
+  if (s == d || valid == 0) return;
   size_t half_bytes = (size_t)page_size * row_bytes;
   const char *sp = base + ((size_t)s * 2 + kv) * half_bytes;
   char *dp = base + ((size_t)d * 2 + kv) * half_bytes;
@@ -513,10 +516,25 @@ __global__ void copy_pages_kernel(PoolPtrs pools, const int32_t *__restrict__ sr
   if ((row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
     const uint4 *s4 = reinterpret_cast<const uint4 *>(sp);
     uint4 *d4 = reinterpret_cast<uint4 *>(dp);
-    size_t n = bytes >> 4;
-    for (size_t i = threadIdx.x; i < n; i += blockDim.x) d4[i] = s4[i];
+    const size_t n = bytes >> 4;
+    const size_t per = (n + parts - 1) / parts;
+    const size_t lo = (size_t)part * per;
+    const size_t hi = lo + per < n ? lo + per : n;
+    size_t i = lo + threadIdx.x;
+    const size_t step = blockDim.x;
+    for (; i + 3 * step < hi; i += 4 * step) {
+      const uint4 a0 = s4[i], a1 = s4[i + step], a2 = s4[i + 2 * step], a3 = s4[i + 3 * step];
+      d4[i] = a0;
+      d4[i + step] = a1;
+      d4[i + 2 * step] = a2;
+      d4[i + 3 * step] = a3;
+    }
+    for (; i < hi; i += step) d4[i] = s4[i];
   } else {
-    for (size_t i = threadIdx.x; i < bytes; i += blockDim.x) dp[i] = sp[i];
+    const size_t per = (bytes + parts - 1) / parts;
+    const size_t lo = (size_t)part * per;
+    const size_t hi = lo + per < bytes ? lo + per : bytes;
+    for (size_t i = lo + threadIdx.x; i < hi; i += blockDim.x) dp[i] = sp[i];
   }
 }
 
@@ -720,8 +738,11 @@ extern "C" int piekv_copy_pages(void *const *pools, int32_t num_layers, const in
       PIEKV_REQUIRE(pools[l0 + i] != nullptr, "copy_pages: pool %d is null", l0 + i);
       pp.p[i] = pools[l0 + i];
     }
-    copy_pages_kernel<<<dim3(count, 2, nl), 256, 0, (cudaStream_t)stream>>>(pp, src_pages, dst_pages, valid_len,
-                                                                             page_size, row_bytes, num_pages, err);
+    // enough CTAs for two waves over the SMs even when only a few pages are copied
+    int parts = 1;
+    while (parts < 8 && (long long)count * 2 * nl * parts < 2ll * sm_count()) parts *= 2;
+    copy_pages_kernel<<<dim3((unsigned)count * parts, 2, nl), 256, 0, (cudaStream_t)stream>>>(
+        pp, src_pages, dst_pages, valid_len, page_size, row_bytes, num_pages, parts, err);
     PIEKV_LAUNCH_CHECK("copy_pages_kernel");
   }
   return 0;

@@ -312,3 +312,119 @@ class NativePageManager:
 
     def release_exported(self, name: str) -> None:
         self._lib.check(self._lib.lib.piekv_pages_release_exported(self._h, name.encode()), "pages_release_exported")
+
+
+class DevicePageTable:
+    """Page tables, reference counts and the free list of one pool kept in DEVICE memory
+    (`piekv_pagestate_*`): the same rules as `IdPool` / `PagePool` / `KvPageList` above - smallest free id
+    first, pages = ceil(tokens / page_size), forks share full pages and copy a partial one, a page goes back
+    to the free list with its last holder - advanced by small stream-ordered kernels.  A decode loop, or a
+    beam search that forks and drops contexts, then runs without the host building or uploading a page
+    table, and the whole step can sit in a CUDA graph.
+
+    Requests live in numbered slots.  Slot lists are int32 device tensors (a slot at most once per call);
+    requests are served in list order, exactly like a host loop over the same list."""
+
+    def __init__(self, num_pages: int, max_requests: int, pages_per_request: int, page_size: int = 16,
+                 device="cuda", max_batch: Optional[int] = None) -> None:
+        import torch
+
+        from . import _lib, ops
+        self._torch, self._lib, self._ops = torch, _lib, ops
+        self.num_pages, self.max_requests = int(num_pages), int(max_requests)
+        self.pages_per_request, self.page_size = int(pages_per_request), int(page_size)
+        self.device = torch.device(device)
+        nbytes = int(_lib.lib.piekv_pagestate_bytes(self.num_pages, self.max_requests, self.pages_per_request))
+        self.state = torch.empty(nbytes // 4, dtype=torch.int32, device=self.device)
+        mb = int(max_batch or min(self.max_requests, 1024))
+        self.max_batch = mb
+        i32 = dict(dtype=torch.int32, device=self.device)
+        self.kv_indptr = torch.zeros(mb + 1, **i32)
+        self.kv_indices = torch.zeros(mb * self.pages_per_request, **i32)
+        self.kv_last_page_len = torch.zeros(mb, **i32)
+        self.pos_ids = torch.zeros(mb, **i32)
+        self.copy_src = torch.zeros(mb, **i32)
+        self.copy_dst = torch.zeros(mb, **i32)
+        self.copy_valid = torch.zeros(mb, **i32)
+        _lib.check(_lib.lib.piekv_pagestate_init(self.state.data_ptr(), nbytes, *self._dims(), self._stream()),
+                   "pagestate_init")
+
+    def _dims(self):
+        return self.num_pages, self.max_requests, self.pages_per_request, self.page_size
+
+    def _stream(self):
+        return self._ops._stream(self.device)
+
+    def _err(self):
+        return self._ops._err_word(self.device).data_ptr()
+
+    def _slots(self, slots, name="slots"):
+        self._ops._require_i32(slots, name)
+        if slots.shape[0] > self.max_batch:
+            raise ValueError(f"{name}: {slots.shape[0]} entries, this table was built for {self.max_batch}")
+        return slots
+
+    def grow(self, slots, delta=1, csr: bool = True):
+        """Make room for `delta` more tokens (an int for all, or an int32 device tensor per request; negative
+        values shrink) in the listed requests - `adjust_kv_pages` of the reference
+        (sdk/rust/inferlet/src/context.rs:356-399).  With `csr`, the page table of exactly this batch is
+        written to this object's buffers and returned as views:
+        (kv_indptr, kv_indices, kv_last_page_len, pos_ids); pos_ids = tokens held before the call."""
+        slots = self._slots(slots)
+        n = slots.shape[0]
+        torch = self._torch
+        deltas_ptr, delta_all = None, 0
+        if isinstance(delta, torch.Tensor):
+            self._ops._require_i32(delta, "delta")
+            if delta.shape[0] != n:
+                raise ValueError("delta: one entry per slot")
+            deltas_ptr = delta.data_ptr()
+        else:
+            delta_all = int(delta)
+        self._lib.check(self._lib.lib.piekv_pagestate_adjust(
+            self.state.data_ptr(), *self._dims(), slots.data_ptr(), deltas_ptr, delta_all, n,
+            self.kv_indptr.data_ptr() if csr else None, self.kv_indices.data_ptr() if csr else None,
+            self.kv_last_page_len.data_ptr() if csr else None, self.pos_ids.data_ptr() if csr else None,
+            self._err(), self._stream()), "pagestate_adjust")
+        if not csr:
+            return None
+        return self.kv_indptr[: n + 1], self.kv_indices, self.kv_last_page_len[:n], self.pos_ids[:n]
+
+    def table_of(self, slots):
+        """The CSR page table of a batch without changing it."""
+        return self.grow(slots, 0, csr=True)
+
+    def release(self, slots) -> None:
+        """The listed requests let go of all their pages (`KvPageList.release`)."""
+        slots = self._slots(slots)
+        self._lib.check(self._lib.lib.piekv_pagestate_release(self.state.data_ptr(), *self._dims(), slots.data_ptr(),
+                                                              slots.shape[0], self._err(), self._stream()),
+                        "pagestate_release")
+
+    def fork(self, parents, children):
+        """children[i] becomes a copy-on-write fork of parents[i] (`KvPageList.fork_cow`).  Returns the device
+        tensors (src_pages, dst_pages, valid_len) for `ops.copy_kv_pages`, one entry per fork (valid 0 where the
+        parent's last page was full and is shared)."""
+        parents, children = self._slots(parents, "parents"), self._slots(children, "children")
+        n = parents.shape[0]
+        if children.shape[0] != n:
+            raise ValueError("parents and children differ in length")
+        self._lib.check(self._lib.lib.piekv_pagestate_fork(
+            self.state.data_ptr(), *self._dims(), parents.data_ptr(), children.data_ptr(), n,
+            self.copy_src.data_ptr(), self.copy_dst.data_ptr(), self.copy_valid.data_ptr(), self._err(),
+            self._stream()), "pagestate_fork")
+        return self.copy_src[:n], self.copy_dst[:n], self.copy_valid[:n]
+
+    def snapshot(self) -> dict:
+        """Host copy of the whole state (synchronises): free page count, per-slot page lists and last-page
+        fill, reference counts, and the set of free ids."""
+        w = self.state.cpu().numpy()
+        r, c, p = self.max_requests, self.pages_per_request, self.num_pages
+        npages = w[16: 16 + r].copy()
+        last = w[16 + r: 16 + 2 * r].copy()
+        table = w[16 + 2 * r: 16 + 2 * r + r * c].reshape(r, c)
+        refs = w[16 + 2 * r + r * c: 16 + 2 * r + r * c + p].copy()
+        bits = w[16 + 2 * r + r * c + p:].view(np.uint32)
+        free = np.unpackbits(bits.view(np.uint8), bitorder="little")[:p].astype(bool)
+        return {"free_pages": int(w[0]), "npages": npages, "last_page_len": last,
+                "pages": [table[i, : npages[i]].tolist() for i in range(r)], "refs": refs, "free": free}
