@@ -254,6 +254,44 @@ int piekv_prefill_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, con
                       int32_t dtype, float sm_scale, void *workspace, int64_t workspace_bytes,
                       int32_t *err, void *stream);
 
+/* ---- the wire form of a batch, decoded on the device ------------------------------------------------
+ *
+ * The reference's runtime sends a step's metadata as little-endian uint32 arrays
+ * (BatchedForwardPassRequest, runtime/src/model/request.rs:250-298); its worker decodes them with numpy,
+ * derives per-token arrays, expands the run-length masks on the CPU and uploads each array
+ * (pie/src/pie_worker/batching.py:28-135,196-239).  With these entry points the arrays are uploaded as
+ * they arrive - concatenated in ONE device buffer `wire`, each field at the word offset `piekv_wire_batch`
+ * names - and the per-token work happens on the device.  The index arrays are used in place:
+ * `(const int32_t *)(wire + layout.kv_page_indptr)` etc. are what the attention entry points take, and
+ * (wire + flattened_masks, wire + mask_indptr) is the `brle_runs` / `brle_indptr` pair of
+ * piekv_prefill_plan_opt. */
+typedef struct piekv_wire_batch {
+  int64_t token_ids, position_ids, kv_page_indices, kv_page_indptr, kv_last_page_lens, qo_indptr,
+      flattened_masks, mask_indptr; /* offsets of the fields in `wire`, in 32-bit words            */
+  int32_t nnz;                      /* tokens: entries of token_ids / position_ids                 */
+  int32_t batch;                    /* requests: kv_page_indptr and qo_indptr hold batch + 1 words  */
+  int32_t total_pages;              /* entries of kv_page_indices                                   */
+  int32_t num_runs;                 /* entries of flattened_masks; mask_indptr holds nnz + 1 words  */
+} piekv_wire_batch;
+
+/* Outputs (each nullable): token_ids_out int64 [nnz] (batching.py:206-208); seq_lens_out [batch];
+ * batch_indices_out / positions_out [nnz] (both or neither) - request and kv position of every token,
+ * the latter also being the position the reference derives for the mask rows (batching.py:113-122);
+ * token_acc_seq_lens_out int64 [nnz + 1], the reference's per-token offsets into the flat mask
+ * (batching.py:124-126; at most 4096 requests).  `lay` is a host struct. */
+int piekv_batch_from_wire(const uint32_t *wire, const piekv_wire_batch *lay, int32_t page_size,
+                          int64_t *token_ids_out, int32_t *seq_lens_out, int32_t *batch_indices_out,
+                          int32_t *positions_out, int64_t *token_acc_seq_lens_out, void *stream);
+
+/* The mask a prefill plan holds in `workspace` (built from bytes, run lengths and / or a window) written
+ * out in the reference's flat form: one byte per (query, key) pair, rows of kv_len_b entries, requests
+ * end to end (`custom_mask` of batching.py:113-135,228-230).  For callers that still want that tensor,
+ * and for checking the device-built mask against the reference's.  `mask_entries` as given to the plan. */
+int piekv_prefill_export_mask(const int32_t *qo_indptr, const int32_t *kv_indptr,
+                              const int32_t *kv_last_page_len, int64_t mask_entries, int32_t batch,
+                              int32_t nnz, int32_t page_size, int32_t num_pages, const void *workspace,
+                              int64_t workspace_bytes, uint8_t *flat_out, void *stream);
+
 /* ---- sliding window and attention sinks ----------------------------------------------------------
  *
  * Other model families of the reference plan their wrappers with `window_left` (a different one per
@@ -378,7 +416,8 @@ int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_c
                             void *stream);
 
 /* sizeof of the structs that cross this boundary, for bindings to check their mirrors against:
- * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options; anything else: -1. */
+ * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options, 3: piekv_wire_batch; anything
+ * else: -1. */
 int32_t piekv_abi_sizeof(int32_t which);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */

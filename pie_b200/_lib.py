@@ -53,6 +53,14 @@ class AttnOptions(C.Structure):
     _fields_ = [("window_left", C.c_int32), ("reserved", C.c_int32), ("sinks", C.c_void_p)]
 
 
+class WireBatch(C.Structure):
+    """Mirror of `piekv_wire_batch`."""
+
+    _fields_ = [(n, C.c_int64) for n in ("token_ids", "position_ids", "kv_page_indices", "kv_page_indptr",
+                                         "kv_last_page_lens", "qo_indptr", "flattened_masks", "mask_indptr")] + \
+               [(n, C.c_int32) for n in ("nnz", "batch", "total_pages", "num_runs")]
+
+
 MAX_PEERS = 8
 PEER_HANDLE_BYTES = 64
 
@@ -141,6 +149,8 @@ SIGNATURES = {
     ),
     "piekv_peer_wait": (C.c_int, [_p, _i32, _i32, _p, _p]),
     "piekv_peer_wait_counted": (C.c_int, [_p, _i32, _p, _p, _p]),
+    "piekv_batch_from_wire": (C.c_int, [_p, C.POINTER(WireBatch), _i32, _p, _p, _p, _p, _p, _p]),
+    "piekv_prefill_export_mask": (C.c_int, [_p, _p, _p, _i64, _i32, _i32, _i32, _i32, _p, _i64, _p, _p]),
     "piekv_pagestate_bytes": (_i64, [_i32, _i32, _i32]),
     "piekv_pagestate_init": (C.c_int, [_p, _i64, _i32, _i32, _i32, _i32, _p]),
     "piekv_pagestate_adjust": (C.c_int, [_p, _i32, _i32, _i32, _i32, _p, _p, _i32, _i32, _p, _p, _p, _p, _p, _p]),

@@ -119,3 +119,94 @@ class Batch:
             "single_token_inference_mode": self.single_token_mode,
             "total_pages_cpu": self.kv_page_indptr[-1] if len(self.kv_page_indptr) else 0,
         }
+
+
+WIRE_FIELDS = ("token_ids", "position_ids", "kv_page_indices", "kv_page_indptr", "kv_last_page_lens", "qo_indptr",
+               "flattened_masks", "mask_indptr")
+
+
+class DeviceBatch:
+    """A batched forward-pass request taken to the device in its wire form.
+
+    The eight uint32 arrays of `BatchedForwardPassRequest` (runtime/src/model/request.rs:250-298) are
+    concatenated into one pinned host buffer and uploaded with ONE copy; what `Batch.__init__` derives on the
+    host per token or per (query, key) pair (pie/src/pie_worker/batching.py:96-135) is derived on the device:
+    `seq_lens`, `batch_indices`, `positions` (kv slot of every token = the position the mask rows are cut at),
+    int64 `token_ids`, optionally `token_acc_seq_lens`, and - through
+    `BatchPrefillWithPagedKVCacheWrapper.plan(brle_mask=batch.brle_inputs())` - the attention mask, bit-packed
+    straight from the run lengths.  The index tensors (`kv_page_indptr`, `kv_page_indices`, `kv_last_page_lens`,
+    `qo_indptr`, `position_ids`) are int32 VIEWS of the uploaded buffer: no conversion, no second copy.
+    The only host work is O(requests): the field lengths and the number of mask entries."""
+
+    def __init__(self, args: Dict[str, Any], kv_page_size: int, device="cuda", acc_seq_lens: bool = False) -> None:
+        import ctypes as C
+
+        from . import _lib, ops
+        dev = torch.device(device)
+        fields = {k: np.ascontiguousarray(_u32(args[k])) for k in WIRE_FIELDS}
+        lay = _lib.WireBatch()
+        off = 0
+        for k in WIRE_FIELDS:
+            setattr(lay, k, off)
+            off += int(fields[k].size)
+        lay.nnz = int(fields["token_ids"].size)
+        lay.batch = max(int(fields["qo_indptr"].size) - 1, 0)
+        lay.total_pages = int(fields["kv_page_indices"].size)
+        lay.num_runs = int(fields["flattened_masks"].size)
+        if fields["kv_page_indptr"].size != lay.batch + 1 or fields["kv_last_page_lens"].size != lay.batch:
+            raise ValueError("kv_page_indptr / kv_last_page_lens / qo_indptr describe different batch sizes")
+        if fields["position_ids"].size != lay.nnz or fields["mask_indptr"].size not in (0, lay.nnz + 1):
+            raise ValueError("position_ids / mask_indptr do not match the number of tokens")
+        host = torch.empty(max(off, 1), dtype=torch.int32).pin_memory()
+        hv = host.numpy().view(np.uint32)
+        for k in WIRE_FIELDS:
+            o = getattr(lay, k)
+            hv[o: o + fields[k].size] = fields[k]
+        self.wire = host.to(dev, non_blocking=True)  # the one upload
+        self.layout = lay
+        self.page_size = int(kv_page_size)
+        self.single_token_mode = bool(args.get("single_token_mode", False))
+        self.total_tokens, self.batch = lay.nnz, lay.batch
+        self.total_pages_cpu = lay.total_pages
+
+        def view(name, n):
+            o = getattr(lay, name)
+            return self.wire[o: o + n]
+
+        self.position_ids = view("position_ids", lay.nnz)
+        self.kv_page_indices = view("kv_page_indices", lay.total_pages)
+        self.kv_page_indptr = view("kv_page_indptr", lay.batch + 1)
+        self.kv_last_page_lens = view("kv_last_page_lens", lay.batch)
+        self.qo_indptr = view("qo_indptr", lay.batch + 1)
+        self._runs = view("flattened_masks", lay.num_runs)
+        self._run_indptr = view("mask_indptr", int(fields["mask_indptr"].size))
+        # O(requests) on the host: how many (query, key) pairs the mask has (sizes the packed mask)
+        counts = np.diff(fields["qo_indptr"].astype(np.int64))
+        npages = np.diff(fields["kv_page_indptr"].astype(np.int64))
+        last = fields["kv_last_page_lens"].astype(np.int64)
+        self.mask_bits = int(np.sum(counts * np.where(npages > 0, (npages - 1) * kv_page_size + last, last)))
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.token_ids = torch.empty(lay.nnz, dtype=torch.int64, device=dev)
+        self.seq_lens = torch.empty(lay.batch, **i32)
+        self.batch_indices = torch.empty(lay.nnz, **i32)
+        self.positions = torch.empty(lay.nnz, **i32)
+        self.token_acc_seq_lens = torch.empty(lay.nnz + 1, dtype=torch.int64, device=dev) if acc_seq_lens else None
+        _lib.check(_lib.lib.piekv_batch_from_wire(
+            self.wire.data_ptr(), C.byref(lay), self.page_size, self.token_ids.data_ptr(), self.seq_lens.data_ptr(),
+            self.batch_indices.data_ptr(), self.positions.data_ptr(),
+            self.token_acc_seq_lens.data_ptr() if acc_seq_lens else None, ops._stream(dev)), "batch_from_wire")
+
+    def brle_inputs(self):
+        """(run lengths, per-token offsets, mask entries) as views of the uploaded buffer, for
+        `BatchPrefillWithPagedKVCacheWrapper.plan(brle_mask=...)`."""
+        return self._runs, self._run_indptr, self.mask_bits
+
+    def get_model_inputs(self) -> Dict[str, Any]:
+        """The reference's `get_model_inputs` dictionary (pie/src/pie_worker/batching.py:196-239) with the mask in
+        its wire form under `brle_mask` instead of the expanded `custom_mask`."""
+        return {
+            "token_ids": self.token_ids, "position_ids": self.position_ids, "qo_indptr": self.qo_indptr,
+            "kv_page_indices": self.kv_page_indices, "kv_page_indptr": self.kv_page_indptr,
+            "kv_last_page_lens": self.kv_last_page_lens, "brle_mask": self.brle_inputs(),
+            "single_token_inference_mode": self.single_token_mode, "total_pages_cpu": self.total_pages_cpu,
+        }

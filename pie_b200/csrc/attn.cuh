@@ -60,6 +60,9 @@ int64_t prefill_tc_workspace_bytes(int batch, int nnz, int num_pages, int64_t ma
 // (mask_bytes must then still name sum qo_len * kv_len, which sizes the packed mask)
 int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
                         cudaStream_t st, const uint32_t *brle_runs = nullptr, const int32_t *brle_indptr = nullptr);
+// the planned packed mask written out as one byte per (query, key) pair (the reference's flat layout)
+int launch_prefill_export_mask(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                               uint8_t *flat, cudaStream_t st);
 int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
                       cudaStream_t st);
 

@@ -301,6 +301,33 @@ __global__ void prefill_window_mask_kernel(const int32_t *__restrict__ qo_indptr
   }
 }
 
+// The packed mask of a planned batch written back in the reference's flat form (one byte per
+// (query, key) pair, rows of kv_len entries, requests end to end; pie/src/pie_worker/batching.py:113-135).
+// One warp per query row.
+__global__ void prefill_unpack_mask_kernel(const int32_t *__restrict__ qo_indptr, const int32_t *__restrict__ kv_indptr,
+                                           const int32_t *__restrict__ last, int batch, int nnz, int page_size,
+                                           const long long *__restrict__ poff, const long long *__restrict__ moff,
+                                           const uint4 *__restrict__ packed, uint8_t *flat) {
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (i >= nnz) return;
+  int lo = 0, hi = batch;
+  while (lo < hi) {
+    int mid = (lo + hi) >> 1;
+    if (qo_indptr[mid + 1] > i)
+      hi = mid;
+    else
+      lo = mid + 1;
+  }
+  const int b = lo < batch ? lo : batch - 1;
+  const int j = i - qo_indptr[b];
+  const int kv = kv_len_of(kv_indptr, last, b, page_size);
+  const int groups = (kv + 127) / 128;
+  const uint32_t *src = reinterpret_cast<const uint32_t *>(packed + poff[b] + (long long)j * groups);
+  uint8_t *dst = flat + moff[b] + (long long)j * kv;
+  for (int t = lane; t < kv; t += 32) dst[t] = (uint8_t)((src[t >> 5] >> (t & 31)) & 1u);
+}
+
 // ------------------------------------------------------------------------------------------------
 // work list: one entry per (request, 128-row tile), ordered by decreasing number of kv tiles
 // ------------------------------------------------------------------------------------------------
@@ -819,6 +846,18 @@ int launch_prefill_plan(const AttnArgs &a, int64_t mask_bytes, void *workspace, 
   prefill_plan_kernel<<<1, 1024, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch, a.page_size, a.causal,
                                           v.tile_base, v.summary, v.sw, masked ? 1 : 0, v.tiles, v.ntiles, v.max_tiles);
   PIEKV_LAUNCH_CHECK("prefill_plan_kernel");
+  return 0;
+}
+
+int launch_prefill_export_mask(const AttnArgs &a, int64_t mask_bytes, void *workspace, int64_t workspace_bytes,
+                               uint8_t *flat, cudaStream_t st) {
+  if (a.nnz == 0 || a.batch == 0 || mask_bytes == 0) return 0;
+  const PlanView v = plan_view(workspace, a.batch, a.nnz, a.num_pages, mask_bytes);
+  PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= v.bytes, "prefill: workspace too small (%lld < %lld bytes)",
+                (long long)workspace_bytes, (long long)v.bytes);
+  prefill_unpack_mask_kernel<<<(a.nnz + 7) / 8, 256, 0, st>>>(a.qo_indptr, a.kv_indptr, a.kv_last_page_len, a.batch,
+                                                               a.nnz, a.page_size, v.poff, v.moff, v.packed, flat);
+  PIEKV_LAUNCH_CHECK("prefill_unpack_mask_kernel");
   return 0;
 }
 

@@ -6,9 +6,12 @@ batch-size bin is captured over static buffers; a step copies its metadata into 
 the batch up to the bin with rows that own one scratch page holding one token, replays the graph and
 returns a copy of the real rows.  Batches larger than the largest bin fall back to an eager plan + run.
 
-What is captured here is the single fused launch of this library (RoPE + append + attention,
-`BatchDecodeWithPagedKVCacheWrapper.run_fused`) instead of the reference's layer loop; the wrapper
-reads the page tables on the device at run time, so replaying with new table contents needs no re-plan.
+What is captured per layer is the single fused launch of this library (RoPE + append + attention,
+`BatchDecodeWithPagedKVCacheWrapper.run_fused`); the wrapper reads the page tables on the device at run
+time, so replaying with new table contents needs no re-plan.  With several layer pools the graph holds the
+whole layer loop over ONE set of step metadata, as the reference's does (llama3.py:915-956): either the
+default loop (layer l reads q/k/v[l] and writes out[l]) or a caller's `body`, which may put its own work
+(projections, norms) between the `attend` calls so that one replay is one whole decode step.
 
 Two deliberate differences from the reference's replay code: the padded rows' page ids are written
 every step (the reference leaves whatever the shared index buffer held beyond the real pages), and
@@ -44,11 +47,22 @@ def pick_bin(bins: List[int], batch: int) -> Optional[int]:
 
 
 class GraphedDecodeStep:
-    """One captured fused decode launch per bin over shared static buffers."""
+    """One captured decode step per bin over shared static buffers: a fused launch per layer.
 
-    def __init__(self, pool: torch.Tensor, num_qo_heads: int, num_kv_heads: int, max_batch: int,
+    `pool` is one layer's pool or a list of them (all of one shape).  `body(runner, b)`, if given, is what
+    gets captured for bin `b` instead of the default layer loop; it calls `runner.attend(layer, q, k, v)` once
+    per layer on tensors of `b` rows that live in static memory of its own."""
+
+    def __init__(self, pool, num_qo_heads: int, num_kv_heads: int, max_batch: int,
                  max_total_pages: int, rope: Optional[ops.RopeConfig] = None,
-                 workspace: Optional[torch.Tensor] = None) -> None:
+                 workspace: Optional[torch.Tensor] = None, body=None) -> None:
+        self.pools = list(pool) if isinstance(pool, (list, tuple)) else [pool]
+        self._single = not isinstance(pool, (list, tuple))
+        self.body = body
+        shapes = {tuple(p.shape) for p in self.pools}
+        if len(shapes) != 1 or len({p.dtype for p in self.pools}) != 1:
+            raise ValueError("layer pools differ in shape or dtype")
+        pool = self.pools[0]
         num_pages, page_size, hkv, d = ops._check_pool(pool)
         if hkv != num_kv_heads:
             raise ValueError("pool kv heads differ from num_kv_heads")
@@ -59,10 +73,12 @@ class GraphedDecodeStep:
         self.bins = graph_bins(max_batch)
         self.max_bin = self.bins[-1]
         dev, dt = pool.device, pool.dtype
-        self.q = torch.zeros((self.max_bin, self.hq, d), dtype=dt, device=dev)
-        self.k = torch.zeros((self.max_bin, self.hkv, d), dtype=dt, device=dev)
-        self.v = torch.zeros((self.max_bin, self.hkv, d), dtype=dt, device=dev)
-        self.out = torch.zeros((self.max_bin, self.hq, d), dtype=dt, device=dev)
+        L = len(self.pools)
+        self.num_layers = L
+        self.q = torch.zeros((L, self.max_bin, self.hq, d), dtype=dt, device=dev)
+        self.k = torch.zeros((L, self.max_bin, self.hkv, d), dtype=dt, device=dev)
+        self.v = torch.zeros((L, self.max_bin, self.hkv, d), dtype=dt, device=dev)
+        self.out = torch.zeros((L, self.max_bin, self.hq, d), dtype=dt, device=dev)
         self.pos = torch.zeros(self.max_bin, dtype=torch.int32, device=dev)
         self.indices = torch.full((int(max_total_pages) + self.max_bin,), self.scratch_page, dtype=torch.int32,
                                   device=dev)
@@ -76,9 +92,20 @@ class GraphedDecodeStep:
         self.graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._pad_ramp = torch.arange(1, self.max_bin + 1, dtype=torch.int32, device=dev)
 
+    def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The fused RoPE + append + attention launch of `layer` on the current step metadata (for `body`).
+        `q` decides the bin: it must have as many rows as the bin being captured."""
+        b = q.shape[0]
+        return self.wrappers[b].run_fused(q, k, v, self.pos[:b], self.pools[layer], self.rope,
+                                          out=out if out is not None else self.out[layer, :b])
+
     def _launch(self, b: int) -> None:
-        self.wrappers[b].run_fused(self.q[:b], self.k[:b], self.v[:b], self.pos[:b], self.pool, self.rope,
-                                   out=self.out[:b])
+        if self.body is not None:
+            self.body(self, b)
+            return
+        for l in range(self.num_layers):
+            self.attend(l, self.q[l, :b], self.k[l, :b], self.v[l, :b], out=self.out[l, :b])
 
     def capture(self) -> None:
         """Capture every bin (the reference's warm-up, llama3.py:315-414)."""
@@ -98,23 +125,34 @@ class GraphedDecodeStep:
             self.graphs[b] = g
         torch.cuda.synchronize(self.pool.device)
 
-    def run(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, position_ids: torch.Tensor,
-            kv_page_indices: torch.Tensor, kv_page_indptr: torch.Tensor, kv_last_page_lens: torch.Tensor,
-            total_pages_cpu: int) -> torch.Tensor:
-        """One decode step (the page lists already hold the new token's slot).  Returns [batch, Hq, D]."""
-        batch = q.shape[0]
+    def run(self, q: Optional[torch.Tensor], k: Optional[torch.Tensor], v: Optional[torch.Tensor],
+            position_ids: torch.Tensor, kv_page_indices: torch.Tensor, kv_page_indptr: torch.Tensor,
+            kv_last_page_lens: torch.Tensor, total_pages_cpu: int) -> torch.Tensor:
+        """One decode step (the page lists already hold the new token's slot).  q / k / v are [batch, H, D]
+        for a single pool, [layers, batch, H, D] for a list of pools, or None with a `body` (which owns its
+        inputs).  Returns [batch, Hq, D] or [layers, batch, Hq, D]."""
+        batch = kv_page_indptr.shape[0] - 1
+        if q is not None and self._single:
+            q, k, v = q[None], k[None], v[None]
+        if q is not None and (q.shape[0] != self.num_layers or q.shape[1] != batch):
+            raise ValueError(f"q must be [{self.num_layers}, {batch}, heads, head_dim]")
         b = pick_bin(self.bins, batch)
         if b is None or b not in self.graphs:
+            if q is None:
+                raise ValueError("a batch beyond the largest bin needs q / k / v (the body is only captured)")
             self.fallback.plan(kv_page_indptr, kv_page_indices, kv_last_page_lens, self.hq, self.hkv, self.d,
                                self.page_size, pos_encoding_mode="NONE", q_data_type=q.dtype)
-            return self.fallback.run_fused(q, k, v, position_ids, self.pool, self.rope)
+            outs = [self.fallback.run_fused(q[l], k[l], v[l], position_ids, self.pools[l], self.rope)
+                    for l in range(self.num_layers)]
+            return outs[0] if self._single else torch.stack(outs)
         total = int(total_pages_cpu)
         if total + (b - batch) > self.indices.numel():
             raise ValueError("more pages than the static index buffer holds")
         indptr, last = self.aux[b]
-        self.q[:batch].copy_(q)
-        self.k[:batch].copy_(k)
-        self.v[:batch].copy_(v)
+        if q is not None:
+            self.q[:, :batch].copy_(q)
+            self.k[:, :batch].copy_(k)
+            self.v[:, :batch].copy_(v)
         self.pos[:batch].copy_(position_ids[:batch])
         indptr[: batch + 1].copy_(kv_page_indptr)
         last[:batch].copy_(kv_last_page_lens)
@@ -126,4 +164,5 @@ class GraphedDecodeStep:
             last[batch:].fill_(1)
             self.pos[batch:b].zero_()
         self.graphs[b].replay()
-        return self.out[:batch].clone()
+        res = self.out[:, :batch].clone()
+        return res[0] if self._single else res

@@ -782,6 +782,24 @@ class BatchPrefillWithPagedKVCacheWrapper:
 
     forward = run
 
+    def export_custom_mask(self, num_query_tokens: int, num_pages: int) -> torch.Tensor:
+        """The mask this plan holds on the device (from bytes, run lengths and / or a window) in the reference's
+        flat boolean form (pie/src/pie_worker/batching.py:113-135): for checking a device-built mask against
+        the reference's, or for a consumer that still wants that tensor."""
+        if self._plan is None:
+            raise RuntimeError("Must call plan() before run()")
+        pl = self._plan
+        if pl["page_size"] != 16:
+            raise ValueError("the packed mask exists for page size 16 only")
+        self._device_plan(int(num_query_tokens), int(num_pages))
+        flat = torch.zeros(pl["mask_bytes"], dtype=torch.uint8, device=pl["qo_indptr"].device)
+        ws = self.workspace_buffer
+        check(lib.piekv_prefill_export_mask(pl["qo_indptr"].data_ptr(), pl["indptr"].data_ptr(),
+                                            pl["last_page_len"].data_ptr(), pl["mask_bytes"], pl["batch"],
+                                            int(num_query_tokens), 16, int(num_pages), ws.data_ptr(), ws.numel(),
+                                            flat.data_ptr(), _stream(flat.device)), "BatchPrefill.export_custom_mask")
+        return flat.view(torch.bool)
+
 
 class BatchAttentionWithAttentionSinkWrapper(BatchPrefillWithPagedKVCacheWrapper):
     """Paged attention with per-head attention sinks and an optional sliding window fixed at construction.
