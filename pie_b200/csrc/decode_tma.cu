@@ -70,6 +70,20 @@ struct FusedArgs {
 
 constexpr int kSmemBatch = 1024;  // kv_indptr is staged in shared memory up to this batch size
 
+// Optional per-CTA time stamps (builds with -DPIEKV_TRACE only): kernel entry, first page consumed, last
+// page consumed, exit; read back with piekv_trace_read.
+#ifdef PIEKV_TRACE
+__device__ unsigned long long g_trace[256 * 4];
+#define PIEKV_STAMP(slot)                                                               \
+  do {                                                                                  \
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) g_trace[blockIdx.x * 4 + (slot)] = global_timer_ns(); \
+  } while (0)
+#else
+#define PIEKV_STAMP(slot) \
+  do {                    \
+  } while (0)
+#endif
+
 __device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap *tmap, int coord4, uint64_t *bar) {
   asm volatile(
       "cp.async.bulk.tensor.5d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
@@ -174,6 +188,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const AttnArgs &a = p.a;
   const int B = a.batch;
   const int c = blockIdx.x;
+  PIEKV_STAMP(0);
   // Programmatic dependent launch: let the next kernel of the stream start its own prologue as SMs
   // free up, and do not touch anything an earlier kernel may still be producing before the wait.
   // Mode 2 is for callers whose page-table arrays are not written by the kernel just before this one
@@ -435,6 +450,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) atomicExch(&sh_abort, 1);
         aborted = true;
       }
+      if (it == 0) PIEKV_STAMP(1);
       if (!aborted && pslot < npg) {
         const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
         const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
@@ -597,6 +613,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ================= close the segment: publish the result or the partial
+    if (g >= hi) PIEKV_STAMP(2);
     const int c_first = cta_of_page(req_begin, total_pages, G);
     const int c_last = cta_of_page(req_end - 1, total_pages, G);
     const int nseg = c_last - c_first + 1;
@@ -729,6 +746,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!arrive_last(&p.counters[b], n_groups)) continue;
     merge_parts((size_t)(c_first + b) * PG, (size_t)kMergeGroup * PG, n_groups, false);
   }
+  PIEKV_STAMP(3);
   finish();
 }
 
@@ -909,6 +927,12 @@ int static_scratch_ptr(void **out) {
 }
 }  // namespace
 }  // namespace piekv
+
+#ifdef PIEKV_TRACE
+extern "C" int piekv_trace_read(unsigned long long *host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, piekv::g_trace, sizeof(unsigned long long) * 256 * 4);
+}
+#endif
 
 extern "C" int64_t piekv_decode_noalloc_max_bytes(void) { return piekv::kStaticScratchBytes; }
 
