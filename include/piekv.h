@@ -92,6 +92,11 @@ const char *piekv_last_error_string(void);
  *     pie/src/pie_worker/batching.py:196-239): the offsets are read before the wait.
  * No reference counterpart. */
 #define PIEKV_OPT_PDL 0
+/* PIEKV_OPT_DETERMINISTIC: 0 (default) - the tuned decode kernel lets SMs that finish early take over
+ * page ranges of slower ones, so how a request's pages are grouped before the partial results are merged
+ * (and with it the last bits of the output) can differ from launch to launch; 1 - every SM keeps to its
+ * own range and equal inputs give bit-identical outputs, at some cost in speed.  No reference counterpart. */
+#define PIEKV_OPT_DETERMINISTIC 1
 int piekv_set_option(int32_t key, int32_t value);
 
 /* ---- metadata (device-resident) ------------------------------------------------- */
@@ -143,9 +148,10 @@ int piekv_rope_append(void *q, void *k, const void *v, int64_t q_stride_n, int64
 
 /* ---- attention ------------------------------------------------------------------- */
 
-/* Bytes of scratch piekv_decode_run needs for `batch` requests (split-KV partials and
- * per-request arrival counters).  The first `piekv_decode_counter_bytes(batch)` bytes hold
- * the counters and must be zero before the first run; runs leave them zero.
+/* Bytes of scratch piekv_decode_run needs at least for `batch` requests (split-KV partials and the
+ * counters and tables of its work partition); given more (up to about three times as much) the kernel
+ * rebalances more freely between SMs.  The first `piekv_decode_counter_bytes(batch)` bytes hold the
+ * counters and tables and must be zero before the first run; runs leave them zero.
  * Reference: the 128 MiB workspace handed to the wrappers (llama3.py:230-232). */
 int64_t piekv_decode_workspace_bytes(int32_t batch, int32_t num_qo_heads, int32_t num_kv_heads,
                                      int32_t head_dim);
@@ -171,8 +177,8 @@ int piekv_decode_run(const void *q, int64_t q_stride_n, int64_t q_stride_h, cons
  * piekv_decode_noalloc_max_bytes() (8 MiB) array inside the library, held by every GPU that loads
  * the library until the process exits.  Calls whose batch / head count need more are rejected with
  * a >0 status and a message; nothing is launched.  The call never allocates (no cudaMalloc /
- * cudaFree, no allocating library routine); it issues one small cudaMemsetAsync of the arrival
- * counters and the kernel.  The first call on each device looks the array's device address up
+ * cudaFree, no allocating library routine); it issues one small cudaMemsetAsync (the counters and
+ * tables at the head of the array) and the kernel.  The first call on each device looks the array's device address up
  * (cudaGetSymbolAddress) and should therefore happen before any stream capture.  All calls on a
  * device share the one array: calls that may overlap on the GPU (different streams) race. */
 int64_t piekv_decode_noalloc_max_bytes(void);

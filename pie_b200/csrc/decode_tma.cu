@@ -1,19 +1,29 @@
 // Paged decode attention for 16-bit K/V, head_dim 128, page_size 16 on sm_100a.
 //
-// Work partition (on the device, no host plan): the flat list of all requests' pages
-// (kv_indices[0 .. kv_indptr[B])) is cut into gridDim.x equal contiguous ranges, one per
-// CTA (one CTA per SM).  A CTA therefore streams the same number of pages whatever the
-// mix of context lengths; where a range crosses a request boundary the CTA closes one
-// "segment" and opens the next.  A request cut across CTAs is finished by whichever CTA
-// delivers its last segment (per-request arrival counter), which merges the partial
-// (max, sum, accumulator) triples from scratch memory.
+// Work partition (on the device, no host plan).  The flat list of all requests' pages
+// (kv_indices[0 .. kv_indptr[B])) is cut into small equal CHUNKS (a few pages each, at most kMaxChunks of
+// them).  Every CTA (one per SM) owns a contiguous run of chunks and walks it front to back; a CTA that
+// runs out takes chunks from the BACK of the CTA with the most work left.  HBM bandwidth is not the same
+// for every SM of the two-die part (some finish an equal share 20 % later than others), so an equal
+// static split would let the slowest SM decide the launch time; with stealing all SMs stop streaming
+// within one chunk of each other.
+//
+// A CTA accumulates a request's pages in registers for as long as the chunks it takes are consecutive:
+// such a RUN of chunk pieces ends at a request boundary, at the end of the CTA's chunks, or (long
+// requests) at a group boundary.  A run that holds a whole request is normalised and stored directly;
+// otherwise the run's (max, sum, accumulator) triple goes to a scratch slot taken from a counter, the
+// slot number is entered in a table at the run's first chunk, and the run adds its number of pieces to
+// the request's arrival counter.  Whoever completes the count merges the request's runs.  A request
+// spread over many chunks is merged in two levels (groups of chunk pieces fold concurrently on different
+// SMs, the last group folds the groups).  Counters and tables are left zero by the CTAs that consume them.
 //
 // Data path: a producer warp gathers pages with TMA.  A page holds K [16, Hkv, 128] then
 // V [16, Hkv, 128]; one 5-D tensor-map box {64 d, 16 tokens, 2 d-halves, Hkv heads, K|V}
 // moves the whole page (Hkv * 8 KiB) and lands it in shared memory regrouped per head as
 // 128-byte-swizzled [token][64 d] tiles, which is the layout ldmatrix wants.  A stage is
 // always 64 KiB = 8 (page, head) tiles: 8/Hkv pages for Hkv heads.  Three stages keep
-// 128-192 KiB per SM in flight.
+// 128-192 KiB per SM in flight.  The producer decides everything about the schedule and describes each
+// stage to the consumers in a small shared-memory record (pages, request, run start / end).
 //
 // Math: consumer warp w owns tile (page w / Hkv, head w % Hkv).  The GQA group's query
 // heads (<= 16) are the M rows of m16n8k16 tensor-core MMAs: S = Q K^T (16 x 16 tokens),
@@ -32,21 +42,41 @@ namespace {
 constexpr int kDim = 128;
 constexpr int kPage = 16;
 constexpr int kConsumerWarps = 8;
+constexpr int kConsumers = kConsumerWarps * 32;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kStages = 3;
 constexpr int kTileBytes = 8192;               // one (page, head): K 4 KiB + V 4 KiB
 constexpr int kStageBytes = 8 * kTileBytes;    // 64 KiB
-constexpr int kCounterBytes = 65536;           // head of the workspace: arrival counters
-constexpr int kMergeGroup = 16;                // partials folded by one CTA at a time
-constexpr int kGroupCounters = 256;            // group counters, indexed by the group's first CTA (grid <= 256)
-constexpr int kMaxBatch = kCounterBytes / 4 - kGroupCounters - 1;  // request counters; then the group counters; then one word
-constexpr int kGroupCounter0 = kMaxBatch;
+constexpr int kMaxGrid = 256;                  // CTAs (SMs) the steal table holds
+
+// The first 64 KiB of the workspace: everything that must be zero when a launch starts and is zero again
+// when it ends (other users of the same workspace leave this block alone).
+//   req_cnt  [kMaxBatch]            arrival counters of the requests (chunk pieces, or groups)
+//   ctl      [16]                   0: scratch slots handed out  1: CTAs finished  2: peer completion
+//   steal    [kMaxGrid] x 64 bit    (hi << 32) | lo of every CTA's remaining chunk range
+//   grp_cnt  [kTable]               arrival counters of the groups of long requests
+//   run_tab  [kTable] x 16 bit      slot + 1 of the run that starts at (chunk + request)
+//   grp_tab  [kTable] x 16 bit      slot + 1 of a folded group, at (first chunk of the group + request)
+constexpr int kCounterBytes = 65536;
+constexpr int kMaxBatch = 2048;
+constexpr int kMaxChunks = 4096;
+constexpr int kTable = kMaxChunks + kMaxBatch;
+constexpr int kCtlWord0 = kMaxBatch;
+constexpr int kStealByte0 = (kMaxBatch + 16) * 4;
+constexpr int kGrpCntByte0 = kStealByte0 + kMaxGrid * 8;
+constexpr int kRunTabByte0 = kGrpCntByte0 + kTable * 4;
+constexpr int kGrpTabByte0 = kRunTabByte0 + kTable * 2;
+static_assert(kGrpTabByte0 + kTable * 2 <= kCounterBytes, "zero-state block of the decode kernel");
+constexpr int kMaxSlots = 65534;               // slot + 1 must fit the 16-bit tables
+constexpr int kMergeList = 1024;               // runs (or groups) one merge can fold
 
 struct DecodeParams {
   AttnArgs a;
   float *part_o;    // [slot][PG][Hq][128]
   float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
-  int *counters;    // [batch], zero between launches
+  int *counters;    // the zero-state block
+  int num_slots;    // scratch slots part_o / part_ml hold
+  int steal;        // 0: every CTA keeps to its own chunks (results reproducible bit for bit)
   int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets
   PeerOut peer;     // n == 0: results go to a.out only
   // Sliding window (a.window_left >= 0): the kernel streams only the pages that hold keys inside each
@@ -92,12 +122,7 @@ __device__ __forceinline__ void tma_load_page(uint32_t dst, const CUtensorMap *t
       : "memory");
 }
 
-__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32)); }
-
-// CTA that owns flat page g when T pages are cut into G ranges [c*T/G, (c+1)*T/G).
-__device__ __forceinline__ int cta_of_page(long long g, long long T, long long G) {
-  return (int)(((g + 1) * G - 1) / T);
-}
+__device__ __forceinline__ void consumer_bar_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kConsumers)); }
 
 // last request whose first page index is <= g, skipping empty requests after it
 __device__ __forceinline__ int request_of_page(const int32_t *indptr, int batch, int g) {
@@ -168,6 +193,141 @@ __global__ void __launch_bounds__(1024) decode_window_kernel(const int32_t *__re
   if (threadIdx.x == 0) win_indptr[batch] = carry;
 }
 
+// What the producer tells the consumers about a stage (written before the stage's barrier is armed).
+struct StageDesc {
+  int g;            // flat index of the stage's first page; -1: no more work
+  int b;            // request
+  int npg;          // pages in the stage
+  int flags;        // kRunStart | kRunEnd
+  int first_chunk;  // chunk the run started in (meaningful with kRunEnd)
+  int pieces;       // chunk pieces of the request the run covered (meaningful with kRunEnd)
+  int page[8];      // physical ids of the stage's pages
+};
+constexpr int kRunStart = 1, kRunEnd = 2;
+
+// 64-bit steal word: (hi << 32) | lo, chunks [lo, hi) are still untaken.  The owner takes from the front
+// (add 1), others from the back (subtract k << 32); the word only ever shrinks the range, so whoever's
+// atomic comes first gets the chunk.
+__device__ __forceinline__ unsigned long long steal_pack(int lo, int hi) {
+  return ((unsigned long long)(unsigned int)hi << 32) | (unsigned int)lo;
+}
+__device__ __forceinline__ int steal_lo(unsigned long long w) { return (int)(unsigned int)(w & 0xffffffffull); }
+__device__ __forceinline__ int steal_hi(unsigned long long w) { return (int)(unsigned int)(w >> 32); }
+
+// The non-zero entries of tab[first .. first + count) in index order -> list (slot numbers); the entries
+// are zeroed on the way.  All consumer threads; returns how many (at most kMergeList).
+__device__ __noinline__ int collect_slots(unsigned short *tab, int first, int count, unsigned short *list,
+                                          int *nlist, int *wsum) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) *nlist = 0;
+  consumer_bar_sync();
+  for (int base = 0; base < count; base += kConsumers) {
+    const int i = base + tid;
+    unsigned short v = 0;
+    if (i < count) {
+      v = __ldcg(tab + first + i);
+      if (v != 0) tab[first + i] = 0;
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, v != 0);
+    if (lane == 0) wsum[warp] = __popc(m);
+    consumer_bar_sync();
+    int off = *nlist;
+    for (int w = 0; w < warp; ++w) off += wsum[w];
+    off += __popc(m & ((1u << lane) - 1u));
+    if (v != 0 && off < kMergeList) list[off] = (unsigned short)(v - 1);
+    consumer_bar_sync();
+    if (tid == 0) {
+      int t = *nlist;
+      for (int w = 0; w < kConsumerWarps; ++w) t += wsum[w];
+      *nlist = t;
+    }
+    consumer_bar_sync();
+  }
+  return min(*nlist, kMergeList);
+}
+
+// Fold the partials of the slots in list[0 .. n) (`subs` sub-slots each): thread -> (query head
+// tid/32 + 8k, 4 consecutive d).  Four heads at a time, two passes whose loads are independent of one
+// another and stay in flight together: first every head's maximum, then the weighted sums.  The result is
+// the request's output row (normalised) or again a partial (maximum, sum, unnormalised accumulator)
+// written to sub-slot 0 of `to_slot`.
+template <typename T, int PG>
+__device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned short *list, int n, int subs, int b,
+                                         int to_slot, int peer_step) {
+  const AttnArgs &a = p.a;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int d4 = lane * 4;
+  const int np = n * subs;
+  const int n_dst = p.peer.n > 0 ? p.peer.n : 1;
+  const int row_heads = p.peer.n > 0 ? p.peer.row_heads : a.hq;
+  const int head_off = p.peer.n > 0 ? p.peer.head_off : 0;
+  const bool use_alt = p.peer.n > 0 && p.peer.step_ptr != nullptr && (peer_step & 1) == 0;
+  for (int q0 = warp; q0 < a.hq; q0 += 4 * kConsumerWarps) {
+    float M[4], L[4];
+    float4 acc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      M[u] = -INFINITY;
+      L[u] = 0.f;
+      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int pp = 0; pp < np; ++pp) {
+      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int qh = q0 + u * kConsumerWarps;
+        if (qh < a.hq) {
+          const float2 ml = __ldcg(p.part_ml + base + qh);
+          M[u] = ml.y > 0.f ? fmaxf(M[u], ml.x) : M[u];
+        }
+      }
+    }
+#pragma unroll 2
+    for (int pp = 0; pp < np; ++pp) {
+      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int qh = q0 + u * kConsumerWarps;
+        if (qh < a.hq) {
+          const float2 ml = __ldcg(p.part_ml + base + qh);
+          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
+          const float w = ml.y > 0.f ? fast_exp2(ml.x - M[u]) : 0.f;  // a warp that saw no page: weight 0
+          L[u] = fmaf(ml.y, w, L[u]);
+          acc[u].x = fmaf(po.x, w, acc[u].x);
+          acc[u].y = fmaf(po.y, w, acc[u].y);
+          acc[u].z = fmaf(po.z, w, acc[u].z);
+          acc[u].w = fmaf(po.w, w, acc[u].w);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int qh = q0 + u * kConsumerWarps;
+      if (qh >= a.hq) continue;
+      if (to_slot >= 0) {
+        __syncwarp();  // every lane has read this head's partials before one of them is overwritten
+        const size_t idx = (size_t)to_slot * PG * a.hq + qh;
+        *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc[u];
+        if (lane == 0) p.part_ml[idx] = make_float2(M[u], L[u]);
+        continue;
+      }
+      const float Ls = add_sink(L[u], M[u], a.sinks, qh);
+      const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+      uint2 pk;
+      pk.x = pack2<T>(acc[u].x * inv, acc[u].y * inv);
+      pk.y = pack2<T>(acc[u].z * inv, acc[u].w * inv);
+      for (int d = 0; d < n_dst; ++d) {
+        void *pb = a.out;
+        if (p.peer.n > 0) pb = use_alt ? p.peer.dst_alt[d] : p.peer.dst[d];
+        T *row = reinterpret_cast<T *>(pb) + ((size_t)b * row_heads + head_off + qh) * kDim;
+        *reinterpret_cast<uint2 *>(row + d4) = pk;
+      }
+      if (a.lse != nullptr && lane == 0)
+        a.lse[(size_t)b * a.hq + qh] = Ls > 0.f ? (M[u] + log2f(Ls)) * 0.6931471805599453f : -INFINITY;
+    }
+  }
+}
+
 template <typename T, int HKV, bool FUSED>
 __global__ void __launch_bounds__(kThreads, 1)
     decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ DecodeParams p,
@@ -176,8 +336,13 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ StageDesc sh_desc[kStages];
   __shared__ int sh_abort;
   __shared__ int sh_last;
+  __shared__ int sh_slot;
+  __shared__ int sh_nlist;
+  __shared__ int sh_wsum[kConsumerWarps];
+  __shared__ unsigned short sh_list[kMergeList];
   __shared__ int32_t sh_indptr[kSmemBatch + 1];
 
   const int warp = threadIdx.x >> 5;
@@ -188,6 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const AttnArgs &a = p.a;
   const int B = a.batch;
   const int c = blockIdx.x;
+  const int G = gridDim.x;
   PIEKV_STAMP(0);
   // Programmatic dependent launch: let the next kernel of the stream start its own prologue as SMs
   // free up, and do not touch anything an earlier kernel may still be producing before the wait.
@@ -215,59 +381,195 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   __syncthreads();
   if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- chunk geometry, the same on every CTA
   const int total_pages = ip[B];
-  // With fewer pages than CTAs only the first `total_pages` CTAs take part, so that every
-  // participating range is non-empty (the segment count of a request relies on that).
-  const int G = min((int)gridDim.x, max(total_pages, 1));
-  const int lo = c < G ? (int)((long long)c * total_pages / G) : 0;
-  const int hi = c < G ? (int)((long long)(c + 1) * total_pages / G) : 0;
+  const int stages_total = (total_pages + PG - 1) / PG;
+  const int cp = PG * max(1, (stages_total + kMaxChunks - 1) / kMaxChunks);  // pages per chunk
+  const int n_chunks = (total_pages + cp - 1) / cp;
+  const int my_lo = (int)((long long)c * n_chunks / G);
+  const int my_hi = (int)((long long)(c + 1) * n_chunks / G);
+  // chunk pieces per merge group of a long request: about what 16 CTAs own
+  const int gsz = 16 * max(1, n_chunks / G);
   const int group = a.hq / HKV;
+
+  int *req_cnt = p.counters;
+  int *ctl = p.counters + kCtlWord0;
+  unsigned long long *steal_tab =
+      reinterpret_cast<unsigned long long *>(reinterpret_cast<uint8_t *>(p.counters) + kStealByte0);
+  int *grp_cnt = reinterpret_cast<int *>(reinterpret_cast<uint8_t *>(p.counters) + kGrpCntByte0);
+  unsigned short *run_tab = reinterpret_cast<unsigned short *>(reinterpret_cast<uint8_t *>(p.counters) + kRunTabByte0);
+  unsigned short *grp_tab = reinterpret_cast<unsigned short *>(reinterpret_cast<uint8_t *>(p.counters) + kGrpTabByte0);
 
   if (warp == kConsumerWarps) {
     // ------------------------------------------------------------------ producer
     int armed = 0;  // stages armed so far
-    if (lo < hi) {
-      int b = request_of_page(ip, B, lo);
-      int g = lo;
-      bool stop = false;
-      while (g < hi && !stop) {
-        while (b < B - 1 && ip[b + 1] <= g) ++b;
-        const int seg_end = min(hi, ip[b + 1]);
-        if (seg_end <= g) {  // non-monotone indptr: give up cleanly
-          if (lane == 0) report_error(a.err, PIEKV_ERR_INDPTR, KID_DECODE, b, g);
-          if (lane == 0) atomicExch(&sh_abort, 1);
-          break;
-        }
-        const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
-        while (g < seg_end) {
-          const int npg = min(PG, seg_end - g);
-          // page ids first, so the load is in flight while we wait for the stage
-          int page = lane < npg ? __ldg(a.kv_indices + g + shift + lane) : 0;
-          const int s = armed % kStages;
-          const uint32_t ph = (armed / kStages) & 1;
-          if (*(volatile int *)&sh_abort) {
-            stop = true;
-            break;
-          }
-          if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
-            if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 100 + s);
-            if (lane == 0) atomicExch(&sh_abort, 1);
-            stop = true;
-            break;
-          }
-          if (lane < npg && (page < 0 || page >= a.num_pages)) {
-            report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
-            page = a.num_pages;  // outside the tensor map: the box is zero-filled
-          }
-          if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(npg * HKV * kTileBytes));
-          __syncwarp();
-          if (lane < npg) {
-            tma_load_page(stage0 + s * kStageBytes + lane * (HKV * kTileBytes), &tmap, page * 2, &full_bar[s]);
-          }
-          g += npg;
-          ++armed;
+    bool ok = true;
+    // publish one stage: wait for the slot, describe it, arm the barrier, issue the page loads
+    auto publish = [&](const StageDesc &d, int page_of_lane) -> bool {
+      const int s = armed % kStages;
+      const uint32_t ph = (armed / kStages) & 1;
+      if (*(volatile int *)&sh_abort) return false;
+      if (!mbar_wait(&empty_bar[s], ph ^ 1)) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 100 + s);
+        if (lane == 0) atomicExch(&sh_abort, 1);
+        return false;
+      }
+      if (lane == 0) {
+        sh_desc[s].g = d.g;
+        sh_desc[s].b = d.b;
+        sh_desc[s].npg = d.npg;
+        sh_desc[s].flags = d.flags;
+        sh_desc[s].first_chunk = d.first_chunk;
+        sh_desc[s].pieces = d.pieces;
+      }
+      if (lane < d.npg) sh_desc[s].page[lane] = page_of_lane;
+      __syncwarp();
+      if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(d.npg * HKV * kTileBytes));
+      __syncwarp();
+      if (lane < d.npg)
+        tma_load_page(stage0 + s * kStageBytes + lane * (HKV * kTileBytes), &tmap, page_of_lane * 2, &full_bar[s]);
+      ++armed;
+      return true;
+    };
+
+    // ---- which chunks: the own range front to back, then the back of whoever has most left
+    if (lane == 0) {
+      // the first chunk is taken without an atomic; the rest of the range is up for grabs
+      atomicExch(&steal_tab[c], steal_pack(min(my_lo + 1, my_hi), my_hi));
+      __threadfence();
+    }
+    __syncwarp();
+    int cur_lo = my_lo, cur_hi = min(my_lo + 1, my_hi);  // interval of chunks in hand
+    auto next_interval = [&](int &lo_out, int &hi_out) -> bool {
+      unsigned long long got = 0;
+      bool have = false;
+      if (lane == 0) {
+        const unsigned long long old = atomicAdd(&steal_tab[c], 1ull);
+        if (steal_lo(old) < steal_hi(old)) {
+          got = steal_pack(steal_lo(old), steal_lo(old) + 1);
+          have = true;
         }
       }
+      have = __shfl_sync(0xffffffffu, have ? 1 : 0, 0) != 0;
+      if (!have && p.steal) {
+        // scratch slots are finite: every stolen interval is a run of its own
+        for (int attempt = 0; attempt < 8 && !have; ++attempt) {
+          int best = 0, who = -1;
+          for (int v = lane; v < G; v += 32) {
+            const unsigned long long w = __ldcg(&steal_tab[v]);
+            const int rem = steal_hi(w) - steal_lo(w);
+            if (v != c && rem > best) {
+              best = rem;
+              who = v;
+            }
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int ow = __shfl_xor_sync(0xffffffffu, who, o);
+            if (ob > best || (ob == best && ow > who)) {
+              best = ob;
+              who = ow;
+            }
+          }
+          if (best <= 0) break;
+          if (lane == 0) {
+            if (__ldcg(&ctl[0]) + 2 * G + B + 8 < p.num_slots) {
+              const int k = max(1, min(4, best / 2));
+              const unsigned long long old = atomicAdd(&steal_tab[who], 0ull - ((unsigned long long)k << 32));
+              const int lo_v = steal_lo(old), hi_v = steal_hi(old);
+              if (lo_v < hi_v) {
+                got = steal_pack(max(lo_v, hi_v - k), hi_v);
+                have = true;
+              }
+            } else {
+              best = -1;  // out of scratch slots: stop stealing
+            }
+          }
+          have = __shfl_sync(0xffffffffu, have ? 1 : 0, 0) != 0;
+          if (__shfl_sync(0xffffffffu, best, 0) < 0) break;
+        }
+      }
+      got = __shfl_sync(0xffffffffu, got, 0);
+      lo_out = steal_lo(got);
+      hi_out = steal_hi(got);
+      return have;
+    };
+
+    // ---- walk the chunks in hand; a run continues while the next chunk is the next one of the same request
+    bool have = cur_lo < cur_hi;
+    bool run_open = false;
+    int run_first = 0, run_pieces = 0;
+    while (have && ok) {
+      int b = request_of_page(ip, B, cur_lo * cp);
+      int nx_lo = 0, nx_hi = 0;
+      bool have_next = false;
+      for (int ck = cur_lo; ck < cur_hi && ok; ++ck) {
+        if (ck + 1 == cur_hi) have_next = next_interval(nx_lo, nx_hi);
+        const int next_ck = ck + 1 < cur_hi ? ck + 1 : (have_next ? nx_lo : -1);
+        int g = ck * cp;
+        const int chunk_end = min(total_pages, g + cp);
+        while (g < chunk_end && ok) {
+          while (b < B - 1 && ip[b + 1] <= g) ++b;
+          const int req_begin = ip[b], req_end = ip[b + 1];
+          const int seg_end = min(chunk_end, req_end);
+          if (seg_end <= g) {  // non-monotone indptr: give up cleanly
+            if (lane == 0) report_error(a.err, PIEKV_ERR_INDPTR, KID_DECODE, b, g);
+            if (lane == 0) atomicExch(&sh_abort, 1);
+            ok = false;
+            break;
+          }
+          const int c_first = req_begin / cp, c_last = (req_end - 1) / cp;
+          const bool two_level = c_last - c_first + 1 > gsz;
+          if (!run_open) {
+            run_open = true;
+            run_first = ck;
+            run_pieces = 0;
+          }
+          ++run_pieces;
+          // does the run go on after this piece?
+          const bool goes_on = seg_end < req_end && next_ck == ck + 1 && !(two_level && (ck + 1 - c_first) % gsz == 0);
+          const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
+          const bool starts = run_pieces == 1;
+          bool first_stage = true;
+          while (g < seg_end) {
+            const int npg = min(PG, seg_end - g);
+            int page = lane < npg ? __ldg(a.kv_indices + g + shift + lane) : 0;
+            if (lane < npg && (page < 0 || page >= a.num_pages)) {
+              report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
+              page = a.num_pages;  // outside the tensor map: the box is zero-filled
+            }
+            StageDesc d;
+            d.g = g;
+            d.b = b;
+            d.npg = npg;
+            d.flags = ((starts && first_stage) ? kRunStart : 0) | ((g + npg >= seg_end && !goes_on) ? kRunEnd : 0);
+            d.first_chunk = run_first;
+            d.pieces = run_pieces;
+            if (!publish(d, page)) {
+              ok = false;
+              break;
+            }
+            first_stage = false;
+            g += npg;
+          }
+          if (!goes_on) run_open = false;
+        }
+      }
+      have = have_next;
+      cur_lo = nx_lo;
+      cur_hi = nx_hi;
+    }
+    if (ok) {  // tell the consumers that nothing follows
+      StageDesc d;
+      d.g = -1;
+      d.b = 0;
+      d.npg = 0;
+      d.flags = 0;
+      d.first_chunk = 0;
+      d.pieces = 0;
+      publish(d, 0);
     }
     // Drain: do not let the CTA retire while a bulk copy may still be landing.
     __syncwarp();
@@ -305,325 +607,349 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (p.peer.n > 0) pb = use_alt ? p.peer.dst_alt[d] : p.peer.dst[d];
     return reinterpret_cast<T *>(pb) + ((size_t)b_ * row_heads + head_off + qh) * kDim;
   };
-  // Every CTA passes here exactly once after its last result store.  The CTA that arrives last
-  // publishes this step's number in every GPU's flag array: all stores of this launch, fenced at
-  // system scope by their threads, are ordered before it.
+  // Every CTA passes here exactly once after its last result store.  The CTA that arrives last tidies the
+  // zero-state block (scratch-slot counter, steal words) and, on a head-sharded run, publishes this step's
+  // number in every GPU's flag array: all stores of this launch, fenced at system scope by their threads,
+  // are ordered before it.
   auto finish = [&]() {
-    if (p.peer.n == 0) return;
-    __threadfence_system();
+    if (p.peer.n > 0) __threadfence_system();
     consumer_bar_sync();
     if (tid == 0) {
-      __threadfence_system();
-      const int old = atomicAdd(p.peer.done, 1);
-      if (old == (int)gridDim.x - 1) {
-        atomicExch(p.peer.done, 0);  // ready for the next launch
-        __threadfence_system();
-        for (int d = 0; d < p.peer.n; ++d)
-          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(peer_step) : "memory");
+      if (p.peer.n > 0) __threadfence_system();
+      const int old = atomicAdd(&ctl[1], 1);
+      if (old == G - 1) {
+        ctl[0] = 0;
+        ctl[1] = 0;  // ready for the next launch
+        for (int v = 0; v < G; ++v) steal_tab[v] = 0ull;
+        if (p.peer.n > 0) {
+          __threadfence_system();
+          for (int d = 0; d < p.peer.n; ++d)
+            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(peer_step) : "memory");
+        }
       }
     }
   };
 
   // requests without any page: softmax over nothing -> zeros
-  for (int b = c; b < B; b += gridDim.x) {
+  for (int b = c; b < B; b += G) {
     if (ip[b + 1] == ip[b]) {
       for (int d = 0; d < n_dst; ++d) {
         T *row = dst_row(d, b, 0);
-        for (int x = tid; x < a.hq * kDim; x += kConsumerWarps * 32) row[x] = Elem<T>::from_f32(0.f);
+        for (int x = tid; x < a.hq * kDim; x += kConsumers) row[x] = Elem<T>::from_f32(0.f);
       }
       if (a.lse != nullptr)
-        for (int x = tid; x < a.hq; x += kConsumerWarps * 32) a.lse[(size_t)b * a.hq + x] = -INFINITY;
+        for (int x = tid; x < a.hq; x += kConsumers) a.lse[(size_t)b * a.hq + x] = -INFINITY;
     }
   }
-  if (lo >= hi) {
-    finish();
-    return;
-  }
+
+  // whoever completes a count sees everybody else's partials
+  auto arrive = [&](int *counter, int add, int expected) -> bool {
+    __threadfence();
+    consumer_bar_sync();
+    if (tid == 0) {
+      const int old = atomicAdd(counter, add);
+      sh_last = (old + add == expected) ? 1 : 0;
+      if (sh_last) *counter = 0;  // ready for the next launch (nobody else touches it any more)
+    }
+    consumer_bar_sync();
+    const bool last = sh_last != 0;
+    consumer_bar_sync();  // everyone has read sh_last before it is rewritten
+    if (last) __threadfence();
+    return last;
+  };
+  auto collect = [&](unsigned short *tab, int first, int count) -> int {
+    return collect_slots(tab, first, count, sh_list, &sh_nlist, sh_wsum);
+  };
+  auto merge_list = [&](int n, int subs, int b_, int to_slot) {
+    merge_slots<T, PG>(p, sh_list, n, subs, b_, to_slot, peer_step);
+  };
 
   uint32_t qa[8][4];
   float o[16][4];
-  int b = request_of_page(ip, B, lo);
-  int g = lo;
-  int it = 0;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  int b = 0, req_begin = 0, req_end = 0, last_len = kPage, rope_pos = 0, win_first = 0;
   bool aborted = false;
 
-  while (g < hi) {
-    // ================= open the segment of request b that starts at flat page g
-    while (b < B - 1 && ip[b + 1] <= g) ++b;
-    const int req_begin = ip[b];
-    const int req_end = ip[b + 1];
-    const int seg_end = min(hi, req_end);
-    if (seg_end <= g) break;  // non-monotone indptr (the producer reports it)
-    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-    {
-      // query fragments of this head's group (rows beyond the group are zero)
-      const T *qb = reinterpret_cast<const T *>(a.q) + (size_t)b * a.q_sn + (size_t)(h * group) * a.q_sh;
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        const int col = ks * 16 + qlane * 2;
-        const uint32_t *r0 = reinterpret_cast<const uint32_t *>(qb + (size_t)quad * a.q_sh + col);
-        const uint32_t *r1 = reinterpret_cast<const uint32_t *>(qb + (size_t)(quad + 8) * a.q_sh + col);
-        qa[ks][0] = quad < group ? __ldg(r0) : 0u;
-        qa[ks][1] = quad + 8 < group ? __ldg(r1) : 0u;
-        qa[ks][2] = quad < group ? __ldg(r0 + 4) : 0u;
-        qa[ks][3] = quad + 8 < group ? __ldg(r1 + 4) : 0u;
-      }
+  for (int it = 0;; ++it) {
+    const int s = it % kStages;
+    const uint32_t ph = (it / kStages) & 1;
+    if (!aborted && *(volatile int *)&sh_abort) aborted = true;
+    if (!aborted && !mbar_wait(&full_bar[s], ph)) {
+      if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
+      if (lane == 0) atomicExch(&sh_abort, 1);
+      aborted = true;
     }
-    int last_len = a.kv_last_page_len[b];
-    if (last_len < 1 || last_len > kPage) {
-      if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
-      last_len = last_len < 1 ? 1 : kPage;
+    if (aborted) break;
+    const int g = sh_desc[s].g;
+    if (g < 0) {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      break;
     }
-    int shift = 0, win_first = 0;
-    if (windowed) {
-      const int2 wm = __ldg(p.win_meta + b);
-      shift = wm.x;
-      win_first = wm.y;
-    }
-    int rope_pos = 0;
-    int last_phys = -1;  // physical id of the request's last page when this segment contains it
-    if (FUSED) {
-      rope_pos = f.pos_ids[b];
-      if (f.rope.mode == PIEKV_ROPE_TABLE && (rope_pos < 0 || rope_pos >= f.rope.table_len)) {
-        if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
-        rope_pos = 0;
-      }
-      if (seg_end == req_end) last_phys = __ldg(a.kv_indices + req_end - 1 + shift);
-      // rotate the query fragments in registers (one rounding to T, as the in-place op does)
-      if (f.rope.mode != PIEKV_ROPE_NONE) {
-        if (!f.rope.interleave) {
-          // element d pairs with d + 64: fragments ks and ks + 4 of the same thread
+    const int npg = sh_desc[s].npg;
+    const int flags = sh_desc[s].flags;
+    const int run_first = sh_desc[s].first_chunk;
+    const int run_pieces = sh_desc[s].pieces;
+    const int my_page = pslot < npg ? sh_desc[s].page[pslot] : -1;
+    if (it == 0) PIEKV_STAMP(1);
+
+    if (flags & kRunStart) {
+      // ================= open a run of request b
+      b = sh_desc[s].b;
+      req_begin = ip[b];
+      req_end = ip[b + 1];
+      m0 = m1 = -INFINITY;
+      l0 = l1 = 0.f;
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
+      for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+      {
+        // query fragments of this head's group (rows beyond the group are zero)
+        const T *qb = reinterpret_cast<const T *>(a.q) + (size_t)b * a.q_sn + (size_t)(h * group) * a.q_sh;
 #pragma unroll
-            for (int hi8 = 0; hi8 < 2; ++hi8) {
-              const int i0 = ks * 16 + hi8 * 8 + qlane * 2;
-              float c0, s0, c1, s1;
-              rope_cos_sin1(f.rope, rope_pos, i0, 64, c0, s0);
-              rope_cos_sin1(f.rope, rope_pos, i0 + 1, 64, c1, s1);
-#pragma unroll
-              for (int rr = 0; rr < 2; ++rr) {
-                const int j = hi8 * 2 + rr;
-                const float2 x = unpack2<T>(qa[ks][j]);
-                const float2 y = unpack2<T>(qa[ks + 4][j]);
-                float xa, ya, xb, yb;
-                rope_rotate(x.x, y.x, c0, s0, xa, ya);
-                rope_rotate(x.y, y.y, c1, s1, xb, yb);
-                qa[ks][j] = pack2<T>(xa, xb);
-                qa[ks + 4][j] = pack2<T>(ya, yb);
-              }
-            }
-          }
-        } else {
-          // pairs (2i, 2i+1) sit in one register
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-#pragma unroll
-            for (int hi8 = 0; hi8 < 2; ++hi8) {
-              const int pair = (ks * 16 + hi8 * 8 + qlane * 2) >> 1;
-              float c0, s0;
-              rope_cos_sin1(f.rope, rope_pos, pair, 64, c0, s0);
-#pragma unroll
-              for (int rr = 0; rr < 2; ++rr) {
-                const int j = hi8 * 2 + rr;
-                const float2 x = unpack2<T>(qa[ks][j]);
-                float xa, ya;
-                rope_rotate(x.x, x.y, c0, s0, xa, ya);
-                qa[ks][j] = pack2<T>(xa, ya);
-              }
-            }
-          }
+        for (int ks = 0; ks < 8; ++ks) {
+          const int col = ks * 16 + qlane * 2;
+          const uint32_t *r0 = reinterpret_cast<const uint32_t *>(qb + (size_t)quad * a.q_sh + col);
+          const uint32_t *r1 = reinterpret_cast<const uint32_t *>(qb + (size_t)(quad + 8) * a.q_sh + col);
+          qa[ks][0] = quad < group ? __ldg(r0) : 0u;
+          qa[ks][1] = quad + 8 < group ? __ldg(r1) : 0u;
+          qa[ks][2] = quad < group ? __ldg(r0 + 4) : 0u;
+          qa[ks][3] = quad + 8 < group ? __ldg(r1 + 4) : 0u;
         }
       }
-    }
-
-    // ================= stream the segment's pages
-    while (g < seg_end) {
-      const int npg = min(PG, seg_end - g);
-      const int s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1;
-      if (!aborted && *(volatile int *)&sh_abort) aborted = true;
-      if (!aborted && !mbar_wait(&full_bar[s], ph)) {
-        if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
-        if (lane == 0) atomicExch(&sh_abort, 1);
-        aborted = true;
+      last_len = a.kv_last_page_len[b];
+      if (last_len < 1 || last_len > kPage) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
+        last_len = last_len < 1 ? 1 : kPage;
       }
-      if (it == 0) PIEKV_STAMP(1);
-      if (!aborted && pslot < npg) {
-        const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
-        const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
-        const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
-        const uint32_t ktile = page_base + h * 4096;
-        const uint32_t vtile = page_base + HKV * 4096 + h * 4096;
-        if (FUSED && g + pslot == req_end - 1) {
-          // This warp owns (last page, head h): rotate the new token's k, copy its v, store both
-          // into the pool for later steps and patch them into the staged tile for this one.
-          const int row = last_len - 1;
-          uint8_t *kp = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + h * 4096;
-          uint8_t *vp = kp + HKV * 4096;
-          const T *ksrc = reinterpret_cast<const T *>(f.k_new) + (size_t)b * f.k_sn + (size_t)h * f.k_sh;
-          const T *vsrc = reinterpret_cast<const T *>(f.v_new) + (size_t)b * f.v_sn + (size_t)h * f.v_sh;
-          const bool page_ok = last_phys >= 0 && last_phys < a.num_pages;
-          T *pool = reinterpret_cast<T *>(const_cast<void *>(a.pool));
-          T *kdst = pool + ((size_t)last_phys * 2 * kPage + row) * (HKV * kDim) + h * kDim;
-          T *vdst = kdst + (size_t)kPage * HKV * kDim;
-          // smem byte offset of element d of `row` inside a [2][16][64] swizzled tile
-          auto tile_off = [&](int d) { return (d >> 6) * 2048 + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2; };
-          if (f.rope.mode == PIEKV_ROPE_NONE) {
-            const int d = lane * 4;
-            const uint2 kv = *reinterpret_cast<const uint2 *>(ksrc + d);
-            *reinterpret_cast<uint2 *>(kp + tile_off(d)) = kv;
-            if (page_ok) *reinterpret_cast<uint2 *>(kdst + d) = kv;
-          } else if (!f.rope.interleave) {
+      win_first = windowed ? __ldg(&p.win_meta[b].y) : 0;
+      if (FUSED) {
+        rope_pos = f.pos_ids[b];
+        if (f.rope.mode == PIEKV_ROPE_TABLE && (rope_pos < 0 || rope_pos >= f.rope.table_len)) {
+          if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
+          rope_pos = 0;
+        }
+        // rotate the query fragments in registers (one rounding to T, as the in-place op does)
+        if (f.rope.mode != PIEKV_ROPE_NONE) {
+          if (!f.rope.interleave) {
+            // element d pairs with d + 64: fragments ks and ks + 4 of the same thread
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-              const int i = lane + 32 * rr;
-              float cc, ss, xo, yo;
-              rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
-              rope_rotate(Elem<T>::to_f32(ksrc[i]), Elem<T>::to_f32(ksrc[i + 64]), cc, ss, xo, yo);
-              const T xt = Elem<T>::from_f32(xo), yt = Elem<T>::from_f32(yo);
-              *reinterpret_cast<T *>(kp + tile_off(i)) = xt;
-              *reinterpret_cast<T *>(kp + tile_off(i + 64)) = yt;
-              if (page_ok) {
-                kdst[i] = xt;
-                kdst[i + 64] = yt;
+            for (int ks = 0; ks < 4; ++ks) {
+#pragma unroll
+              for (int hi8 = 0; hi8 < 2; ++hi8) {
+                const int i0 = ks * 16 + hi8 * 8 + qlane * 2;
+                float c0, s0, c1, s1;
+                rope_cos_sin1(f.rope, rope_pos, i0, 64, c0, s0);
+                rope_cos_sin1(f.rope, rope_pos, i0 + 1, 64, c1, s1);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                  const int j = hi8 * 2 + rr;
+                  const float2 x = unpack2<T>(qa[ks][j]);
+                  const float2 y = unpack2<T>(qa[ks + 4][j]);
+                  float xa, ya, xb, yb;
+                  rope_rotate(x.x, y.x, c0, s0, xa, ya);
+                  rope_rotate(x.y, y.y, c1, s1, xb, yb);
+                  qa[ks][j] = pack2<T>(xa, xb);
+                  qa[ks + 4][j] = pack2<T>(ya, yb);
+                }
               }
             }
           } else {
+            // pairs (2i, 2i+1) sit in one register
 #pragma unroll
-            for (int rr = 0; rr < 2; ++rr) {
-              const int i = lane + 32 * rr;  // pair (2i, 2i+1)
-              float cc, ss, xo, yo;
-              rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
-              rope_rotate(Elem<T>::to_f32(ksrc[2 * i]), Elem<T>::to_f32(ksrc[2 * i + 1]), cc, ss, xo, yo);
-              const uint32_t pk = pack2<T>(xo, yo);
-              *reinterpret_cast<uint32_t *>(kp + tile_off(2 * i)) = pk;
-              if (page_ok) *reinterpret_cast<uint32_t *>(kdst + 2 * i) = pk;
+            for (int ks = 0; ks < 8; ++ks) {
+#pragma unroll
+              for (int hi8 = 0; hi8 < 2; ++hi8) {
+                const int pair = (ks * 16 + hi8 * 8 + qlane * 2) >> 1;
+                float c0, s0;
+                rope_cos_sin1(f.rope, rope_pos, pair, 64, c0, s0);
+#pragma unroll
+                for (int rr = 0; rr < 2; ++rr) {
+                  const int j = hi8 * 2 + rr;
+                  const float2 x = unpack2<T>(qa[ks][j]);
+                  float xa, ya;
+                  rope_rotate(x.x, x.y, c0, s0, xa, ya);
+                  qa[ks][j] = pack2<T>(xa, ya);
+                }
+              }
             }
-          }
-          {
-            const int d = lane * 4;
-            const uint2 vv = *reinterpret_cast<const uint2 *>(vsrc + d);
-            *reinterpret_cast<uint2 *>(vp + tile_off(d)) = vv;
-            if (page_ok) *reinterpret_cast<uint2 *>(vdst + d) = vv;
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-        }
-        if (valid < kPage) {
-          // rows past the end of the context may hold anything: zero the V rows so that
-          // 0 * garbage cannot produce NaN (their scores are masked to -inf below)
-          uint8_t *vptr = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + HKV * 4096 + h * 4096;
-          for (int x = lane; x < (kPage - valid) * 16; x += 32) {
-            const int row = valid + (x >> 4);
-            const int hf = (x >> 3) & 1;
-            const int ch = x & 7;
-            *reinterpret_cast<uint4 *>(vptr + hf * 2048 + row * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-        }
-        // ---- S = Q K^T : 16 rows x 16 tokens
-        float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        {
-          const int mi = lane >> 3, r = lane & 7;
-          const int t = (mi >> 1) * 8 + r;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const int hf = ks >> 2;
-            const int ch = (ks & 3) * 2 + (mi & 1);
-            uint32_t kb[4];
-            ldmatrix_x4(kb, ktile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
-            mma_16816<T>(sc[0], qa[ks], kb[0], kb[1]);
-            mma_16816<T>(sc[1], qa[ks], kb[2], kb[3]);
-          }
-        }
-        // ---- online softmax (base 2); rows quad and quad+8, tokens nt*8 + qlane*2 + {0,1}
-        float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int tok = nt * 8 + qlane * 2 + e;
-            const bool ok = tok < valid && tok >= tok_lo;
-            sc[nt][e] = ok ? sc[nt][e] * scale_log2 : -INFINITY;
-            sc[nt][2 + e] = ok ? sc[nt][2 + e] * scale_log2 : -INFINITY;
-            mx0 = fmaxf(mx0, sc[nt][e]);
-            mx1 = fmaxf(mx1, sc[nt][2 + e]);
-          }
-        }
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-        const float mu0 = mn0 == -INFINITY ? 0.f : mn0;
-        const float mu1 = mn1 == -INFINITY ? 0.f : mn1;
-        const float al0 = fast_exp2(m0 - mu0), al1 = fast_exp2(m1 - mu1);
-        m0 = mn0;
-        m1 = mn1;
-        float ps0 = 0.f, ps1 = 0.f;
-#pragma unroll
-        for (int nt = 0; nt < 2; ++nt) {
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            sc[nt][e] = fast_exp2(sc[nt][e] - mu0);
-            sc[nt][2 + e] = fast_exp2(sc[nt][2 + e] - mu1);
-            ps0 += sc[nt][e];
-            ps1 += sc[nt][2 + e];
-          }
-        }
-        l0 = l0 * al0 + ps0;
-        l1 = l1 * al1 + ps1;
-        if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
-#pragma unroll
-          for (int nt = 0; nt < 16; ++nt) {
-            o[nt][0] *= al0;
-            o[nt][1] *= al0;
-            o[nt][2] *= al1;
-            o[nt][3] *= al1;
-          }
-        }
-        // ---- O += P V
-        uint32_t pa[4];
-        pa[0] = pack2<T>(sc[0][0], sc[0][1]);
-        pa[1] = pack2<T>(sc[0][2], sc[0][3]);
-        pa[2] = pack2<T>(sc[1][0], sc[1][1]);
-        pa[3] = pack2<T>(sc[1][2], sc[1][3]);
-        {
-          const int mi = lane >> 3, r = lane & 7;
-          const int t = (mi & 1) * 8 + r;
-#pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const int hf = i >> 2;
-            const int ch = (i & 3) * 2 + (mi >> 1);
-            uint32_t vb[4];
-            ldmatrix_x4_trans(vb, vtile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
-            mma_16816<T>(o[2 * i], pa, vb[0], vb[1]);
-            mma_16816<T>(o[2 * i + 1], pa, vb[2], vb[3]);
           }
         }
       }
-      __syncwarp();
-      if (lane == 0 && !aborted) mbar_arrive(&empty_bar[s]);
-      g += npg;
-      ++it;
     }
 
-    // ================= close the segment: publish the result or the partial
-    if (g >= hi) PIEKV_STAMP(2);
-    const int c_first = cta_of_page(req_begin, total_pages, G);
-    const int c_last = cta_of_page(req_end - 1, total_pages, G);
-    const int nseg = c_last - c_first + 1;
+    // ================= the stage's pages
+    if (pslot < npg) {
+      const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
+      const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
+      const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
+      const uint32_t ktile = page_base + h * 4096;
+      const uint32_t vtile = page_base + HKV * 4096 + h * 4096;
+      if (FUSED && g + pslot == req_end - 1) {
+        // This warp owns (last page, head h): rotate the new token's k, copy its v, store both
+        // into the pool for later steps and patch them into the staged tile for this one.
+        const int row = last_len - 1;
+        const int last_phys = my_page;
+        uint8_t *kp = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + h * 4096;
+        uint8_t *vp = kp + HKV * 4096;
+        const T *ksrc = reinterpret_cast<const T *>(f.k_new) + (size_t)b * f.k_sn + (size_t)h * f.k_sh;
+        const T *vsrc = reinterpret_cast<const T *>(f.v_new) + (size_t)b * f.v_sn + (size_t)h * f.v_sh;
+        const bool page_ok = last_phys >= 0 && last_phys < a.num_pages;
+        T *pool = reinterpret_cast<T *>(const_cast<void *>(a.pool));
+        T *kdst = pool + ((size_t)last_phys * 2 * kPage + row) * (HKV * kDim) + h * kDim;
+        T *vdst = kdst + (size_t)kPage * HKV * kDim;
+        // smem byte offset of element d of `row` inside a [2][16][64] swizzled tile
+        auto tile_off = [&](int d) { return (d >> 6) * 2048 + row * 128 + ((((d & 63) >> 3) ^ (row & 7)) << 4) + (d & 7) * 2; };
+        if (f.rope.mode == PIEKV_ROPE_NONE) {
+          const int d = lane * 4;
+          const uint2 kv = *reinterpret_cast<const uint2 *>(ksrc + d);
+          *reinterpret_cast<uint2 *>(kp + tile_off(d)) = kv;
+          if (page_ok) *reinterpret_cast<uint2 *>(kdst + d) = kv;
+        } else if (!f.rope.interleave) {
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int i = lane + 32 * rr;
+            float cc, ss, xo, yo;
+            rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
+            rope_rotate(Elem<T>::to_f32(ksrc[i]), Elem<T>::to_f32(ksrc[i + 64]), cc, ss, xo, yo);
+            const T xt = Elem<T>::from_f32(xo), yt = Elem<T>::from_f32(yo);
+            *reinterpret_cast<T *>(kp + tile_off(i)) = xt;
+            *reinterpret_cast<T *>(kp + tile_off(i + 64)) = yt;
+            if (page_ok) {
+              kdst[i] = xt;
+              kdst[i + 64] = yt;
+            }
+          }
+        } else {
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int i = lane + 32 * rr;  // pair (2i, 2i+1)
+            float cc, ss, xo, yo;
+            rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
+            rope_rotate(Elem<T>::to_f32(ksrc[2 * i]), Elem<T>::to_f32(ksrc[2 * i + 1]), cc, ss, xo, yo);
+            const uint32_t pk = pack2<T>(xo, yo);
+            *reinterpret_cast<uint32_t *>(kp + tile_off(2 * i)) = pk;
+            if (page_ok) *reinterpret_cast<uint32_t *>(kdst + 2 * i) = pk;
+          }
+        }
+        {
+          const int d = lane * 4;
+          const uint2 vv = *reinterpret_cast<const uint2 *>(vsrc + d);
+          *reinterpret_cast<uint2 *>(vp + tile_off(d)) = vv;
+          if (page_ok) *reinterpret_cast<uint2 *>(vdst + d) = vv;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      if (valid < kPage) {
+        // rows past the end of the context may hold anything: zero the V rows so that
+        // 0 * garbage cannot produce NaN (their scores are masked to -inf below)
+        uint8_t *vptr = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + HKV * 4096 + h * 4096;
+        for (int x = lane; x < (kPage - valid) * 16; x += 32) {
+          const int row = valid + (x >> 4);
+          const int hf = (x >> 3) & 1;
+          const int ch = x & 7;
+          *reinterpret_cast<uint4 *>(vptr + hf * 2048 + row * 128 + ch * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+      }
+      // ---- S = Q K^T : 16 rows x 16 tokens
+      float sc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int t = (mi >> 1) * 8 + r;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int hf = ks >> 2;
+          const int ch = (ks & 3) * 2 + (mi & 1);
+          uint32_t kb[4];
+          ldmatrix_x4(kb, ktile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
+          mma_16816<T>(sc[0], qa[ks], kb[0], kb[1]);
+          mma_16816<T>(sc[1], qa[ks], kb[2], kb[3]);
+        }
+      }
+      // ---- online softmax (base 2); rows quad and quad+8, tokens nt*8 + qlane*2 + {0,1}
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = nt * 8 + qlane * 2 + e;
+          const bool okt = tok < valid && tok >= tok_lo;
+          sc[nt][e] = okt ? sc[nt][e] * scale_log2 : -INFINITY;
+          sc[nt][2 + e] = okt ? sc[nt][2 + e] * scale_log2 : -INFINITY;
+          mx0 = fmaxf(mx0, sc[nt][e]);
+          mx1 = fmaxf(mx1, sc[nt][2 + e]);
+        }
+      }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float mu0 = mn0 == -INFINITY ? 0.f : mn0;
+      const float mu1 = mn1 == -INFINITY ? 0.f : mn1;
+      const float al0 = fast_exp2(m0 - mu0), al1 = fast_exp2(m1 - mu1);
+      m0 = mn0;
+      m1 = mn1;
+      float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          sc[nt][e] = fast_exp2(sc[nt][e] - mu0);
+          sc[nt][2 + e] = fast_exp2(sc[nt][2 + e] - mu1);
+          ps0 += sc[nt][e];
+          ps1 += sc[nt][2 + e];
+        }
+      }
+      l0 = l0 * al0 + ps0;
+      l1 = l1 * al1 + ps1;
+      if (__any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f)) {
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) {
+          o[nt][0] *= al0;
+          o[nt][1] *= al0;
+          o[nt][2] *= al1;
+          o[nt][3] *= al1;
+        }
+      }
+      // ---- O += P V
+      uint32_t pa[4];
+      pa[0] = pack2<T>(sc[0][0], sc[0][1]);
+      pa[1] = pack2<T>(sc[0][2], sc[0][3]);
+      pa[2] = pack2<T>(sc[1][0], sc[1][1]);
+      pa[3] = pack2<T>(sc[1][2], sc[1][3]);
+      {
+        const int mi = lane >> 3, r = lane & 7;
+        const int t = (mi & 1) * 8 + r;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int hf = i >> 2;
+          const int ch = (i & 3) * 2 + (mi >> 1);
+          uint32_t vb[4];
+          ldmatrix_x4_trans(vb, vtile + hf * 2048 + t * 128 + ((ch ^ r) << 4));
+          mma_16816<T>(o[2 * i], pa, vb[0], vb[1]);
+          mma_16816<T>(o[2 * i + 1], pa, vb[2], vb[3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);
+    if (!(flags & kRunEnd)) continue;
+
+    // ================= close the run: publish the result or the partial
+    PIEKV_STAMP(2);
+    const int c_first = req_begin / cp;
+    const int c_last = (req_end - 1) / cp;
+    const int nseg = c_last - c_first + 1;  // chunk pieces of the request
     float ls0 = l0, ls1 = l1;  // quad-reduce the running sums
     ls0 += __shfl_xor_sync(0xffffffffu, ls0, 1);
     ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
     ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
     ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
-    if (PG == 1 && nseg == 1) {
-      // the whole request lived in this CTA: normalise and store
+    if (PG == 1 && run_pieces == nseg) {
+      // the whole request lived in this run: normalise and store
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int row = quad + half * 8;
@@ -652,101 +978,76 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       continue;
     }
-    const size_t pidx = (size_t)(c + b) * PG + pslot;
+    // a scratch slot for this run
+    if (tid == 0) sh_slot = atomicAdd(&ctl[0], 1);
+    consumer_bar_sync();
+    const int slot = sh_slot;
+    consumer_bar_sync();
+    if (slot >= p.num_slots) {
+      if (tid == 0) report_error(a.err, PIEKV_ERR_PAGE_CAPACITY, KID_DECODE, c, slot);
+      if (tid == 0) atomicExch(&sh_abort, 1);
+      aborted = true;
+      break;
+    }
+    {
+      const size_t pidx = (size_t)slot * PG + pslot;
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int row = quad + half * 8;
-      if (row < group) {
-        const int qh = h * group + row;
-        float2 *orow = reinterpret_cast<float2 *>(p.part_o + (pidx * a.hq + qh) * kDim);
+      for (int half = 0; half < 2; ++half) {
+        const int row = quad + half * 8;
+        if (row < group) {
+          const int qh = h * group + row;
+          float2 *orow = reinterpret_cast<float2 *>(p.part_o + (pidx * a.hq + qh) * kDim);
 #pragma unroll
-        for (int nt = 0; nt < 16; ++nt) orow[nt * 4 + qlane] = make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
-        if (qlane == 0) p.part_ml[pidx * a.hq + qh] = make_float2(half ? m1 : m0, half ? ls1 : ls0);
+          for (int nt = 0; nt < 16; ++nt) orow[nt * 4 + qlane] = make_float2(o[nt][half * 2], o[nt][half * 2 + 1]);
+          if (qlane == 0) p.part_ml[pidx * a.hq + qh] = make_float2(half ? m1 : m0, half ? ls1 : ls0);
+        }
       }
     }
-    // Combine `n` partials of request b, `stride` slots apart starting at slot `first`: thread ->
-    // (query head tid/32 + 8k, 4 consecutive d).  Two passes so that the loads of a pass are
-    // independent of one another and stay in flight together: first the global maximum, then the
-    // weighted sums.  The result is either the request's output row (normalised) or again a partial
-    // (maximum, sum, unnormalised accumulator) written over slot `first`.
-    auto merge_parts = [&](size_t first, size_t stride, int n, bool to_partial) {
-      const int d4 = (tid & 31) * 4;
-      for (int qh = tid >> 5; qh < a.hq; qh += kConsumerWarps) {
-        float M = -INFINITY;
-#pragma unroll 8
-        for (int pp = 0; pp < n; ++pp) {
-          const float2 ml = __ldcg(p.part_ml + (first + pp * stride) * a.hq + qh);
-          M = ml.y > 0.f ? fmaxf(M, ml.x) : M;
-        }
-        float L = 0.f;
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-        for (int pp = 0; pp < n; ++pp) {
-          const size_t idx = (first + pp * stride) * a.hq + qh;
-          const float2 ml = __ldcg(p.part_ml + idx);
-          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + idx * kDim + d4));
-          const float w = ml.y > 0.f ? fast_exp2(ml.x - M) : 0.f;  // a warp that saw no page: weight 0
-          L = fmaf(ml.y, w, L);
-          acc.x = fmaf(po.x, w, acc.x);
-          acc.y = fmaf(po.y, w, acc.y);
-          acc.z = fmaf(po.z, w, acc.z);
-          acc.w = fmaf(po.w, w, acc.w);
-        }
-        if (to_partial) {
-          __syncwarp();  // every lane has read slot `first` of this head before it is overwritten
-          const size_t idx = first * a.hq + qh;
-          *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc;
-          if ((tid & 31) == 0) p.part_ml[idx] = make_float2(M, L);
-          continue;
-        }
-        L = add_sink(L, M, a.sinks, qh);
-        const float inv = L > 0.f ? 1.f / L : 0.f;
-        uint2 pk;
-        pk.x = pack2<T>(acc.x * inv, acc.y * inv);
-        pk.y = pack2<T>(acc.z * inv, acc.w * inv);
-        if (p.peer.n == 0) {
-          *reinterpret_cast<uint2 *>(out + ((size_t)b * a.hq + qh) * kDim + d4) = pk;
-        } else {
-          for (int d = 0; d < n_dst; ++d) *reinterpret_cast<uint2 *>(dst_row(d, b, qh) + d4) = pk;
-        }
-        if (a.lse != nullptr && (tid & 31) == 0)
-          a.lse[(size_t)b * a.hq + qh] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
-      }
-    };
-    // whoever arrives last on a counter sees everybody else's partials
-    auto arrive_last = [&](int *counter, int expected) -> bool {
+    // The run's registers are dead from here on (the next stage opens a new run); saying so keeps them from
+    // being saved around the merge calls below.
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
+    m0 = m1 = -INFINITY;
+    l0 = l1 = 0.f;
+    const int tab_idx = run_first + b;  // unique per (chunk piece, request)
+    if (nseg <= gsz) {
       __threadfence();
       consumer_bar_sync();
-      if (tid == 0) {
-        const int old = atomicAdd(counter, 1);
-        sh_last = (old == expected - 1) ? 1 : 0;
-        if (sh_last) *counter = 0;  // ready for the next launch (nobody else touches it any more)
-      }
-      consumer_bar_sync();
-      const bool last = sh_last != 0;
-      consumer_bar_sync();  // everyone has read sh_last before it is rewritten
-      if (last) __threadfence();
-      return last;
-    };
-    if (nseg <= kMergeGroup) {
-      if (!arrive_last(&p.counters[b], nseg)) continue;
-      merge_parts((size_t)(c_first + b) * PG, 1, nseg * PG, false);
+      if (tid == 0) run_tab[tab_idx] = (unsigned short)(slot + 1);
+      if (!arrive(&req_cnt[b], run_pieces, nseg)) continue;
+      const int n = collect(run_tab, c_first + b, nseg);
+      merge_list(n, PG, b, -1);
       continue;
     }
-    // A request cut over many CTAs (one long context): merging 100+ partials in a single CTA would sit
-    // on the critical path of the whole launch.  Segments are grouped kMergeGroup at a time; the last
-    // CTA of a group folds the group into one partial (groups fold concurrently on different SMs), and
-    // the last group to finish folds the groups.
-    const int gi = (c - c_first) / kMergeGroup;
-    const int g_first = c_first + gi * kMergeGroup;
-    const int g_size = min(kMergeGroup, c_last + 1 - g_first);
-    const int n_groups = (nseg + kMergeGroup - 1) / kMergeGroup;
-    if (!arrive_last(&p.counters[kGroupCounter0 + g_first], g_size)) continue;
-    merge_parts((size_t)(g_first + b) * PG, 1, g_size * PG, true);
-    if (!arrive_last(&p.counters[b], n_groups)) continue;
-    merge_parts((size_t)(c_first + b) * PG, (size_t)kMergeGroup * PG, n_groups, false);
+    // A request spread over many chunks (one long context): merging 100+ partials in a single CTA would sit
+    // on the critical path of the whole launch.  Its chunk pieces are grouped gsz at a time (runs end at
+    // group boundaries); whoever completes a group folds it into one partial (groups fold concurrently on
+    // different SMs), and whoever completes the last group folds the groups.
+    const int gi = (run_first - c_first) / gsz;
+    const int g_first = c_first + gi * gsz;
+    const int g_size = min(gsz, c_last + 1 - g_first);
+    const int n_groups = (nseg + gsz - 1) / gsz;
+    __threadfence();
+    consumer_bar_sync();
+    if (tid == 0) run_tab[tab_idx] = (unsigned short)(slot + 1);
+    if (!arrive(&grp_cnt[g_first + b], run_pieces, g_size)) continue;
+    {
+      const int n = collect(run_tab, g_first + b, g_size);
+      merge_list(n, PG, b, slot);  // into sub-slot 0 of this run's own slot
+    }
+    __threadfence();
+    consumer_bar_sync();
+    if (tid == 0) grp_tab[g_first + b] = (unsigned short)(slot + 1);
+    if (!arrive(&req_cnt[b], 1, n_groups)) continue;
+    {
+      const int n = collect(grp_tab, c_first + b, nseg);
+      merge_list(n, 1, b, -1);
+    }
   }
   PIEKV_STAMP(3);
+  if (aborted && tid == 0) steal_tab[c] = 0ull;  // nothing of an abandoned range may look stealable later
   finish();
 }
 
@@ -807,25 +1108,38 @@ bool decode_tma_supported(const AttnArgs &a, int dtype) {
   return true;
 }
 
-int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
+// Scratch slots (one per run that has to be merged): the least a launch can need when every CTA keeps to its
+// own chunks - a run per CTA, per request boundary and per group boundary - and what lets idle CTAs take
+// over other CTAs' chunks freely (every stolen interval is a run of its own).
+static int64_t min_slots(int batch) { return 2ll * sm_count() + batch + 64; }
+static int64_t full_slots(int batch) { return 6ll * sm_count() + 2ll * batch + 64; }
+static int64_t slot_bytes(int hq, int hkv) {
   const int pg = (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8) ? 8 / hkv : 1;
-  const int64_t slots = (int64_t)sm_count() + batch;
-  const int64_t window_meta = (((int64_t)batch + 1) * 12 + 255) / 256 * 256;  // win_indptr + win_meta
-  return kCounterBytes + slots * pg * hq * (kDim * 4 + 8) + 512 + window_meta;
+  return (int64_t)pg * hq * (kDim * 4 + 8);
+}
+static int64_t window_meta_bytes(int batch) { return (((int64_t)batch + 1) * 12 + 255) / 256 * 256; }
+
+int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
+  return kCounterBytes + min_slots(batch) * slot_bytes(hq, hkv) + 512 + window_meta_bytes(batch);
 }
 
 static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, DecodeParams *p,
                    CUtensorMap *tm, cudaStream_t st) {
   const int pg = 8 / a.hkv;
-  const int64_t slots = (int64_t)sm_count() + a.batch;
   const int64_t need = decode_tma_workspace_bytes(a.batch, a.hq, a.hkv);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "decode: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)need);
   PIEKV_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "decode: workspace must be 256-byte aligned");
-  PIEKV_REQUIRE(sm_count() <= kGroupCounters, "decode: %d SMs, the group counters hold %d", sm_count(), kGroupCounters);
+  PIEKV_REQUIRE(sm_count() <= kMaxGrid, "decode: %d SMs, the steal table holds %d", sm_count(), kMaxGrid);
+  // as many scratch slots as the workspace holds, up to what free stealing can use
+  int64_t slots = (workspace_bytes - kCounterBytes - 512 - window_meta_bytes(a.batch)) / slot_bytes(a.hq, a.hkv);
+  if (slots > full_slots(a.batch)) slots = full_slots(a.batch);
+  if (slots > kMaxSlots) slots = kMaxSlots;
   p->a = a;
   p->peer = PeerOut{};
   p->pdl = get_option(PIEKV_OPT_PDL);
+  p->steal = get_option(PIEKV_OPT_DETERMINISTIC) ? 0 : 1;
+  p->num_slots = (int)slots;
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p->counters = reinterpret_cast<int *>(ws);
   p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
@@ -875,7 +1189,7 @@ int launch_decode_fused_tma(const AttnArgs &a, int dtype, const void *k, const v
   if (int rc = prepare(a, dtype, workspace, workspace_bytes, &p, &tm, st)) return rc;
   if (peer != nullptr && peer->n > 0) {
     p.peer = *peer;
-    p.peer.done = p.counters + (kCounterBytes / 4 - 1);  // last word of the counter block
+    p.peer.done = nullptr;  // completion is counted in the zero-state block
   }
   FusedArgs f;
   f.k_new = k;
@@ -978,12 +1292,9 @@ extern "C" int piekv_decode_run_noalloc(const void *q, int64_t q_stride_n, int64
   if (!decode_tma_supported(a, dtype)) return launch_attn_generic(a, dtype, st);
   void *scratch = nullptr;
   if (int rc = static_scratch_ptr(&scratch)) return rc;
-  // the arrival counters must be zero when the kernel starts, whatever an earlier call left behind
-  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)batch * sizeof(int), st);
-  if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaMemsetAsync");
-  // and the group counters of the two-level merge, at the tail of the counter block
-  e = cudaMemsetAsync(reinterpret_cast<uint8_t *>(scratch) + (size_t)kGroupCounter0 * sizeof(int), 0,
-                      (size_t)(kGroupCounters + 1) * sizeof(int), st);
+  // the zero-state block (counters, tables) must be zero when the kernel starts, whatever an earlier call
+  // left behind
+  cudaError_t e = cudaMemsetAsync(scratch, 0, (size_t)kCounterBytes, st);
   if (e != cudaSuccess) return cuda_status(e, "decode_run_noalloc: cudaMemsetAsync");
   return launch_decode_tma(a, dtype, scratch, kStaticScratchBytes, st);
 }

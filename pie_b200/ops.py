@@ -135,6 +135,13 @@ def set_programmatic_dependent_launch(mode: int) -> None:
     check(lib.piekv_set_option(_lib.OPT_PDL, int(mode)), "set_option")
 
 
+def set_deterministic(on: bool) -> None:
+    """True: the tuned decode kernel keeps every SM to its own page range, so equal inputs give bit-identical
+    outputs; False (default): SMs that finish early take over work of slower ones (faster; the grouping of
+    the partial results, hence the last bits, may differ between launches).  See PIEKV_OPT_DETERMINISTIC."""
+    check(lib.piekv_set_option(_lib.OPT_DETERMINISTIC, 1 if on else 0), "set_option")
+
+
 def _check_pool(pool: torch.Tensor, name: str = "paged_kv_cache"):
     if isinstance(pool, (tuple, list)):
         raise ValueError(f"{name}: separate (k_cache, v_cache) tensors are not supported; pass the "
