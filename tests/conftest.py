@@ -21,3 +21,15 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def deterministic_decode():
+    """The tuned decode kernel with every SM kept to its own page range, so that two launches on equal inputs
+    can be compared bit for bit (by default idle SMs take over work of slower ones and the grouping of the
+    partial results varies from launch to launch)."""
+    from pie_b200 import ops
+
+    ops.set_deterministic(True)
+    yield
+    ops.set_deterministic(False)

@@ -95,8 +95,17 @@ def test_decode_against_oracle(dtype, hq, hkv, d, ctx):
     assert (lse.cpu() - ref_lse).abs().max().item() <= 2e-3
 
 
-def test_decode_many_short_requests_and_one_long():
+@pytest.mark.parametrize("deterministic", [True, False])
+def test_decode_many_short_requests_and_one_long(deterministic):
     # more requests than SMs, plus one request that is split across every CTA
+    ops.set_deterministic(deterministic)
+    try:
+        _many_short_and_one_long(deterministic)
+    finally:
+        ops.set_deterministic(False)
+
+
+def _many_short_and_one_long(deterministic):
     ctx = [1 + (i * 7) % 40 for i in range(300)] + [20000]
     sc = make_scenario(32, 8, 128, torch.bfloat16, [(c - 1, 1) for c in ctx], seed=3, scale=0.5)
     m = sc.meta
@@ -107,7 +116,11 @@ def test_decode_many_short_requests_and_one_long():
     # the arrival counters are back at zero, so the same workspace serves the next launch
     assert int(ws[: ops.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
     out2 = _run_decode(sc, ws)
-    assert torch.equal(out, out2)
+    if deterministic:
+        assert torch.equal(out, out2)
+    else:  # which SM took which pages may differ between the launches: rounding only
+        assert (out.float() - out2.float()).abs().max().item() <= 4e-3
+        assert (out2.cpu().float() - ref.float()).abs().max().item() <= 2e-2
 
 
 def test_decode_empty_request_and_nan_in_stale_rows():
@@ -381,7 +394,7 @@ def test_prefill_tensor_core_path_multi_tile(dtype, causal):
 
 
 @pytest.mark.parametrize("mode", [1, 2])
-def test_decode_with_programmatic_dependent_launch(mode):
+def test_decode_with_programmatic_dependent_launch(mode, deterministic_decode):
     """Back-to-back fused steps launched with the PDL attribute give the same pages and outputs."""
     from pie_b200 import workloads as W2
     hq, hkv, d = 32, 8, 128
@@ -440,12 +453,21 @@ def test_prefill_ignores_nan_in_stale_rows_and_unused_pages(hq, hkv, causal):
     assert (out.float() - ref.float()).abs().max().item() <= 2e-2
 
 
+@pytest.mark.parametrize("deterministic", [True, False])
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (8, 2), (16, 1)])   # 1, 4 and 8 page slots per stage
-@pytest.mark.parametrize("ctx", [[40000], [20000, 17, 30000, 3], [5000, 5000, 5000]])
-def test_decode_two_level_merge_of_long_requests(hq, hkv, ctx):
-    """Requests cut over more than 16 CTAs are merged in two levels (groups of 16 partials fold on
-    different SMs, the last group folds the groups); 17..148 segments per request are all exercised by
-    these lengths, and the counters must come back to zero."""
+@pytest.mark.parametrize("ctx", [[40000], [20000, 17, 30000, 3], [5000, 5000, 5000], [70000, 66000]])
+def test_decode_two_level_merge_of_long_requests(hq, hkv, ctx, deterministic):
+    """Requests spread over many chunks are merged in two levels (groups of chunk pieces fold on different
+    SMs, whoever completes the last group folds the groups), with and without work stealing between SMs;
+    two long requests side by side share chunk boundaries; the counters and tables must come back to zero."""
+    ops.set_deterministic(deterministic)
+    try:
+        _two_level(hq, hkv, ctx, deterministic)
+    finally:
+        ops.set_deterministic(False)
+
+
+def _two_level(hq, hkv, ctx, deterministic):
     sc = make_scenario(hq, hkv, 128, torch.bfloat16, [(c - 1, 1) for c in ctx], seed=9, scale=0.5)
     m = sc.meta
     ref, ref_lse = R.decode_attention(sc.q, sc.pool, m.kv_indptr, m.kv_indices, m.kv_last_page_len, return_lse=True)
@@ -456,4 +478,8 @@ def test_decode_two_level_merge_of_long_requests(hq, hkv, ctx):
     assert (lse.cpu() - ref_lse).abs().max().item() <= 2e-2
     assert int(ws[: ops.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
     out2, _ = _run_decode(sc, ws, return_lse=True)
-    assert torch.equal(out, out2)
+    if deterministic:
+        assert torch.equal(out, out2)
+    else:
+        assert (out.float() - out2.float()).abs().max().item() <= 4e-3
+    assert int(ws[: ops.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0

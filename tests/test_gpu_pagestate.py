@@ -138,7 +138,7 @@ def _beam_schedule(groups, beams, steps, every, seed):
     return plan
 
 
-def test_beam_search_on_device_page_tables_equals_the_host_run():
+def test_beam_search_on_device_page_tables_equals_the_host_run(deterministic_decode):
     """Config 4 at full size: 16 prefixes of 1024 tokens x 4 beams, 64 decode steps, top-2 of each group kept
     and forked every 8 steps."""
     groups, beams, prefix, steps, every = 16, 4, 1024, 64, 8
@@ -230,7 +230,7 @@ def test_beam_search_on_device_page_tables_equals_the_host_run():
     assert sum(len(v_[0]) for v_ in plan.values()) > 0 and pp.available() < P
 
 
-def test_device_page_tables_inside_a_cuda_graph():
+def test_device_page_tables_inside_a_cuda_graph(deterministic_decode):
     """One decode step - page-table advance, CSR gather and the fused attention launch - captured once and
     replayed: the page tables move on by themselves from replay to replay."""
     HQ, HKV, D, B, P = 32, 8, 128, 24, 2048

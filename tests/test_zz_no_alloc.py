@@ -49,7 +49,7 @@ def _run_both(sc, ws):
     return out_ws, out_na
 
 
-def test_noalloc_matches_workspace_entry_point_twice():
+def test_noalloc_matches_workspace_entry_point_twice(deterministic_decode):
     ws = torch.zeros(64 << 20, dtype=torch.uint8, device="cuda")
     first = make_scenario(32, 8, 128, torch.bfloat16, [(c - 1, 1) for c in (4000, 37, 1500, 16, 900, 5)], seed=41,
                           scale=0.5)
