@@ -43,7 +43,13 @@ constexpr int kDim = 128;
 constexpr int kPage = 16;
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumers = kConsumerWarps * 32;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
+// Three warpgroups: two of consumer warps, one that holds the producer warp (its other three warps leave at
+// once).  The third gives most of its registers to the consumers, whose accumulators (a [16 x 128] fp32 tile
+// per warp) plus the bookkeeping of the work partition do not fit the 168 registers a 384-thread CTA starts with.
+constexpr int kThreads = 384;
+constexpr int kRegsLaunch = 168, kRegsConsumer = 224, kRegsProducer = 56;
+static_assert(kConsumers * kRegsConsumer + 128 * kRegsProducer <= kThreads * kRegsLaunch, "register budget of the CTA");
+static_assert(kRegsConsumer % 8 == 0 && kRegsProducer % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr int kStages = 3;
 constexpr int kTileBytes = 8192;               // one (page, head): K 4 KiB + V 4 KiB
 constexpr int kStageBytes = 8 * kTileBytes;    // 64 KiB
@@ -385,7 +391,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // ---- chunk geometry, the same on every CTA
   const int total_pages = ip[B];
   const int stages_total = (total_pages + PG - 1) / PG;
-  const int cp = PG * max(1, (stages_total + kMaxChunks - 1) / kMaxChunks);  // pages per chunk
+  // pages per chunk: at most kMaxChunks chunks, and two stages or more once there is enough work, so that a
+  // chunk's first loads are in flight while the producer finds out what it will do next
+  const int cp = PG * max(stages_total >= 8 * G ? 2 : 1, (stages_total + kMaxChunks - 1) / kMaxChunks);
   const int n_chunks = (total_pages + cp - 1) / cp;
   const int my_lo = (int)((long long)c * n_chunks / G);
   const int my_hi = (int)((long long)(c + 1) * n_chunks / G);
@@ -401,7 +409,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   unsigned short *run_tab = reinterpret_cast<unsigned short *>(reinterpret_cast<uint8_t *>(p.counters) + kRunTabByte0);
   unsigned short *grp_tab = reinterpret_cast<unsigned short *>(reinterpret_cast<uint8_t *>(p.counters) + kGrpTabByte0);
 
-  if (warp == kConsumerWarps) {
+  if (warp >= kConsumerWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsProducer));
+    if (warp > kConsumerWarps) return;  // idle warps of the third warpgroup
     // ------------------------------------------------------------------ producer
     int armed = 0;  // stages armed so far
     bool ok = true;
@@ -506,8 +516,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       int nx_lo = 0, nx_hi = 0;
       bool have_next = false;
       for (int ck = cur_lo; ck < cur_hi && ok; ++ck) {
-        if (ck + 1 == cur_hi) have_next = next_interval(nx_lo, nx_hi);
-        const int next_ck = ck + 1 < cur_hi ? ck + 1 : (have_next ? nx_lo : -1);
+        // What follows this chunk decides whether the run goes on, which only the chunk's LAST stage has to
+        // say: the next interval is fetched (an atomic, perhaps a look at every CTA's range) when the rest
+        // of the chunk's loads are already in flight.
+        bool next_known = ck + 1 < cur_hi;
+        int next_ck = ck + 1;
         int g = ck * cp;
         const int chunk_end = min(total_pages, g + cp);
         while (g < chunk_end && ok) {
@@ -528,11 +541,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             run_pieces = 0;
           }
           ++run_pieces;
-          // does the run go on after this piece?
-          const bool goes_on = seg_end < req_end && next_ck == ck + 1 && !(two_level && (ck + 1 - c_first) % gsz == 0);
           const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
           const bool starts = run_pieces == 1;
           bool first_stage = true;
+          bool goes_on = false;
           while (g < seg_end) {
             const int npg = min(PG, seg_end - g);
             int page = lane < npg ? __ldg(a.kv_indices + g + shift + lane) : 0;
@@ -540,11 +552,21 @@ __global__ void __launch_bounds__(kThreads, 1)
               report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
               page = a.num_pages;  // outside the tensor map: the box is zero-filled
             }
+            const bool last_stage = g + npg >= seg_end;
+            if (last_stage && seg_end < req_end) {
+              // the piece ends with the chunk, not with the request: does the run go on?
+              if (!next_known) {
+                have_next = next_interval(nx_lo, nx_hi);
+                next_ck = have_next ? nx_lo : -1;
+                next_known = true;
+              }
+              goes_on = next_ck == ck + 1 && !(two_level && (ck + 1 - c_first) % gsz == 0);
+            }
             StageDesc d;
             d.g = g;
             d.b = b;
             d.npg = npg;
-            d.flags = ((starts && first_stage) ? kRunStart : 0) | ((g + npg >= seg_end && !goes_on) ? kRunEnd : 0);
+            d.flags = ((starts && first_stage) ? kRunStart : 0) | ((last_stage && !goes_on) ? kRunEnd : 0);
             d.first_chunk = run_first;
             d.pieces = run_pieces;
             if (!publish(d, page)) {
@@ -555,6 +577,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             g += npg;
           }
           if (!goes_on) run_open = false;
+        }
+        if (!next_known && ok) {  // the chunk ended with a request: still need to know what comes next
+          have_next = next_interval(nx_lo, nx_hi);
+          next_known = true;
         }
       }
       have = have_next;
@@ -583,6 +609,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 
   // -------------------------------------------------------------------- consumers
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsConsumer));
   const int tid = threadIdx.x;   // 0..255
   const int pslot = warp / HKV;  // page slot within a stage
   const int h = warp % HKV;      // kv head
@@ -616,16 +643,18 @@ __global__ void __launch_bounds__(kThreads, 1)
     consumer_bar_sync();
     if (tid == 0) {
       if (p.peer.n > 0) __threadfence_system();
-      const int old = atomicAdd(&ctl[1], 1);
-      if (old == G - 1) {
-        ctl[0] = 0;
-        ctl[1] = 0;  // ready for the next launch
-        for (int v = 0; v < G; ++v) steal_tab[v] = 0ull;
-        if (p.peer.n > 0) {
-          __threadfence_system();
-          for (int d = 0; d < p.peer.n; ++d)
-            asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(peer_step) : "memory");
-        }
+      sh_last = atomicAdd(&ctl[1], 1) == G - 1 ? 1 : 0;
+    }
+    consumer_bar_sync();
+    if (sh_last == 0) return;
+    for (int v = tid; v < G; v += kConsumers) steal_tab[v] = 0ull;
+    if (tid == 0) {
+      ctl[0] = 0;
+      ctl[1] = 0;  // ready for the next launch
+      if (p.peer.n > 0) {
+        __threadfence_system();
+        for (int d = 0; d < p.peer.n; ++d)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer.flag[d]), "r"(peer_step) : "memory");
       }
     }
   };
