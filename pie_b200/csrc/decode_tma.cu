@@ -443,28 +443,36 @@ __global__ void __launch_bounds__(kThreads, 1)
       return true;
     };
 
-    // ---- which chunks: the own range front to back, then the back of whoever has most left
+    // ---- which chunks: the own range front to back, then the back of whoever has most left.
+    // The first part of the own range is private (walked without any atomic, like a static split); the
+    // rest is shared: the owner claims it chunk by chunk with an atomic issued one chunk ahead (so that the
+    // answer is there when it is needed), others may take chunks from its back.
+    const int my_n = my_hi - my_lo;
+    const int priv = p.steal ? max(min(my_n, 1), my_n - max(2, my_n / 3)) : my_n;
     if (lane == 0) {
-      // the first chunk is taken without an atomic; the rest of the range is up for grabs
-      atomicExch(&steal_tab[c], steal_pack(min(my_lo + 1, my_hi), my_hi));
+      atomicExch(&steal_tab[c], steal_pack(my_lo + priv, my_hi));
       __threadfence();
     }
     __syncwarp();
-    int cur_lo = my_lo, cur_hi = min(my_lo + 1, my_hi);  // interval of chunks in hand
+    int cur_lo = my_lo, cur_hi = my_lo + priv;  // interval of chunks in hand
+    unsigned long long claim = 0;                // lane 0: answer of the claim in flight
+    bool claim_out = false;                      // a claim has been issued and not yet looked at
+    auto issue_claim = [&]() {
+      if (lane == 0) claim = atomicAdd(&steal_tab[c], 1ull);
+      claim_out = true;
+    };
     auto next_interval = [&](int &lo_out, int &hi_out) -> bool {
       unsigned long long got = 0;
       bool have = false;
-      if (lane == 0) {
-        const unsigned long long old = atomicAdd(&steal_tab[c], 1ull);
-        if (steal_lo(old) < steal_hi(old)) {
-          got = steal_pack(steal_lo(old), steal_lo(old) + 1);
-          have = true;
-        }
+      if (!claim_out) issue_claim();
+      claim_out = false;
+      if (lane == 0 && steal_lo(claim) < steal_hi(claim)) {
+        got = steal_pack(steal_lo(claim), steal_lo(claim) + 1);
+        have = true;
       }
       have = __shfl_sync(0xffffffffu, have ? 1 : 0, 0) != 0;
       if (!have && p.steal) {
-        // scratch slots are finite: every stolen interval is a run of its own
-        for (int attempt = 0; attempt < 8 && !have; ++attempt) {
+        for (int attempt = 0; attempt < 4 && !have; ++attempt) {
           int best = 0, who = -1;
           for (int v = lane; v < G; v += 32) {
             const unsigned long long w = __ldcg(&steal_tab[v]);
@@ -483,10 +491,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               who = ow;
             }
           }
-          if (best <= 0) break;
+          if (best < 2) break;  // a last chunk is finished sooner by its owner than taken over
+          int stop = 0;
           if (lane == 0) {
+            // scratch slots are finite and every stolen interval is a run of its own
             if (__ldcg(&ctl[0]) + 2 * G + B + 8 < p.num_slots) {
-              const int k = max(1, min(4, best / 2));
+              const int k = min(8, best / 2);
               const unsigned long long old = atomicAdd(&steal_tab[who], 0ull - ((unsigned long long)k << 32));
               const int lo_v = steal_lo(old), hi_v = steal_hi(old);
               if (lo_v < hi_v) {
@@ -494,11 +504,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 have = true;
               }
             } else {
-              best = -1;  // out of scratch slots: stop stealing
+              stop = 1;
             }
           }
           have = __shfl_sync(0xffffffffu, have ? 1 : 0, 0) != 0;
-          if (__shfl_sync(0xffffffffu, best, 0) < 0) break;
+          if (__shfl_sync(0xffffffffu, stop, 0)) break;
         }
       }
       got = __shfl_sync(0xffffffffu, got, 0);
@@ -509,6 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     // ---- walk the chunks in hand; a run continues while the next chunk is the next one of the same request
     bool have = cur_lo < cur_hi;
+    if (!have) have = next_interval(cur_lo, cur_hi);
     bool run_open = false;
     int run_first = 0, run_pieces = 0;
     while (have && ok) {
@@ -517,10 +528,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool have_next = false;
       for (int ck = cur_lo; ck < cur_hi && ok; ++ck) {
         // What follows this chunk decides whether the run goes on, which only the chunk's LAST stage has to
-        // say: the next interval is fetched (an atomic, perhaps a look at every CTA's range) when the rest
-        // of the chunk's loads are already in flight.
+        // say.  For the last chunk in hand the claim of the next one is issued now and looked at then.
         bool next_known = ck + 1 < cur_hi;
         int next_ck = ck + 1;
+        if (!next_known && !claim_out) issue_claim();
         int g = ck * cp;
         const int chunk_end = min(total_pages, g + cp);
         while (g < chunk_end && ok) {
@@ -545,9 +556,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           const bool starts = run_pieces == 1;
           bool first_stage = true;
           bool goes_on = false;
+          // the piece's page ids, 32 at a time in one coalesced load (lane l holds page id_base + l)
+          int id_base = g;
+          int ids = g + lane < seg_end ? __ldg(a.kv_indices + g + shift + lane) : 0;
           while (g < seg_end) {
             const int npg = min(PG, seg_end - g);
-            int page = lane < npg ? __ldg(a.kv_indices + g + shift + lane) : 0;
+            if (g + npg > id_base + 32) {
+              id_base = g;
+              ids = g + lane < seg_end ? __ldg(a.kv_indices + g + shift + lane) : 0;
+            }
+            int page = __shfl_sync(0xffffffffu, ids, (g - id_base + lane) & 31);
             if (lane < npg && (page < 0 || page >= a.num_pages)) {
               report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
               page = a.num_pages;  // outside the tensor map: the box is zero-filled
