@@ -277,7 +277,8 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
       L[u] = 0.f;
       acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    for (int pp = 0; pp < np; ++pp) {
+    // pass 1, lanes over the partials: every (partial, head) maximum is one independent load
+    for (int pp = lane; pp < np; pp += 32) {
       const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
@@ -288,7 +289,13 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
         }
       }
     }
-#pragma unroll 2
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+#pragma unroll
+      for (int o_ = 16; o_ > 0; o_ >>= 1) M[u] = fmaxf(M[u], __shfl_xor_sync(0xffffffffu, M[u], o_));
+    }
+    // pass 2, lanes over d: four partials (x four heads) of loads in flight at a time
+#pragma unroll 4
     for (int pp = 0; pp < np; ++pp) {
       const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
 #pragma unroll
@@ -449,11 +456,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // answer is there when it is needed), others may take chunks from its back.
     const int my_n = my_hi - my_lo;
     const int priv = p.steal ? max(min(my_n, 1), my_n - max(2, my_n / 3)) : my_n;
-    if (lane == 0) {
-      atomicExch(&steal_tab[c], steal_pack(my_lo + priv, my_hi));
-      __threadfence();
-    }
-    __syncwarp();
+    if (lane == 0) atomicExch(&steal_tab[c], steal_pack(my_lo + priv, my_hi));  // nothing else is published with it
     int cur_lo = my_lo, cur_hi = my_lo + priv;  // interval of chunks in hand
     unsigned long long claim = 0;                // lane 0: answer of the claim in flight
     bool claim_out = false;                      // a claim has been issued and not yet looked at
@@ -496,7 +499,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) {
             // scratch slots are finite and every stolen interval is a run of its own
             if (__ldcg(&ctl[0]) + 2 * G + B + 8 < p.num_slots) {
-              const int k = min(8, best / 2);
+              // small bites: everybody is about to finish, and what is taken here cannot be taken back
+              const int k = best >= 8 ? 2 : 1;
               const unsigned long long old = atomicAdd(&steal_tab[who], 0ull - ((unsigned long long)k << 32));
               const int lo_v = steal_lo(old), hi_v = steal_hi(old);
               if (lo_v < hi_v) {
@@ -667,6 +671,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (sh_last == 0) return;
     for (int v = tid; v < G; v += kConsumers) steal_tab[v] = 0ull;
     if (tid == 0) {
+#ifdef PIEKV_TRACE
+      g_trace[255 * 4] = (unsigned long long)ctl[0];  // scratch slots (= merged runs) this launch used
+#endif
       ctl[0] = 0;
       ctl[1] = 0;  // ready for the next launch
       if (p.peer.n > 0) {
