@@ -225,8 +225,7 @@ __device__ __forceinline__ int steal_hi(unsigned long long w) { return (int)(uns
 __device__ __noinline__ int collect_slots(unsigned short *tab, int first, int count, unsigned short *list,
                                           int *nlist, int *wsum) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (tid == 0) *nlist = 0;
-  consumer_bar_sync();
+  int done = 0;  // entries found so far (the same in every thread)
   for (int base = 0; base < count; base += kConsumers) {
     const int i = base + tid;
     unsigned short v = 0;
@@ -237,19 +236,20 @@ __device__ __noinline__ int collect_slots(unsigned short *tab, int first, int co
     const unsigned m = __ballot_sync(0xffffffffu, v != 0);
     if (lane == 0) wsum[warp] = __popc(m);
     consumer_bar_sync();
-    int off = *nlist;
-    for (int w = 0; w < warp; ++w) off += wsum[w];
+    int off = done, all = done;
+#pragma unroll
+    for (int w = 0; w < kConsumerWarps; ++w) {
+      const int n = wsum[w];
+      if (w < warp) off += n;
+      all += n;
+    }
     off += __popc(m & ((1u << lane) - 1u));
     if (v != 0 && off < kMergeList) list[off] = (unsigned short)(v - 1);
-    consumer_bar_sync();
-    if (tid == 0) {
-      int t = *nlist;
-      for (int w = 0; w < kConsumerWarps; ++w) t += wsum[w];
-      *nlist = t;
-    }
-    consumer_bar_sync();
+    done = all;
+    consumer_bar_sync();  // the list is complete (and wsum free) before anybody goes on
   }
-  return min(*nlist, kMergeList);
+  (void)nlist;
+  return min(done, kMergeList);
 }
 
 // Fold the partials of the slots in list[0 .. n) (`subs` sub-slots each): thread -> (query head
@@ -696,20 +696,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   }
 
-  // whoever completes a count sees everybody else's partials
-  auto arrive = [&](int *counter, int add, int expected) -> bool {
-    __threadfence();
+  // Publish this run (or folded group) and count it in.  Every thread's stores come before the barrier;
+  // thread 0 then writes the table entry, fences once (the fence covers what it has synchronised with) and
+  // adds to the counter.  Whoever completes a count sees everybody else's partials (read through L2).
+  auto arrive = [&](unsigned short *tab_entry, int slot_, int *counter, int add, int expected) -> bool {
     consumer_bar_sync();
     if (tid == 0) {
+      *tab_entry = (unsigned short)(slot_ + 1);
+      __threadfence();
       const int old = atomicAdd(counter, add);
       sh_last = (old + add == expected) ? 1 : 0;
-      if (sh_last) *counter = 0;  // ready for the next launch (nobody else touches it any more)
+      if (sh_last) {
+        *counter = 0;  // ready for the next launch (nobody else touches it any more)
+        __threadfence();
+      }
     }
     consumer_bar_sync();
-    const bool last = sh_last != 0;
-    consumer_bar_sync();  // everyone has read sh_last before it is rewritten
-    if (last) __threadfence();
-    return last;
+    return sh_last != 0;
   };
   auto collect = [&](unsigned short *tab, int first, int count) -> int {
     return collect_slots(tab, first, count, sh_list, &sh_nlist, sh_wsum);
@@ -722,6 +725,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   float o[16][4];
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   int b = 0, req_begin = 0, req_end = 0, last_len = kPage, rope_pos = 0, win_first = 0;
+  int my_slot = 0;  // thread 0: the open run's scratch slot
   bool aborted = false;
 
   for (int it = 0;; ++it) {
@@ -749,6 +753,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     if (flags & kRunStart) {
       // ================= open a run of request b
+      // (a scratch slot is asked for now so that its number is there when the run closes; a run that turns
+      // out to hold a whole request leaves its slot unused)
+      if (tid == 0) my_slot = atomicAdd(&ctl[0], 1);
       b = sh_desc[s].b;
       req_begin = ip[b];
       req_end = ip[b + 1];
@@ -1032,11 +1039,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       continue;
     }
-    // a scratch slot for this run
-    if (tid == 0) sh_slot = atomicAdd(&ctl[0], 1);
+    // the run's scratch slot
+    if (tid == 0) sh_slot = my_slot;
     consumer_bar_sync();
     const int slot = sh_slot;
-    consumer_bar_sync();
     if (slot >= p.num_slots) {
       if (tid == 0) report_error(a.err, PIEKV_ERR_PAGE_CAPACITY, KID_DECODE, c, slot);
       if (tid == 0) atomicExch(&sh_abort, 1);
@@ -1067,10 +1073,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     l0 = l1 = 0.f;
     const int tab_idx = run_first + b;  // unique per (chunk piece, request)
     if (nseg <= gsz) {
-      __threadfence();
-      consumer_bar_sync();
-      if (tid == 0) run_tab[tab_idx] = (unsigned short)(slot + 1);
-      if (!arrive(&req_cnt[b], run_pieces, nseg)) continue;
+      if (!arrive(&run_tab[tab_idx], slot, &req_cnt[b], run_pieces, nseg)) continue;
       const int n = collect(run_tab, c_first + b, nseg);
       merge_list(n, PG, b, -1);
       continue;
@@ -1083,18 +1086,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int g_first = c_first + gi * gsz;
     const int g_size = min(gsz, c_last + 1 - g_first);
     const int n_groups = (nseg + gsz - 1) / gsz;
-    __threadfence();
-    consumer_bar_sync();
-    if (tid == 0) run_tab[tab_idx] = (unsigned short)(slot + 1);
-    if (!arrive(&grp_cnt[g_first + b], run_pieces, g_size)) continue;
+    if (!arrive(&run_tab[tab_idx], slot, &grp_cnt[g_first + b], run_pieces, g_size)) continue;
     {
       const int n = collect(run_tab, g_first + b, g_size);
       merge_list(n, PG, b, slot);  // into sub-slot 0 of this run's own slot
     }
-    __threadfence();
-    consumer_bar_sync();
-    if (tid == 0) grp_tab[g_first + b] = (unsigned short)(slot + 1);
-    if (!arrive(&req_cnt[b], 1, n_groups)) continue;
+    if (!arrive(&grp_tab[g_first + b], slot, &req_cnt[b], 1, n_groups)) continue;
     {
       const int n = collect(grp_tab, c_first + b, nseg);
       merge_list(n, 1, b, -1);
