@@ -109,10 +109,10 @@ constexpr int kSmemBatch = 1024;  // kv_indptr is staged in shared memory up to 
 // Optional per-CTA time stamps (builds with -DPIEKV_TRACE only): kernel entry, first page consumed, last
 // page consumed, exit; read back with piekv_trace_read.
 #ifdef PIEKV_TRACE
-__device__ unsigned long long g_trace[256 * 4];
+__device__ unsigned long long g_trace[256 * 8];
 #define PIEKV_STAMP(slot)                                                               \
   do {                                                                                  \
-    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) g_trace[blockIdx.x * 4 + (slot)] = global_timer_ns(); \
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); \
   } while (0)
 #else
 #define PIEKV_STAMP(slot) \
@@ -349,6 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   extern __shared__ uint8_t smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStages];
   __shared__ __align__(8) uint64_t empty_bar[kStages];
+  __shared__ __align__(8) uint64_t desc_bar[kStages];  // the stage's record is written (its pages may still be in flight)
   __shared__ StageDesc sh_desc[kStages];
   __shared__ int sh_abort;
   __shared__ int sh_last;
@@ -387,6 +388,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], kConsumerWarps);
+      mbar_init(&desc_bar[s], 1);
     }
     sh_abort = 0;
     sh_last = 0;
@@ -442,6 +444,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (lane < d.npg) sh_desc[s].page[lane] = page_of_lane;
       __syncwarp();
+      // the record first: the consumers open a run (query loads, rotation) while the pages are in flight
+      if (lane == 0) mbar_arrive(&desc_bar[s]);
       if (lane == 0) mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(d.npg * HKV * kTileBytes));
       __syncwarp();
       if (lane < d.npg)
@@ -672,7 +676,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int v = tid; v < G; v += kConsumers) steal_tab[v] = 0ull;
     if (tid == 0) {
 #ifdef PIEKV_TRACE
-      g_trace[255 * 4] = (unsigned long long)ctl[0];  // scratch slots (= merged runs) this launch used
+      g_trace[255 * 8] = (unsigned long long)ctl[0];  // scratch slots (= merged runs) this launch used
 #endif
       ctl[0] = 0;
       ctl[1] = 0;  // ready for the next launch
@@ -732,18 +736,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int s = it % kStages;
     const uint32_t ph = (it / kStages) & 1;
     if (!aborted && *(volatile int *)&sh_abort) aborted = true;
-    if (!aborted && !mbar_wait(&full_bar[s], ph)) {
-      if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
+    if (!aborted && !mbar_wait(&desc_bar[s], ph)) {
+      if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 200 + s);
       if (lane == 0) atomicExch(&sh_abort, 1);
       aborted = true;
     }
     if (aborted) break;
     const int g = sh_desc[s].g;
-    if (g < 0) {
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&empty_bar[s]);
-      break;
-    }
+    if (g < 0) break;  // (the closing record is armed without pages; nobody waits for its slot)
     const int npg = sh_desc[s].npg;
     const int flags = sh_desc[s].flags;
     const int run_first = sh_desc[s].first_chunk;
@@ -839,6 +839,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ================= the stage's pages
+    if (!mbar_wait(&full_bar[s], ph)) {
+      if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
+      if (lane == 0) atomicExch(&sh_abort, 1);
+      aborted = true;
+      break;
+    }
     if (pslot < npg) {
       const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
       const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
@@ -1073,9 +1079,13 @@ __global__ void __launch_bounds__(kThreads, 1)
     l0 = l1 = 0.f;
     const int tab_idx = run_first + b;  // unique per (chunk piece, request)
     if (nseg <= gsz) {
+      PIEKV_STAMP(4);
       if (!arrive(&run_tab[tab_idx], slot, &req_cnt[b], run_pieces, nseg)) continue;
+      PIEKV_STAMP(5);
       const int n = collect(run_tab, c_first + b, nseg);
+      PIEKV_STAMP(6);
       merge_list(n, PG, b, -1);
+      PIEKV_STAMP(7);
       continue;
     }
     // A request spread over many chunks (one long context): merging 100+ partials in a single CTA would sit
@@ -1295,7 +1305,7 @@ int static_scratch_ptr(void **out) {
 
 #ifdef PIEKV_TRACE
 extern "C" int piekv_trace_read(unsigned long long *host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, piekv::g_trace, sizeof(unsigned long long) * 256 * 4);
+  return (int)cudaMemcpyFromSymbol(host_out, piekv::g_trace, sizeof(unsigned long long) * 256 * 8);
 }
 #endif
 
