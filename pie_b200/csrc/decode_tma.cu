@@ -109,13 +109,35 @@ constexpr int kSmemBatch = 1024;  // kv_indptr is staged in shared memory up to 
 // Optional per-CTA time stamps (builds with -DPIEKV_TRACE only): kernel entry, first page consumed, last
 // page consumed, exit; read back with piekv_trace_read.
 #ifdef PIEKV_TRACE
-__device__ unsigned long long g_trace[256 * 8];
+__device__ unsigned long long g_trace[256 * 16];
 #define PIEKV_STAMP(slot)                                                               \
   do {                                                                                  \
-    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) g_trace[blockIdx.x * 8 + (slot)] = global_timer_ns(); \
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) g_trace[blockIdx.x * 16 + (slot)] = global_timer_ns(); \
+  } while (0)
+#define PIEKV_ACC_BEGIN() const unsigned long long acc_t0__ = global_timer_ns()
+#define PIEKV_ACC_END(slot)                                                                              \
+  do {                                                                                                   \
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0) {                                            \
+      g_trace[blockIdx.x * 16 + (slot)] += global_timer_ns() - acc_t0__;                                 \
+      g_trace[blockIdx.x * 16 + (slot) + 1] += 1;                                                        \
+    }                                                                                                    \
+  } while (0)
+#define PIEKV_ACC_RESET()                                                                                \
+  do {                                                                                                   \
+    if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 0)                                              \
+      for (int z__ = 8; z__ < 16; ++z__) g_trace[blockIdx.x * 16 + z__] = 0;                             \
   } while (0)
 #else
 #define PIEKV_STAMP(slot) \
+  do {                    \
+  } while (0)
+#define PIEKV_ACC_BEGIN() \
+  do {                    \
+  } while (0)
+#define PIEKV_ACC_END(slot) \
+  do {                      \
+  } while (0)
+#define PIEKV_ACC_RESET() \
   do {                    \
   } while (0)
 #endif
@@ -253,8 +275,7 @@ __device__ __noinline__ int collect_slots(unsigned short *tab, int first, int co
 }
 
 // Fold the partials of the slots in list[0 .. n) (`subs` sub-slots each): thread -> (query head
-// tid/32 + 8k, 4 consecutive d).  Four heads at a time, two passes whose loads are independent of one
-// another and stay in flight together: first every head's maximum, then the weighted sums.  The result is
+// tid/32 + 8k, 4 consecutive d), four heads at a time.  The result is
 // the request's output row (normalised) or again a partial (maximum, sum, unnormalised accumulator)
 // written to sub-slot 0 of `to_slot`.
 template <typename T, int PG>
@@ -277,24 +298,9 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
       L[u] = 0.f;
       acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // pass 1, lanes over the partials: every (partial, head) maximum is one independent load
-    for (int pp = lane; pp < np; pp += 32) {
-      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int qh = q0 + u * kConsumerWarps;
-        if (qh < a.hq) {
-          const float2 ml = __ldcg(p.part_ml + base + qh);
-          M[u] = ml.y > 0.f ? fmaxf(M[u], ml.x) : M[u];
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-#pragma unroll
-      for (int o_ = 16; o_ > 0; o_ >>= 1) M[u] = fmaxf(M[u], __shfl_xor_sync(0xffffffffu, M[u], o_));
-    }
-    // pass 2, lanes over d: four partials (x four heads) of loads in flight at a time
+    // One pass with a running maximum: no load depends on another one's value, so four partials (x four
+    // heads) of loads are in flight together and a typical merge is a single trip to L2 - which, while the
+    // other SMs are still streaming, takes microseconds.
 #pragma unroll 4
     for (int pp = 0; pp < np; ++pp) {
       const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
@@ -304,12 +310,17 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
         if (qh < a.hq) {
           const float2 ml = __ldcg(p.part_ml + base + qh);
           const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
-          const float w = ml.y > 0.f ? fast_exp2(ml.x - M[u]) : 0.f;  // a warp that saw no page: weight 0
-          L[u] = fmaf(ml.y, w, L[u]);
-          acc[u].x = fmaf(po.x, w, acc[u].x);
-          acc[u].y = fmaf(po.y, w, acc[u].y);
-          acc[u].z = fmaf(po.z, w, acc[u].z);
-          acc[u].w = fmaf(po.w, w, acc[u].w);
+          if (ml.y > 0.f) {  // (a warp that saw no page contributes nothing)
+            const float mn = fmaxf(M[u], ml.x);
+            const float so = fast_exp2(M[u] - mn);  // M = -inf at first: 0
+            const float w = fast_exp2(ml.x - mn);
+            M[u] = mn;
+            L[u] = fmaf(L[u], so, ml.y * w);
+            acc[u].x = fmaf(acc[u].x, so, po.x * w);
+            acc[u].y = fmaf(acc[u].y, so, po.y * w);
+            acc[u].z = fmaf(acc[u].z, so, po.z * w);
+            acc[u].w = fmaf(acc[u].w, so, po.w * w);
+          }
         }
       }
     }
@@ -369,6 +380,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int c = blockIdx.x;
   const int G = gridDim.x;
   PIEKV_STAMP(0);
+  PIEKV_ACC_RESET();
   // Programmatic dependent launch: let the next kernel of the stream start its own prologue as SMs
   // free up, and do not touch anything an earlier kernel may still be producing before the wait.
   // Mode 2 is for callers whose page-table arrays are not written by the kernel just before this one
@@ -676,7 +688,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     for (int v = tid; v < G; v += kConsumers) steal_tab[v] = 0ull;
     if (tid == 0) {
 #ifdef PIEKV_TRACE
-      g_trace[255 * 8] = (unsigned long long)ctl[0];  // scratch slots (= merged runs) this launch used
+      g_trace[255 * 16] = (unsigned long long)ctl[0];  // scratch slots (= merged runs) this launch used
 #endif
       ctl[0] = 0;
       ctl[1] = 0;  // ready for the next launch
@@ -736,12 +748,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int s = it % kStages;
     const uint32_t ph = (it / kStages) & 1;
     if (!aborted && *(volatile int *)&sh_abort) aborted = true;
+    PIEKV_ACC_BEGIN();
     if (!aborted && !mbar_wait(&desc_bar[s], ph)) {
       if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 200 + s);
       if (lane == 0) atomicExch(&sh_abort, 1);
       aborted = true;
     }
     if (aborted) break;
+    PIEKV_ACC_END(8);
     const int g = sh_desc[s].g;
     if (g < 0) break;  // (the closing record is armed without pages; nobody waits for its slot)
     const int npg = sh_desc[s].npg;
@@ -839,6 +853,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ================= the stage's pages
+    PIEKV_ACC_END(10);  // (since the record wait began: record wait + run opening)
     if (!mbar_wait(&full_bar[s], ph)) {
       if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
       if (lane == 0) atomicExch(&sh_abort, 1);
@@ -1003,6 +1018,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
+    PIEKV_ACC_END(12);  // (since the record wait began: the whole stage)
     if (!(flags & kRunEnd)) continue;
 
     // ================= close the run: publish the result or the partial
@@ -1305,7 +1321,7 @@ int static_scratch_ptr(void **out) {
 
 #ifdef PIEKV_TRACE
 extern "C" int piekv_trace_read(unsigned long long *host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, piekv::g_trace, sizeof(unsigned long long) * 256 * 8);
+  return (int)cudaMemcpyFromSymbol(host_out, piekv::g_trace, sizeof(unsigned long long) * 256 * 16);
 }
 #endif
 
