@@ -221,6 +221,26 @@ __global__ void __launch_bounds__(1024) decode_window_kernel(const int32_t *__re
   if (threadIdx.x == 0) win_indptr[batch] = carry;
 }
 
+// Run header: what the consumers need to open a run (the request's query rows and, for the fused step,
+// its new k / v rows and RoPE position), brought into shared memory by the producer ahead of time with
+// bulk copies, so that opening a run costs no trip to global memory while the page pipeline drains.
+constexpr int kHdrQBytes = 8192;   // up to 32 query heads
+constexpr int kHdrKOff = kHdrQBytes, kHdrVOff = kHdrKOff + 2048, kHdrMetaOff = kHdrVOff + 2048;
+constexpr int kHdrBytes = kHdrMetaOff + 32;
+constexpr int kHdrSlots = 2;
+
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // What the producer tells the consumers about a stage (written before the stage's barrier is armed).
 struct StageDesc {
   int g;            // flat index of the stage's first page; -1: no more work
@@ -229,6 +249,8 @@ struct StageDesc {
   int flags;        // kRunStart | kRunEnd
   int first_chunk;  // chunk the run started in (meaningful with kRunEnd)
   int pieces;       // chunk pieces of the request the run covered (meaningful with kRunEnd)
+  int hdr;          // run header: slot | phase << 1, or -1 when the consumers load the rows themselves
+  int pad;
   int page[8];      // physical ids of the stage's pages
 };
 constexpr int kRunStart = 1, kRunEnd = 2;
@@ -298,28 +320,38 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
       L[u] = 0.f;
       acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    // One pass with a running maximum: no load depends on another one's value, so four partials (x four
-    // heads) of loads are in flight together and a typical merge is a single trip to L2 - which, while the
-    // other SMs are still streaming, takes microseconds.
-#pragma unroll 4
-    for (int pp = 0; pp < np; ++pp) {
-      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+    // One pass with a running maximum, four partials at a time: all of a batch's loads (x four heads) are
+    // issued before any value is used, so a typical merge is a single trip to L2 - which, while the other
+    // SMs are still streaming, takes microseconds.
+    for (int p0 = 0; p0 < np; p0 += 4) {
+      float2 ml[4][4];
+      float4 po[4][4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int qh = q0 + u * kConsumerWarps;
-        if (qh < a.hq) {
-          const float2 ml = __ldcg(p.part_ml + base + qh);
-          const float4 po = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
-          if (ml.y > 0.f) {  // (a warp that saw no page contributes nothing)
-            const float mn = fmaxf(M[u], ml.x);
+      for (int j = 0; j < 4; ++j) {
+        const int pp = min(p0 + j, np - 1);  // (a slot read twice at the end of the list gets weight 0)
+        const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int qh = min(q0 + u * kConsumerWarps, a.hq - 1);
+          ml[j][u] = __ldcg(p.part_ml + base + qh);
+          po[j][u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const bool live = p0 + j < np;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (live && ml[j][u].y > 0.f) {  // (a warp that saw no page contributes nothing)
+            const float mn = fmaxf(M[u], ml[j][u].x);
             const float so = fast_exp2(M[u] - mn);  // M = -inf at first: 0
-            const float w = fast_exp2(ml.x - mn);
+            const float w = fast_exp2(ml[j][u].x - mn);
             M[u] = mn;
-            L[u] = fmaf(L[u], so, ml.y * w);
-            acc[u].x = fmaf(acc[u].x, so, po.x * w);
-            acc[u].y = fmaf(acc[u].y, so, po.y * w);
-            acc[u].z = fmaf(acc[u].z, so, po.z * w);
-            acc[u].w = fmaf(acc[u].w, so, po.w * w);
+            L[u] = fmaf(L[u], so, ml[j][u].y * w);
+            acc[u].x = fmaf(acc[u].x, so, po[j][u].x * w);
+            acc[u].y = fmaf(acc[u].y, so, po[j][u].y * w);
+            acc[u].z = fmaf(acc[u].z, so, po[j][u].z * w);
+            acc[u].w = fmaf(acc[u].w, so, po[j][u].w * w);
           }
         }
       }
@@ -369,6 +401,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   __shared__ int sh_wsum[kConsumerWarps];
   __shared__ unsigned short sh_list[kMergeList];
   __shared__ int32_t sh_indptr[kSmemBatch + 1];
+  __shared__ __align__(8) uint64_t hdr_full[kHdrSlots];
+  __shared__ __align__(8) uint64_t hdr_empty[kHdrSlots];
+  __shared__ __align__(128) uint8_t sh_hdr[kHdrSlots][kHdrBytes];
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -402,6 +437,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_init(&empty_bar[s], kConsumerWarps);
       mbar_init(&desc_bar[s], 1);
     }
+    for (int s = 0; s < kHdrSlots; ++s) {
+      mbar_init(&hdr_full[s], FUSED ? 2 : 1);  // the bulk copies' arming arrival (+ the position's copy)
+      mbar_init(&hdr_empty[s], kConsumerWarps);
+    }
     sh_abort = 0;
     sh_last = 0;
     mbar_fence_init();
@@ -421,6 +460,14 @@ __global__ void __launch_bounds__(kThreads, 1)
   // chunk pieces per merge group of a long request: about what 16 CTAs own
   const int gsz = 16 * max(1, n_chunks / G);
   const int group = a.hq / HKV;
+
+  // Run headers need the rows contiguous and 16-byte aligned for bulk copies, and at most 32 query heads.
+  bool use_hdr = a.hq * kDim * (int)sizeof(T) <= kHdrQBytes && a.q_sh == kDim &&
+                 (reinterpret_cast<uintptr_t>(a.q) & 15) == 0 && ((a.q_sn * (int64_t)sizeof(T)) & 15) == 0;
+  if (FUSED)
+    use_hdr = use_hdr && f.k_sh == kDim && f.v_sh == kDim && (reinterpret_cast<uintptr_t>(f.k_new) & 15) == 0 &&
+              (reinterpret_cast<uintptr_t>(f.v_new) & 15) == 0 && ((f.k_sn * (int64_t)sizeof(T)) & 15) == 0 &&
+              ((f.v_sn * (int64_t)sizeof(T)) & 15) == 0 && f.pos_ids != nullptr;
 
   int *req_cnt = p.counters;
   int *ctl = p.counters + kCtlWord0;
@@ -453,6 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         sh_desc[s].flags = d.flags;
         sh_desc[s].first_chunk = d.first_chunk;
         sh_desc[s].pieces = d.pieces;
+        sh_desc[s].hdr = d.hdr;
       }
       if (lane < d.npg) sh_desc[s].page[lane] = page_of_lane;
       __syncwarp();
@@ -542,6 +590,34 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!have) have = next_interval(cur_lo, cur_hi);
     bool run_open = false;
     int run_first = 0, run_pieces = 0;
+    int hdr_n = 0, run_hdr = -1;  // headers started so far; the open run's header word
+    // bring request b_'s rows into the next header slot (asynchronously) and return its header word
+    auto start_header = [&](int b_) -> int {
+      if (!use_hdr) return -1;
+      const int hs = hdr_n % kHdrSlots;
+      const int hph = (hdr_n / kHdrSlots) & 1;
+      if (!mbar_wait(&hdr_empty[hs], hph ^ 1)) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 300 + hs);
+        if (lane == 0) atomicExch(&sh_abort, 1);
+        return -2;
+      }
+      if (lane == 0) {
+        const uint32_t dst = smem_u32(&sh_hdr[hs][0]);
+        const uint32_t qbytes = (uint32_t)(a.hq * kDim * sizeof(T));
+        const uint32_t kbytes = FUSED ? (uint32_t)(HKV * kDim * sizeof(T)) : 0u;
+        mbar_arrive_expect_tx(&hdr_full[hs], qbytes + 2 * kbytes);
+        bulk_copy_g2s(dst, reinterpret_cast<const T *>(a.q) + (size_t)b_ * a.q_sn, qbytes, &hdr_full[hs]);
+        if (FUSED) {
+          bulk_copy_g2s(dst + kHdrKOff, reinterpret_cast<const T *>(f.k_new) + (size_t)b_ * f.k_sn, kbytes, &hdr_full[hs]);
+          bulk_copy_g2s(dst + kHdrVOff, reinterpret_cast<const T *>(f.v_new) + (size_t)b_ * f.v_sn, kbytes, &hdr_full[hs]);
+          cp_async_4(dst + kHdrMetaOff, f.pos_ids + b_);
+          cp_async_arrive_noinc(&hdr_full[hs]);
+        }
+      }
+      __syncwarp();
+      ++hdr_n;
+      return hs | (hph << 1);
+    };
     while (have && ok) {
       int b = request_of_page(ip, B, cur_lo * cp);
       int nx_lo = 0, nx_hi = 0;
@@ -570,6 +646,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             run_open = true;
             run_first = ck;
             run_pieces = 0;
+            run_hdr = start_header(b);
+            if (run_hdr == -2) {
+              ok = false;
+              break;
+            }
           }
           ++run_pieces;
           const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
@@ -607,6 +688,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             d.flags = ((starts && first_stage) ? kRunStart : 0) | ((last_stage && !goes_on) ? kRunEnd : 0);
             d.first_chunk = run_first;
             d.pieces = run_pieces;
+            d.hdr = run_hdr;
             if (!publish(d, page)) {
               ok = false;
               break;
@@ -633,6 +715,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       d.flags = 0;
       d.first_chunk = 0;
       d.pieces = 0;
+      d.hdr = -1;
       publish(d, 0);
     }
     // Drain: do not let the CTA retire while a bulk copy may still be landing.
@@ -642,6 +725,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int it = first; it < armed; ++it) {
         mbar_wait(&full_bar[it % kStages], (it / kStages) & 1, 200000000ull);
       }
+      for (int hn = hdr_n > kHdrSlots ? hdr_n - kHdrSlots : 0; hn < hdr_n; ++hn)
+        mbar_wait(&hdr_full[hn % kHdrSlots], (hn / kHdrSlots) & 1, 200000000ull);
     }
     return;
   }
@@ -737,35 +822,47 @@ __global__ void __launch_bounds__(kThreads, 1)
     merge_slots<T, PG>(p, sh_list, n, subs, b_, to_slot, peer_step);
   };
 
-  uint32_t qa[8][4];
-  float o[16][4];
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   int b = 0, req_begin = 0, req_end = 0, last_len = kPage, rope_pos = 0, win_first = 0;
   int my_slot = 0;  // thread 0: the open run's scratch slot
-  bool aborted = false;
-
-  for (int it = 0;; ++it) {
-    const int s = it % kStages;
-    const uint32_t ph = (it / kStages) & 1;
-    if (!aborted && *(volatile int *)&sh_abort) aborted = true;
-    PIEKV_ACC_BEGIN();
-    if (!aborted && !mbar_wait(&desc_bar[s], ph)) {
+  int cur_hdr = -1; // the open run's header word (-1: rows are read from global memory)
+  bool aborted = false, finished = false;
+  int it = 0, s = 0, g = 0, npg = 0, flags = 0, run_first = 0, run_pieces = 0, my_page = -1;
+  uint32_t ph = 0;
+  // Wait for the record of stage `it` and read it: 1 a stage, 0 nothing follows, -1 given up.
+  auto fetch = [&]() -> int {
+    s = it % kStages;
+    ph = (it / kStages) & 1;
+    if (*(volatile int *)&sh_abort) return -1;
+    if (!mbar_wait(&desc_bar[s], ph)) {
       if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 200 + s);
       if (lane == 0) atomicExch(&sh_abort, 1);
-      aborted = true;
+      return -1;
     }
-    if (aborted) break;
-    PIEKV_ACC_END(8);
-    const int g = sh_desc[s].g;
-    if (g < 0) break;  // (the closing record is armed without pages; nobody waits for its slot)
-    const int npg = sh_desc[s].npg;
-    const int flags = sh_desc[s].flags;
-    const int run_first = sh_desc[s].first_chunk;
-    const int run_pieces = sh_desc[s].pieces;
-    const int my_page = pslot < npg ? sh_desc[s].page[pslot] : -1;
-    if (it == 0) PIEKV_STAMP(1);
+    g = sh_desc[s].g;
+    if (g < 0) return 0;  // (the closing record is armed without pages; nobody waits for its slot)
+    npg = sh_desc[s].npg;
+    flags = sh_desc[s].flags;
+    run_first = sh_desc[s].first_chunk;
+    run_pieces = sh_desc[s].pieces;
+    my_page = pslot < npg ? sh_desc[s].page[pslot] : -1;
+    return 1;
+  };
 
-    if (flags & kRunStart) {
+  // One iteration per run: the accumulators live inside it, so nothing of a finished run is kept (or saved
+  // around the merge calls) once its partial is written.
+  while (true) {
+    {
+      const int r = fetch();
+      if (r <= 0) {
+        aborted = r < 0;
+        break;
+      }
+    }
+    if (it == 0) PIEKV_STAMP(1);
+    uint32_t qa[8][4];
+    float o[16][4];
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    {
       // ================= open a run of request b
       // (a scratch slot is asked for now so that its number is there when the run closes; a run that turns
       // out to hold a whole request leaves its slot unused)
@@ -777,7 +874,29 @@ __global__ void __launch_bounds__(kThreads, 1)
       l0 = l1 = 0.f;
 #pragma unroll
       for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-      {
+      cur_hdr = sh_desc[s].hdr;
+      last_len = __ldg(a.kv_last_page_len + b);  // (used, and checked, at the request's last page)
+      win_first = windowed ? __ldg(&p.win_meta[b].y) : 0;
+      if (cur_hdr >= 0) {
+        // the rows are (or are about to be) in shared memory: no trip to global memory here
+        if (!mbar_wait(&hdr_full[cur_hdr & 1], (uint32_t)(cur_hdr >> 1))) {
+          if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, 310);
+          if (lane == 0) atomicExch(&sh_abort, 1);
+          aborted = true;
+          break;
+        }
+        const T *qb = reinterpret_cast<const T *>(&sh_hdr[cur_hdr & 1][0]) + (size_t)(h * group) * kDim;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const int col = ks * 16 + qlane * 2;
+          const uint32_t *r0 = reinterpret_cast<const uint32_t *>(qb + (size_t)quad * kDim + col);
+          const uint32_t *r1 = reinterpret_cast<const uint32_t *>(qb + (size_t)(quad + 8) * kDim + col);
+          qa[ks][0] = quad < group ? *r0 : 0u;
+          qa[ks][1] = quad + 8 < group ? *r1 : 0u;
+          qa[ks][2] = quad < group ? *(r0 + 4) : 0u;
+          qa[ks][3] = quad + 8 < group ? *(r1 + 4) : 0u;
+        }
+      } else {
         // query fragments of this head's group (rows beyond the group are zero)
         const T *qb = reinterpret_cast<const T *>(a.q) + (size_t)b * a.q_sn + (size_t)(h * group) * a.q_sh;
 #pragma unroll
@@ -791,14 +910,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           qa[ks][3] = quad + 8 < group ? __ldg(r1 + 4) : 0u;
         }
       }
-      last_len = a.kv_last_page_len[b];
-      if (last_len < 1 || last_len > kPage) {
-        if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
-        last_len = last_len < 1 ? 1 : kPage;
-      }
-      win_first = windowed ? __ldg(&p.win_meta[b].y) : 0;
       if (FUSED) {
-        rope_pos = f.pos_ids[b];
+        rope_pos = cur_hdr >= 0 ? *reinterpret_cast<const int *>(&sh_hdr[cur_hdr & 1][kHdrMetaOff]) : f.pos_ids[b];
         if (f.rope.mode == PIEKV_ROPE_TABLE && (rope_pos < 0 || rope_pos >= f.rope.table_len)) {
           if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
           rope_pos = 0;
@@ -852,8 +965,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
 
+    for (;;) {
     // ================= the stage's pages
-    PIEKV_ACC_END(10);  // (since the record wait began: record wait + run opening)
     if (!mbar_wait(&full_bar[s], ph)) {
       if (lane == 0) report_error(a.err, PIEKV_ERR_WAIT_TIMEOUT, KID_DECODE, c, s);
       if (lane == 0) atomicExch(&sh_abort, 1);
@@ -861,6 +974,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       break;
     }
     if (pslot < npg) {
+      if (g + pslot == req_end - 1 && (last_len < 1 || last_len > kPage)) {
+        if (lane == 0) report_error(a.err, PIEKV_ERR_LAST_PAGE_LEN, KID_DECODE, b, last_len);
+        last_len = last_len < 1 ? 1 : kPage;
+      }
       const int valid = (g + pslot == req_end - 1) ? last_len : kPage;
       const int tok_lo = (g + pslot == req_begin) ? win_first : 0;  // window start inside the first page
       const uint32_t page_base = stage0 + s * kStageBytes + pslot * (HKV * kTileBytes);
@@ -873,8 +990,10 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int last_phys = my_page;
         uint8_t *kp = stage0_ptr + s * kStageBytes + pslot * (HKV * kTileBytes) + h * 4096;
         uint8_t *vp = kp + HKV * 4096;
-        const T *ksrc = reinterpret_cast<const T *>(f.k_new) + (size_t)b * f.k_sn + (size_t)h * f.k_sh;
-        const T *vsrc = reinterpret_cast<const T *>(f.v_new) + (size_t)b * f.v_sn + (size_t)h * f.v_sh;
+        const T *ksrc = cur_hdr >= 0 ? reinterpret_cast<const T *>(&sh_hdr[cur_hdr & 1][kHdrKOff]) + h * kDim
+                                     : reinterpret_cast<const T *>(f.k_new) + (size_t)b * f.k_sn + (size_t)h * f.k_sh;
+        const T *vsrc = cur_hdr >= 0 ? reinterpret_cast<const T *>(&sh_hdr[cur_hdr & 1][kHdrVOff]) + h * kDim
+                                     : reinterpret_cast<const T *>(f.v_new) + (size_t)b * f.v_sn + (size_t)h * f.v_sh;
         const bool page_ok = last_phys >= 0 && last_phys < a.num_pages;
         T *pool = reinterpret_cast<T *>(const_cast<void *>(a.pool));
         T *kdst = pool + ((size_t)last_phys * 2 * kPage + row) * (HKV * kDim) + h * kDim;
@@ -1018,8 +1137,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(&empty_bar[s]);
-    PIEKV_ACC_END(12);  // (since the record wait began: the whole stage)
-    if (!(flags & kRunEnd)) continue;
+    ++it;
+    if (flags & kRunEnd) break;
+    {
+      const int r = fetch();
+      if (r <= 0) {  // (a run always ends with a stage that says so; this is the way out after a fault)
+        aborted = r < 0;
+        finished = r == 0;
+        break;
+      }
+    }
+    }  // stages of the run
+    if (aborted || finished) break;
+    if (cur_hdr >= 0 && lane == 0) mbar_arrive(&hdr_empty[cur_hdr & 1]);  // the run's rows are no longer needed
 
     // ================= close the run: publish the result or the partial
     PIEKV_STAMP(2);
@@ -1085,14 +1215,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
     }
-    // The run's registers are dead from here on (the next stage opens a new run); saying so keeps them from
-    // being saved around the merge calls below.
-#pragma unroll
-    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < 8; ++ks) qa[ks][0] = qa[ks][1] = qa[ks][2] = qa[ks][3] = 0u;
-    m0 = m1 = -INFINITY;
-    l0 = l1 = 0.f;
     const int tab_idx = run_first + b;  // unique per (chunk piece, request)
     if (nseg <= gsz) {
       PIEKV_STAMP(4);
