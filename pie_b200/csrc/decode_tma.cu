@@ -404,6 +404,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   __shared__ __align__(8) uint64_t hdr_full[kHdrSlots];
   __shared__ __align__(8) uint64_t hdr_empty[kHdrSlots];
   __shared__ __align__(128) uint8_t sh_hdr[kHdrSlots][kHdrBytes];
+  __shared__ float2 sh_cs[kDim / 2];  // fused step: (cos, sin) of the open run's position, one entry per pair
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -916,8 +917,16 @@ __global__ void __launch_bounds__(kThreads, 1)
           if (lane == 0) report_error(a.err, PIEKV_ERR_TABLE_RANGE, KID_DECODE, b, rope_pos);
           rope_pos = 0;
         }
-        // rotate the query fragments in registers (one rounding to T, as the in-place op does)
+        // rotate the query fragments in registers (one rounding to T, as the in-place op does); the 64
+        // (cos, sin) pairs of the position are evaluated once for the CTA, not once per warp and quad
         if (f.rope.mode != PIEKV_ROPE_NONE) {
+          consumer_bar_sync();  // nobody still reads the previous run's pairs
+          if (tid < kDim / 2) {
+            float cc, ss;
+            rope_cos_sin1(f.rope, rope_pos, tid, 64, cc, ss);
+            sh_cs[tid] = make_float2(cc, ss);
+          }
+          consumer_bar_sync();
           if (!f.rope.interleave) {
             // element d pairs with d + 64: fragments ks and ks + 4 of the same thread
 #pragma unroll
@@ -925,17 +934,15 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int hi8 = 0; hi8 < 2; ++hi8) {
                 const int i0 = ks * 16 + hi8 * 8 + qlane * 2;
-                float c0, s0, c1, s1;
-                rope_cos_sin1(f.rope, rope_pos, i0, 64, c0, s0);
-                rope_cos_sin1(f.rope, rope_pos, i0 + 1, 64, c1, s1);
+                const float2 cs0 = sh_cs[i0], cs1 = sh_cs[i0 + 1];
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                   const int j = hi8 * 2 + rr;
                   const float2 x = unpack2<T>(qa[ks][j]);
                   const float2 y = unpack2<T>(qa[ks + 4][j]);
                   float xa, ya, xb, yb;
-                  rope_rotate(x.x, y.x, c0, s0, xa, ya);
-                  rope_rotate(x.y, y.y, c1, s1, xb, yb);
+                  rope_rotate(x.x, y.x, cs0.x, cs0.y, xa, ya);
+                  rope_rotate(x.y, y.y, cs1.x, cs1.y, xb, yb);
                   qa[ks][j] = pack2<T>(xa, xb);
                   qa[ks + 4][j] = pack2<T>(ya, yb);
                 }
@@ -948,14 +955,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int hi8 = 0; hi8 < 2; ++hi8) {
                 const int pair = (ks * 16 + hi8 * 8 + qlane * 2) >> 1;
-                float c0, s0;
-                rope_cos_sin1(f.rope, rope_pos, pair, 64, c0, s0);
+                const float2 cs0 = sh_cs[pair];
 #pragma unroll
                 for (int rr = 0; rr < 2; ++rr) {
                   const int j = hi8 * 2 + rr;
                   const float2 x = unpack2<T>(qa[ks][j]);
                   float xa, ya;
-                  rope_rotate(x.x, x.y, c0, s0, xa, ya);
+                  rope_rotate(x.x, x.y, cs0.x, cs0.y, xa, ya);
                   qa[ks][j] = pack2<T>(xa, ya);
                 }
               }
@@ -1009,9 +1015,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
             const int i = lane + 32 * rr;
-            float cc, ss, xo, yo;
-            rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
-            rope_rotate(Elem<T>::to_f32(ksrc[i]), Elem<T>::to_f32(ksrc[i + 64]), cc, ss, xo, yo);
+            float xo, yo;
+            const float2 cs = sh_cs[i];
+            rope_rotate(Elem<T>::to_f32(ksrc[i]), Elem<T>::to_f32(ksrc[i + 64]), cs.x, cs.y, xo, yo);
             const T xt = Elem<T>::from_f32(xo), yt = Elem<T>::from_f32(yo);
             *reinterpret_cast<T *>(kp + tile_off(i)) = xt;
             *reinterpret_cast<T *>(kp + tile_off(i + 64)) = yt;
@@ -1024,9 +1030,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
           for (int rr = 0; rr < 2; ++rr) {
             const int i = lane + 32 * rr;  // pair (2i, 2i+1)
-            float cc, ss, xo, yo;
-            rope_cos_sin1(f.rope, rope_pos, i, 64, cc, ss);
-            rope_rotate(Elem<T>::to_f32(ksrc[2 * i]), Elem<T>::to_f32(ksrc[2 * i + 1]), cc, ss, xo, yo);
+            float xo, yo;
+            const float2 cs = sh_cs[i];
+            rope_rotate(Elem<T>::to_f32(ksrc[2 * i]), Elem<T>::to_f32(ksrc[2 * i + 1]), cs.x, cs.y, xo, yo);
             const uint32_t pk = pack2<T>(xo, yo);
             *reinterpret_cast<uint32_t *>(kp + tile_off(2 * i)) = pk;
             if (page_ok) *reinterpret_cast<uint32_t *>(kdst + 2 * i) = pk;
