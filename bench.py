@@ -1375,7 +1375,7 @@ def main():
                          "NCCL join stays eager)")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="decode70b on several GPUs: how the head-sharded outputs are joined")
-    ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2],
+    ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2, 3],
                     help="decode: programmatic dependent launch mode of the timed steps (see PIEKV_OPT_PDL)")
     ap.add_argument("--min-timed-ms", type=float, default=250.0,
                     help="decode: replay the captured graph of --steps steps until the timed region lasts this long")

@@ -89,14 +89,20 @@ const char *piekv_last_error_string(void);
  *   0 off (default); 1 on, the kernel waits for the previous kernel before reading anything;
  *   2 on, and the caller guarantees that kv_indptr is not written by the kernel immediately before
  *     (the reference uploads the page tables once per step ahead of the layer loop,
- *     pie/src/pie_worker/batching.py:196-239): the offsets are read before the wait.
+ *     pie/src/pie_worker/batching.py:196-239): the offsets are read before the wait;
+ *   3 as 2, and the caller also guarantees that the kernel immediately before wrote at most into the last
+ *     two pages of any request of this batch (true when it is the previous decode step of the same
+ *     requests, which appended one token each; false after a prefill, a refill or a page copy): the first
+ *     pages of every SM's share are then requested before the wait, so that the launch and its first
+ *     memory round trip hide behind the tail of the kernel before.
  * No reference counterpart. */
 #define PIEKV_OPT_PDL 0
-/* PIEKV_OPT_DETERMINISTIC: 0 (default) - the tuned decode kernel lets SMs that finish early take over
- * page ranges of slower ones, so how a request's pages are grouped before the partial results are merged
- * (and with it the last bits of the output) can differ from launch to launch; 1 - every SM keeps to its
- * own range and equal inputs give bit-identical outputs, at some cost in speed.  No reference counterpart. */
-#define PIEKV_OPT_DETERMINISTIC 1
+/* PIEKV_OPT_WORK_STEALING: 0 (default) - in the tuned decode kernel every SM keeps to its own page range
+ * and equal inputs give bit-identical outputs; 1 - SMs that finish early take over page ranges of slower
+ * ones, so how a request's pages are grouped before the partial results are merged (and with it the last
+ * bits of the output) can differ from launch to launch.  It pays when the per-SM work is very uneven in
+ * time; on the benchmark configurations it does not.  No reference counterpart. */
+#define PIEKV_OPT_WORK_STEALING 1
 int piekv_set_option(int32_t key, int32_t value);
 
 /* ---- metadata (device-resident) ------------------------------------------------- */

@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "libpiekv.so"
 PIEKV_F32, PIEKV_F16, PIEKV_BF16 = 0, 1, 2
 ROPE_NONE, ROPE_PLAIN, ROPE_LLAMA31, ROPE_TABLE = 0, 1, 2, 3
 OPT_PDL = 0
-OPT_DETERMINISTIC = 1
+OPT_WORK_STEALING = 1
 
 PIEKV_ERR_WAIT_TIMEOUT = 5
 STATUS_OUT_OF_PAGES = 8

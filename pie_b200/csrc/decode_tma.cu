@@ -2,11 +2,13 @@
 //
 // Work partition (on the device, no host plan).  The flat list of all requests' pages
 // (kv_indices[0 .. kv_indptr[B])) is cut into small equal CHUNKS (a few pages each, at most kMaxChunks of
-// them).  Every CTA (one per SM) owns a contiguous run of chunks and walks it front to back; a CTA that
-// runs out takes chunks from the BACK of the CTA with the most work left.  HBM bandwidth is not the same
-// for every SM of the two-die part (some finish an equal share 20 % later than others), so an equal
-// static split would let the slowest SM decide the launch time; with stealing all SMs stop streaming
-// within one chunk of each other.
+// them).  Every CTA (one per SM) owns a contiguous run of chunks and walks it front to back.  Optionally
+// (PIEKV_OPT_WORK_STEALING) a CTA that runs out takes chunks from the BACK of the CTA with the most work
+// left: HBM bandwidth is not the same for every SM of the two-die part (some finish an equal share 10 %
+// later than others), and with stealing all SMs stop streaming within a chunk of each other - but every
+// stolen piece is a run of its own with a partial to merge, and measured on config 2 the two effects
+// cancel (99.7 us either way), so the default is the static split, whose results are reproducible bit for
+// bit.
 //
 // A CTA accumulates a request's pages in registers for as long as the chunks it takes are consecutive:
 // such a RUN of chunk pieces ends at a request boundary, at the end of the CTA's chunks, or (long
@@ -83,7 +85,8 @@ struct DecodeParams {
   int *counters;    // the zero-state block
   int num_slots;    // scratch slots part_o / part_ml hold
   int steal;        // 0: every CTA keeps to its own chunks (results reproducible bit for bit)
-  int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets
+  int pdl;          // programmatic dependent launch: 0 off, 1 wait first, 2 wait after the page-table offsets,
+                    // 3 as 2 and the producer's first pages before the wait
   PeerOut peer;     // n == 0: results go to a.out only
   // Sliding window (a.window_left >= 0): the kernel streams only the pages that hold keys inside each
   // request's window.  win_indptr [B+1] is the prefix sum of those page counts (it takes kv_indptr's place
@@ -447,7 +450,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_fence_init();
   }
   __syncthreads();
-  if (p.pdl == 2) asm volatile("griddepcontrol.wait;" ::: "memory");
+  // Mode 3 adds to mode 2 the promise that the kernel just before wrote at most into the LAST TWO pages of any
+  // request (a decode step appends one token: the page it wrote is the next step's last or last but one):
+  // the producer warp then starts bringing in its first pages before it waits, everybody else waits here.
+  if (p.pdl == 2 || (p.pdl == 3 && warp != kConsumerWarps)) asm volatile("griddepcontrol.wait;" ::: "memory");
 
   // ---- chunk geometry, the same on every CTA
   const int total_pages = ip[B];
@@ -521,8 +527,47 @@ __global__ void __launch_bounds__(kThreads, 1)
     // answer is there when it is needed), others may take chunks from its back.
     const int my_n = my_hi - my_lo;
     const int priv = p.steal ? max(min(my_n, 1), my_n - max(2, my_n / 3)) : my_n;
-    if (lane == 0) atomicExch(&steal_tab[c], steal_pack(my_lo + priv, my_hi));  // nothing else is published with it
     int cur_lo = my_lo, cur_hi = my_lo + priv;  // interval of chunks in hand
+    // ---- mode 3: the first stages of the own range go out before the wait (never a piece's last stage, which
+    // may have to say that the run ends, and never one of a request's last two pages)
+    int resume_g = -1, resume_b = 0;
+    if (p.pdl == 3) {
+      if (cur_lo < cur_hi) {
+        const int b0 = request_of_page(ip, B, cur_lo * cp);
+        int g = cur_lo * cp;
+        const int seg_end = min(min(total_pages, g + cp), ip[b0 + 1]);
+        const int safe_end = ip[b0 + 1] - 2;
+        int n = 0;
+        while (n < kStages && g + min(PG, seg_end - g) < seg_end && g + min(PG, seg_end - g) <= safe_end) {
+          const int npg = min(PG, seg_end - g);
+          int page = lane < npg ? __ldg(a.kv_indices + g + lane) : 0;
+          if (lane < npg && (page < 0 || page >= a.num_pages)) {
+            report_error(a.err, PIEKV_ERR_PAGE_ID, KID_DECODE, g + lane, page);
+            page = a.num_pages;
+          }
+          StageDesc d;
+          d.g = g;
+          d.b = b0;
+          d.npg = npg;
+          d.flags = n == 0 ? kRunStart : 0;
+          d.first_chunk = cur_lo;
+          d.pieces = 1;
+          d.hdr = use_hdr ? 0 : -1;  // the first header is slot 0, phase 0; its copies follow the wait
+          if (!publish(d, page)) {
+            ok = false;
+            break;
+          }
+          g += npg;
+          ++n;
+        }
+        if (n > 0) {
+          resume_g = g;
+          resume_b = b0;
+        }
+      }
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+    }
+    if (lane == 0) atomicExch(&steal_tab[c], steal_pack(my_lo + priv, my_hi));  // nothing else is published with it
     unsigned long long claim = 0;                // lane 0: answer of the claim in flight
     bool claim_out = false;                      // a claim has been issued and not yet looked at
     auto issue_claim = [&]() {
@@ -619,6 +664,13 @@ __global__ void __launch_bounds__(kThreads, 1)
       ++hdr_n;
       return hs | (hph << 1);
     };
+    if (resume_g >= 0 && ok) {  // the run opened before the wait: its rows can be fetched now
+      run_open = true;
+      run_first = cur_lo;
+      run_pieces = 1;
+      run_hdr = start_header(resume_b);
+      if (run_hdr == -2) ok = false;
+    }
     while (have && ok) {
       int b = request_of_page(ip, B, cur_lo * cp);
       int nx_lo = 0, nx_hi = 0;
@@ -632,6 +684,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         int g = ck * cp;
         const int chunk_end = min(total_pages, g + cp);
         while (g < chunk_end && ok) {
+          const bool resumed = resume_g >= 0;  // (only the very first piece can be one begun before the wait)
+          if (resumed) g = resume_g;
+          resume_g = -1;
           while (b < B - 1 && ip[b + 1] <= g) ++b;
           const int req_begin = ip[b], req_end = ip[b + 1];
           const int seg_end = min(chunk_end, req_end);
@@ -653,10 +708,10 @@ __global__ void __launch_bounds__(kThreads, 1)
               break;
             }
           }
-          ++run_pieces;
+          if (!resumed) ++run_pieces;
           const int shift = windowed ? __ldg(&p.win_meta[b].x) : 0;
           const bool starts = run_pieces == 1;
-          bool first_stage = true;
+          bool first_stage = !resumed;
           bool goes_on = false;
           // the piece's page ids, 32 at a time in one coalesced load (lane l holds page id_base + l)
           int id_base = g;
@@ -1343,7 +1398,7 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
   p->a = a;
   p->peer = PeerOut{};
   p->pdl = get_option(PIEKV_OPT_PDL);
-  p->steal = get_option(PIEKV_OPT_DETERMINISTIC) ? 0 : 1;
+  p->steal = get_option(PIEKV_OPT_WORK_STEALING) ? 1 : 0;
   p->num_slots = (int)slots;
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p->counters = reinterpret_cast<int *>(ws);

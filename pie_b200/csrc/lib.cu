@@ -47,8 +47,8 @@ int get_option(int key) { return key >= 0 && key < 8 ? g_options[key] : 0; }
 
 extern "C" int piekv_set_option(int32_t key, int32_t value) {
   PIEKV_REQUIRE(key >= 0 && key < 8, "set_option: unknown key %d", key);
-  if (key == PIEKV_OPT_PDL) PIEKV_REQUIRE(value >= 0 && value <= 2, "set_option: PDL mode %d not in 0..2", value);
-  if (key == PIEKV_OPT_DETERMINISTIC) PIEKV_REQUIRE(value == 0 || value == 1, "set_option: deterministic must be 0 or 1");
+  if (key == PIEKV_OPT_PDL) PIEKV_REQUIRE(value >= 0 && value <= 3, "set_option: PDL mode %d not in 0..3", value);
+  if (key == PIEKV_OPT_WORK_STEALING) PIEKV_REQUIRE(value == 0 || value == 1, "set_option: work stealing must be 0 or 1");
   piekv::g_options[key] = value;
   return 0;
 }

@@ -131,15 +131,22 @@ def device_error(device=None, clear: bool = True) -> Optional[dict]:
 
 def set_programmatic_dependent_launch(mode: int) -> None:
     """0 off, 1 on, 2 on with the promise that the page-table arrays are not written by the kernel that
-    runs immediately before a decode call (see PIEKV_OPT_PDL in include/piekv.h)."""
+    runs immediately before a decode call, 3 with the further promise that that kernel wrote at most into
+    the last two pages of any request (the previous decode step of the same requests); see PIEKV_OPT_PDL in
+    include/piekv.h."""
     check(lib.piekv_set_option(_lib.OPT_PDL, int(mode)), "set_option")
 
 
+def set_work_stealing(on: bool) -> None:
+    """False (default): the tuned decode kernel keeps every SM to its own page range and equal inputs give
+    bit-identical outputs.  True: SMs that finish early take over work of slower ones; the grouping of the
+    partial results, hence the last bits, may then differ between launches.  See PIEKV_OPT_WORK_STEALING."""
+    check(lib.piekv_set_option(_lib.OPT_WORK_STEALING, 1 if on else 0), "set_option")
+
+
 def set_deterministic(on: bool) -> None:
-    """True: the tuned decode kernel keeps every SM to its own page range, so equal inputs give bit-identical
-    outputs; False (default): SMs that finish early take over work of slower ones (faster; the grouping of
-    the partial results, hence the last bits, may differ between launches).  See PIEKV_OPT_DETERMINISTIC."""
-    check(lib.piekv_set_option(_lib.OPT_DETERMINISTIC, 1 if on else 0), "set_option")
+    """`set_work_stealing(not on)`."""
+    set_work_stealing(not on)
 
 
 def _check_pool(pool: torch.Tensor, name: str = "paged_kv_cache"):

@@ -25,9 +25,8 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture
 def deterministic_decode():
-    """The tuned decode kernel with every SM kept to its own page range, so that two launches on equal inputs
-    can be compared bit for bit (by default idle SMs take over work of slower ones and the grouping of the
-    partial results varies from launch to launch)."""
+    """The tuned decode kernel with every SM kept to its own page range (the default), so that two launches on
+    equal inputs can be compared bit for bit; set explicitly in case an earlier test left work stealing on."""
     from pie_b200 import ops
 
     ops.set_deterministic(True)

@@ -393,25 +393,28 @@ def test_prefill_tensor_core_path_multi_tile(dtype, causal):
         assert (out2.float() - out.float()).abs().max().item() <= 1e-2
 
 
-@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("mode", [1, 2, 3])
 def test_decode_with_programmatic_dependent_launch(mode, deterministic_decode):
-    """Back-to-back fused steps launched with the PDL attribute give the same pages and outputs."""
+    """Back-to-back fused steps launched with the PDL attribute give the same pages and outputs (mode 3, whose
+    promise - the kernel before wrote only into the last two pages of a request - holds for consecutive
+    decode steps, lets every SM request its first pages before the previous step has finished)."""
     from pie_b200 import workloads as W2
     hq, hkv, d = 32, 8, 128
     results = {}
     for pdl in (0, mode):
         ops.set_programmatic_dependent_launch(pdl)
         try:
-            reqs = W2.PagedRequests(W2.seeded_perm(1024, 3))
-            for c in (15, 16, 1000, 1, 250, 3000, 77):
+            reqs = W2.PagedRequests(W2.seeded_perm(4096, 3))
+            ctxs = (15, 16, 1000, 1, 250, 3000, 77, 9000, 14, 12000, 31)  # page boundaries are crossed on the way
+            for c in ctxs:
                 reqs.add(c)
             metas = W2.decode_steps(reqs, 12)
-            pool = W2.randn((1024, 2, 16, hkv, d), 5, torch.bfloat16, 0.5).cuda()
+            pool = W2.randn((4096, 2, 16, hkv, d), 5, torch.bfloat16, 0.5).cuda()
             w = ops.BatchDecodeWithPagedKVCacheWrapper(_workspace(), "NHD")
             outs = []
-            q = W2.randn((7, hq, d), 100, torch.bfloat16, 0.5).cuda()
-            k = W2.randn((7, hkv, d), 200, torch.bfloat16, 0.5).cuda()
-            v = W2.randn((7, hkv, d), 300, torch.bfloat16, 0.5).cuda()
+            q = W2.randn((len(ctxs), hq, d), 100, torch.bfloat16, 0.5).cuda()
+            k = W2.randn((len(ctxs), hkv, d), 200, torch.bfloat16, 0.5).cuda()
+            v = W2.randn((len(ctxs), hkv, d), 300, torch.bfloat16, 0.5).cuda()
             tabs = [(dev(m.kv_indptr), dev(m.kv_indices), dev(m.kv_last_page_len), dev(m.pos_ids)) for m in metas]
             torch.cuda.synchronize()
             for indptr, indices, last, pos in tabs:  # launched back to back, no host sync in between
