@@ -215,7 +215,11 @@ def run_ours(args):
     launches = [0]
     es = 2
 
-    ops.set_programmatic_dependent_launch(args.pdl)  # page tables are static inputs here: prologue overlaps the tail
+    # Programmatic dependent launch: the page tables are static inputs, and the kernel before a step is the
+    # previous decode step of the same requests, which wrote one token per request - into what is now a
+    # request's last or last-but-one page (mode 3's promise; it also holds where the replayed graph wraps
+    # around to its first step, whose contexts are shorter).
+    ops.set_programmatic_dependent_launch(args.pdl)
 
     def qkv_views(t):
         q = t[:, : HQ * D].view(B, HQ, D)
@@ -1375,7 +1379,7 @@ def main():
                          "NCCL join stays eager)")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="decode70b on several GPUs: how the head-sharded outputs are joined")
-    ap.add_argument("--pdl", type=int, default=2, choices=[0, 1, 2, 3],
+    ap.add_argument("--pdl", type=int, default=3, choices=[0, 1, 2, 3],
                     help="decode: programmatic dependent launch mode of the timed steps (see PIEKV_OPT_PDL)")
     ap.add_argument("--min-timed-ms", type=float, default=250.0,
                     help="decode: replay the captured graph of --steps steps until the timed region lasts this long")
