@@ -299,91 +299,107 @@ __device__ __noinline__ int collect_slots(unsigned short *tab, int first, int co
   return min(done, kMergeList);
 }
 
-// Fold the partials of the slots in list[0 .. n) (`subs` sub-slots each): thread -> (query head
-// tid/32 + 8k, 4 consecutive d), four heads at a time.  The result is
-// the request's output row (normalised) or again a partial (maximum, sum, unnormalised accumulator)
-// written to sub-slot 0 of `to_slot`.
-template <typename T, int PG>
-__device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned short *list, int n, int subs, int b,
-                                         int to_slot, int peer_step) {
+// Fold the partials of the slots in list[0 .. n) (`subs` sub-slots each) for the HW query heads
+// q0, q0 + 8, ... of this warp; lanes own 4 consecutive d.  One pass with a running maximum, 16 / HW partials
+// at a time: all of a batch's loads are issued before any value is used, so a typical merge is a single trip
+// to L2 - which, while the other SMs are still streaming, takes microseconds.  The result is the request's
+// output row (normalised) or again a partial (maximum, sum, unnormalised accumulator) written to sub-slot 0
+// of `to_slot`.
+template <typename T, int PG, int HW>
+__device__ __forceinline__ void merge_heads(const DecodeParams &p, const unsigned short *list, int np, int subs, int b,
+                                            int to_slot, int peer_step, int q0) {
+  constexpr int PB = 16 / HW;  // partials per batch
   const AttnArgs &a = p.a;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
   const int d4 = lane * 4;
-  const int np = n * subs;
+  float M[HW], L[HW];
+  float4 acc[HW];
+#pragma unroll
+  for (int u = 0; u < HW; ++u) {
+    M[u] = -INFINITY;
+    L[u] = 0.f;
+    acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  for (int p0 = 0; p0 < np; p0 += PB) {
+    float2 ml[PB][HW];
+    float4 po[PB][HW];
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      const int pp = min(p0 + j, np - 1);  // (a slot read twice at the end of the list gets weight 0)
+      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+#pragma unroll
+      for (int u = 0; u < HW; ++u) {
+        const int qh = min(q0 + u * kConsumerWarps, a.hq - 1);
+        ml[j][u] = __ldcg(p.part_ml + base + qh);
+        po[j][u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+      const bool live = p0 + j < np;
+#pragma unroll
+      for (int u = 0; u < HW; ++u) {
+        if (live && ml[j][u].y > 0.f) {  // (a warp that saw no page contributes nothing)
+          const float mn = fmaxf(M[u], ml[j][u].x);
+          const float so = fast_exp2(M[u] - mn);  // M = -inf at first: 0
+          const float w = fast_exp2(ml[j][u].x - mn);
+          M[u] = mn;
+          L[u] = fmaf(L[u], so, ml[j][u].y * w);
+          acc[u].x = fmaf(acc[u].x, so, po[j][u].x * w);
+          acc[u].y = fmaf(acc[u].y, so, po[j][u].y * w);
+          acc[u].z = fmaf(acc[u].z, so, po[j][u].z * w);
+          acc[u].w = fmaf(acc[u].w, so, po[j][u].w * w);
+        }
+      }
+    }
+  }
   const int n_dst = p.peer.n > 0 ? p.peer.n : 1;
   const int row_heads = p.peer.n > 0 ? p.peer.row_heads : a.hq;
   const int head_off = p.peer.n > 0 ? p.peer.head_off : 0;
   const bool use_alt = p.peer.n > 0 && p.peer.step_ptr != nullptr && (peer_step & 1) == 0;
-  for (int q0 = warp; q0 < a.hq; q0 += 4 * kConsumerWarps) {
-    float M[4], L[4];
-    float4 acc[4];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      M[u] = -INFINITY;
-      L[u] = 0.f;
-      acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int u = 0; u < HW; ++u) {
+    const int qh = q0 + u * kConsumerWarps;
+    if (qh >= a.hq) continue;
+    if (to_slot >= 0) {
+      __syncwarp();  // every lane has read this head's partials before one of them is overwritten
+      const size_t idx = (size_t)to_slot * PG * a.hq + qh;
+      *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc[u];
+      if (lane == 0) p.part_ml[idx] = make_float2(M[u], L[u]);
+      continue;
     }
-    // One pass with a running maximum, four partials at a time: all of a batch's loads (x four heads) are
-    // issued before any value is used, so a typical merge is a single trip to L2 - which, while the other
-    // SMs are still streaming, takes microseconds.
-    for (int p0 = 0; p0 < np; p0 += 4) {
-      float2 ml[4][4];
-      float4 po[4][4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int pp = min(p0 + j, np - 1);  // (a slot read twice at the end of the list gets weight 0)
-        const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int qh = min(q0 + u * kConsumerWarps, a.hq - 1);
-          ml[j][u] = __ldcg(p.part_ml + base + qh);
-          po[j][u] = __ldcg(reinterpret_cast<const float4 *>(p.part_o + (base + qh) * kDim + d4));
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const bool live = p0 + j < np;
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (live && ml[j][u].y > 0.f) {  // (a warp that saw no page contributes nothing)
-            const float mn = fmaxf(M[u], ml[j][u].x);
-            const float so = fast_exp2(M[u] - mn);  // M = -inf at first: 0
-            const float w = fast_exp2(ml[j][u].x - mn);
-            M[u] = mn;
-            L[u] = fmaf(L[u], so, ml[j][u].y * w);
-            acc[u].x = fmaf(acc[u].x, so, po[j][u].x * w);
-            acc[u].y = fmaf(acc[u].y, so, po[j][u].y * w);
-            acc[u].z = fmaf(acc[u].z, so, po[j][u].z * w);
-            acc[u].w = fmaf(acc[u].w, so, po[j][u].w * w);
-          }
-        }
-      }
+    const float Ls = add_sink(L[u], M[u], a.sinks, qh);
+    const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+    uint2 pk;
+    pk.x = pack2<T>(acc[u].x * inv, acc[u].y * inv);
+    pk.y = pack2<T>(acc[u].z * inv, acc[u].w * inv);
+    for (int d = 0; d < n_dst; ++d) {
+      void *pb = a.out;
+      if (p.peer.n > 0) pb = use_alt ? p.peer.dst_alt[d] : p.peer.dst[d];
+      T *row = reinterpret_cast<T *>(pb) + ((size_t)b * row_heads + head_off + qh) * kDim;
+      *reinterpret_cast<uint2 *>(row + d4) = pk;
     }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int qh = q0 + u * kConsumerWarps;
-      if (qh >= a.hq) continue;
-      if (to_slot >= 0) {
-        __syncwarp();  // every lane has read this head's partials before one of them is overwritten
-        const size_t idx = (size_t)to_slot * PG * a.hq + qh;
-        *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc[u];
-        if (lane == 0) p.part_ml[idx] = make_float2(M[u], L[u]);
-        continue;
-      }
-      const float Ls = add_sink(L[u], M[u], a.sinks, qh);
-      const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
-      uint2 pk;
-      pk.x = pack2<T>(acc[u].x * inv, acc[u].y * inv);
-      pk.y = pack2<T>(acc[u].z * inv, acc[u].w * inv);
-      for (int d = 0; d < n_dst; ++d) {
-        void *pb = a.out;
-        if (p.peer.n > 0) pb = use_alt ? p.peer.dst_alt[d] : p.peer.dst[d];
-        T *row = reinterpret_cast<T *>(pb) + ((size_t)b * row_heads + head_off + qh) * kDim;
-        *reinterpret_cast<uint2 *>(row + d4) = pk;
-      }
-      if (a.lse != nullptr && lane == 0)
-        a.lse[(size_t)b * a.hq + qh] = Ls > 0.f ? (M[u] + log2f(Ls)) * 0.6931471805599453f : -INFINITY;
-    }
+    if (a.lse != nullptr && lane == 0)
+      a.lse[(size_t)b * a.hq + qh] = Ls > 0.f ? (M[u] + log2f(Ls)) * 0.6931471805599453f : -INFINITY;
+  }
+}
+
+// All consumer threads: warp w folds heads w, w + 8, ... (up to four at a time; with few heads per warp more
+// partials are in flight per batch instead).
+template <typename T, int PG>
+__device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned short *list, int n, int subs, int b,
+                                         int to_slot, int peer_step) {
+  const int warp = threadIdx.x >> 5;
+  const int np = n * subs;
+  const int hq = p.a.hq;
+  for (int q0 = warp; q0 < hq; q0 += 4 * kConsumerWarps) {
+    const int left = (hq - q0 + kConsumerWarps - 1) / kConsumerWarps;  // heads of this warp from q0 on
+    if (left >= 3)
+      merge_heads<T, PG, 4>(p, list, np, subs, b, to_slot, peer_step, q0);
+    else if (left == 2)
+      merge_heads<T, PG, 2>(p, list, np, subs, b, to_slot, peer_step, q0);
+    else
+      merge_heads<T, PG, 1>(p, list, np, subs, b, to_slot, peer_step, q0);
   }
 }
 
