@@ -1090,6 +1090,67 @@ def beam_leg():
         "device_error_word": ops.device_error(dev)}
 
 
+def run_copy(args):
+    """`--workload copy`: the page-copy kernel (copy-on-write of forked pages) and the RoPE + append kernel
+    alone, with CUDA events: achieved bytes/s (read + written) against the measured HBM copy bandwidth."""
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG2
+    HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    num_pages = 16384
+    peak, peak_kind = load_peaks()
+    pool = W.randn((num_pages, 2, 16, HKV, D), 500, cfg.dtype, 0.5, device=dev)
+    rows = []
+
+    def timed(fn, reps=50):
+        for _ in range(5):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps * 1e3
+
+    perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(9)).to(torch.int32)
+    for pairs, valid in ((32, 8), (32, 16), (512, 16), (4096, 16)):
+        src = perm[:pairs].to(dev)
+        dst = perm[num_pages // 2: num_pages // 2 + pairs].to(dev)
+        val = torch.full((pairs,), valid, dtype=torch.int32, device=dev)
+        us = timed(lambda: ops.copy_kv_pages(pool, src, dst, val))
+        nbytes = 2 * pairs * 2 * valid * HKV * D * 2
+        rows.append({"kernel": "copy_pages_kernel", "pairs": pairs, "valid_tokens": valid, "bytes": nbytes,
+                     "us": us, "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak})
+    # RoPE + append of a prefill-sized batch (config 3: 20480 tokens)
+    meta = W.config3_meta(num_pages=8192)
+    n = meta.nnz
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+    qkv = W.randn((n, (HQ + 2 * HKV) * D), 501, cfg.dtype, 0.5, device=dev)
+    q = qkv[:, : HQ * D].view(n, HQ, D)
+    k = qkv[:, HQ * D: (HQ + HKV) * D].view(n, HKV, D)
+    v = qkv[:, (HQ + HKV) * D:].view(n, HKV, D)
+    qo, indptr, indices, last, pos = t(meta.qo_indptr), t(meta.kv_indptr), t(meta.kv_indices), \
+        t(meta.kv_last_page_len), t(meta.pos_ids)
+    seq = ops.get_seq_lens(indptr, last, 16)
+    bi, kp = ops.get_batch_indices_positions(qo, seq, n)
+    rope = ops.RopeConfig()
+    us = timed(lambda: ops.rope_append_paged_kv_cache(q, k, v, pos, bi, kp, pool[:8192], indices, indptr, last, rope), 30)
+    nbytes = n * ((HQ + 2 * HKV) * D * 2 + HQ * D * 2 + 2 * HKV * D * 2)
+    rows.append({"kernel": "rope_append_tokens_kernel", "tokens": n, "bytes": nbytes, "us": us,
+                 "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak})
+    us = timed(lambda: ops.append_paged_kv_cache(k, v, bi, kp, pool[:8192], indices, indptr, last), 30)
+    nbytes = n * (2 * 2 * HKV * D * 2)
+    rows.append({"kernel": "rope_append_tokens_kernel (append only)", "tokens": n, "bytes": nbytes, "us": us,
+                 "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak})
+    print(json.dumps({"workload": "page copy and RoPE + append kernels alone, 32q/8kv heads, D128, bf16, page16",
+                      "peak_GBps": peak, "peak_source": peak_kind, "rows": rows,
+                      "device_error_word": ops.device_error(dev)}), flush=True)
+
+
 def run_beam(args):
     print(json.dumps(beam_leg()), flush=True)
 
@@ -1370,7 +1431,7 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
     ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
     ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam", "copy"],
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
@@ -1402,6 +1463,8 @@ def main():
         run_decode70b(args)
     elif args.workload == "beam":
         run_beam(args)
+    elif args.workload == "copy":
+        run_copy(args)
     else:
         run_ours(args)
 
