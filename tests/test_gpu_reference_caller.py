@@ -320,7 +320,7 @@ def test_reference_forward_pass_runs_on_this_library_eagerly_and_through_its_gra
     check_calls(reference.log.calls)  # the prefill step and the metadata calls still run eagerly
     # The prefill step runs eagerly in both engines.  For the decode steps the reference's captured graph leaves
     # its result in a tensor of the graph's own memory pool, and `_run_layers_graphed` hands back the static
-    # INPUT rows (llama3.py:389-402,954-956), so its hidden states say nothing about the operators.  The pools
+    # INPUT rows (llama3.py:396-411,956), so its hidden states say nothing about the operators.  The pools
     # do: the second layer's new K / V rows are computed, inside the graph, from the first layer's attention
     # output over the page tables of that step.
     assert torch.equal(eager_out[0].view(torch.int16), graph_out[0].view(torch.int16))
