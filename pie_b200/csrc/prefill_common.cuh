@@ -27,7 +27,7 @@ constexpr int kCounterBytes = 65536;
 constexpr int kSortBins = 1024;
 
 // Plan of one batch, built on the device into the workspace (after the counter area):
-//   header | tile_base[B+1] | poff[B+1] | moff[B+1] | tiles[max_tiles] | summary[max_tiles][sw] | packed mask
+//   header (word 0: tiles, words 2-3: items claimed / CTAs finished) | tile_base[B+1] | poff[B+1] | moff[B+1] | tiles[max_tiles] | summary[max_tiles][sw] | packed mask
 struct PlanView {
   int *ntiles;             // header word 0
   int32_t *tile_base;      // first q-tile index of every request (prefix of ceil(qo_len / 128))
@@ -45,6 +45,7 @@ struct PrefillParams {
   AttnArgs a;
   const int2 *tiles;
   const int *ntiles;
+  int *claim;              // [0] items handed out, [1] CTAs that ran out of items; zero between launches
   const int32_t *tile_base;
   const long long *poff;
   const uint32_t *summary;

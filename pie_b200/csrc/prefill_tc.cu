@@ -366,6 +366,8 @@ __global__ void prefill_plan_kernel(const int32_t *__restrict__ qo_indptr, const
       acc += c;
     }
     *ntiles = acc < max_tiles ? acc : max_tiles;
+    ntiles[2] = 0;  // items claimed and CTAs finished: the persistent kernel's counters, which every
+    ntiles[3] = 0;  // launch leaves at zero again
   }
   __syncthreads();
   for (int b = threadIdx.x; b < batch; b += blockDim.x) {
@@ -887,6 +889,7 @@ int launch_prefill_tc(const AttnArgs &a, int dtype, int64_t mask_bytes, void *wo
   PrefillParams p;
   p.a = a;
   p.ntiles = v.ntiles;
+  p.claim = v.ntiles + 2;
   p.tiles = v.tiles;
   p.tile_base = v.tile_base;
   p.poff = v.poff;
