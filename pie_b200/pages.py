@@ -224,6 +224,45 @@ class KvPageList:
         self.pool.release([removed])
         self._set_last(self.total_tokens)
 
+    def drop_masked_kv_pages(self, masked: Sequence[bool]) -> List[int]:
+        """Drop every FULL page all of whose tokens are masked (`masked[t]` true = token t is hidden from every
+        later query), newest first, and return the indices (positions in the page list) that were dropped, in
+        the order they were dropped - the caller removes the same token ranges from its token / position /
+        mask lists.  The last page is only a candidate when it is full.  The physical pages go back to the pool
+        (sdk/rust/inferlet/src/context.rs:298-345; used for attention-sink style windows)."""
+        if len(masked) < self.total_tokens:
+            raise ValueError(f"mask covers {len(masked)} tokens, the context holds {self.total_tokens}")
+        total = self.total_tokens
+        committed = total // self.page_size
+        flags = np.asarray(masked[: committed * self.page_size], dtype=bool).reshape(committed, self.page_size)
+        dropped: List[int] = []
+        for i in range(committed - 1, -1, -1):
+            if flags[i].all():
+                self.pool.release([self.pages.pop(i)])
+                dropped.append(i)
+        self._set_last(total - len(dropped) * self.page_size)
+        return dropped
+
+
+def eval_max_num_kv_pages(free_bytes: int, gpu_mem_utilization: float, page_size: int, num_kv_heads: int,
+                          head_dim: int, num_layers: int, dtype, tensor_parallel_size: int = 1,
+                          group=None, device=None) -> int:
+    """How many KV pages fit: `free_bytes * gpu_mem_utilization` over the bytes of one page across all layers,
+    with the KV heads split over the tensor-parallel ranks (pie/src/pie_worker/model/llama3.py:177-202).  With
+    a process group the free-memory figure is first reduced to the MINIMUM over its ranks, so every rank sizes
+    the same pool (pie/src/pie_worker/utils.py:108-119)."""
+    import torch
+
+    if group is not None or (torch.distributed.is_available() and torch.distributed.is_initialized()
+                             and tensor_parallel_size > 1):
+        t = torch.tensor(int(free_bytes), dtype=torch.int64, device=device if device is not None else "cpu")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN, group=group)
+        free_bytes = int(t.item())
+    es = torch.empty((), dtype=dtype).element_size()
+    local_kv_heads = num_kv_heads // tensor_parallel_size
+    per_page = es * 2 * page_size * local_kv_heads * head_dim * num_layers
+    return int((free_bytes * gpu_mem_utilization) // per_page)
+
 
 def build_csr(contexts: Sequence[KvPageList]) -> Tuple[np.ndarray, np.ndarray, np.ndarray]:
     """(kv_page_indices, kv_page_indptr, kv_last_page_lens) int32 of a batch of contexts."""

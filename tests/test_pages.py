@@ -2,6 +2,7 @@
 (sdk/javascript/__test__/kv-page-manager.ts and runtime/src/utils.rs IdPool semantics)."""
 import numpy as np
 import pytest
+import torch
 
 from pie_b200.pages import IdPool, KvPageList, PagePool, PoolExhausted, build_csr
 
@@ -194,3 +195,44 @@ def test_native_export_rejects_a_page_listed_twice():
     got, _ = m.alloc(3, 6)
     assert p not in got                           # and it is not handed out again
     m.close()
+
+
+def test_drop_masked_kv_pages_follows_the_context_rule():
+    """Full pages whose tokens are all masked go back to the pool, newest first; a partial last page stays
+    (sdk/rust/inferlet/src/context.rs:298-345)."""
+    pool = PagePool(16)
+    ctx = KvPageList(pool, 4)
+    ctx.grow(4 * 5 + 2)  # five full pages and a partial one
+    pages = list(ctx.pages)
+    masked = np.zeros(22, dtype=bool)
+    masked[4:12] = True    # pages 1 and 2 entirely
+    masked[12:15] = True   # page 3 all but one token
+    masked[20:22] = True   # the partial page, entirely - not a candidate
+    before = pool.available()
+    dropped = ctx.drop_masked_kv_pages(masked)
+    assert dropped == [2, 1]
+    assert ctx.pages == [pages[0], pages[3], pages[4], pages[5]]
+    assert ctx.total_tokens == 14 and ctx.last_page_len == 2
+    assert pool.available() == before + 2
+    # a context of full pages that loses its last page, then everything
+    full = KvPageList(pool, 4)
+    full.grow(8)
+    assert full.drop_masked_kv_pages([False] * 4 + [True] * 4) == [1]
+    assert full.total_tokens == 4 and full.last_page_len == 4
+    assert full.drop_masked_kv_pages([True] * 4) == [0]
+    assert full.total_tokens == 0 and full.last_page_len == 0 and full.pages == []
+    with pytest.raises(ValueError):
+        ctx.drop_masked_kv_pages([True] * 3)
+
+
+def test_pool_sizing_follows_the_reference_formula():
+    """pie/src/pie_worker/model/llama3.py:177-202: usable bytes over the bytes of a page across all layers, KV
+    heads divided over the tensor-parallel ranks."""
+    from pie_b200.pages import eval_max_num_kv_pages
+
+    free = 100 * 2 ** 30
+    per_page = 2 * 2 * 16 * 8 * 128 * 32  # bf16, K+V, 16 tokens, 8 kv heads, D 128, 32 layers
+    assert eval_max_num_kv_pages(free, 0.9, 16, 8, 128, 32, torch.bfloat16) == int(free * 0.9 // per_page)
+    assert eval_max_num_kv_pages(free, 0.9, 16, 8, 128, 32, torch.bfloat16, tensor_parallel_size=4) == \
+        int(free * 0.9 // (per_page // 4))
+    assert eval_max_num_kv_pages(free, 0.5, 16, 8, 128, 32, torch.float32) == int(free * 0.5 // (per_page * 2))

@@ -45,7 +45,13 @@ def _worker(rank, world, port, ret):
         counts = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
         dist.all_gather(counts, torch.tensor([len(mine)]))
         ok_cover = int(sum(c.item() for c in counts)) == m.batch
-        ret[rank] = (ok_tp, ok_dp, ok_cover)
+        # pool sizing: every rank ends with the pool that fits the rank with the least free memory
+        from pie_b200.pages import eval_max_num_kv_pages
+        free = (100 if rank == 0 else 60) * 2 ** 30
+        pages = eval_max_num_kv_pages(free, 0.9, 16, 8, 128, 32, torch.bfloat16, tensor_parallel_size=world,
+                                      group=dist.group.WORLD)
+        ok_pages = pages == int(60 * 2 ** 30 * 0.9 // (2 * 2 * 16 * (8 // world) * 128 * 32))
+        ret[rank] = (ok_tp, ok_dp, ok_cover and ok_pages)
     finally:
         dist.destroy_process_group()
 
