@@ -637,12 +637,13 @@ def prefill_subrecord(dev):
 # secondary workload: 70B-shaped decode with eviction churn, KV heads sharded over the ranks
 # ---------------------------------------------------------------------------------------------
 def decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=False, batch=256, num_pages=None,
-                  group_world=None):
+                  group_world=None, shard_of=1):
     """One timed leg of the 70B-shaped workload.  `world` ranks share the heads (world == 1: all heads on this
     GPU, no join).  Returns a dict of raw figures; every rank of the group must call it together when
     world > 1.  64 q / 8 kv heads, D128, bf16, `batch` requests with lognormal contexts; every 32 steps 20 % of
     the requests are evicted, their pages recycled and the slots refilled with 1024-token contexts written
-    through the RoPE + append kernel."""
+    through the RoPE + append kernel.  `shard_of` > 1 (one GPU only): the head counts one rank of that many
+    would hold, with no join - the per-GPU shape of the sharded step, for profiling."""
     import torch.distributed as dist
 
     from pie_b200 import ops, parallel
@@ -650,7 +651,7 @@ def decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=False, bat
 
     cfg = W.CONFIG5
     B, D = batch, cfg.head_dim
-    hq, hkv = cfg.num_qo_heads // world, cfg.num_kv_heads // world
+    hq, hkv = cfg.num_qo_heads // (world * shard_of), cfg.num_kv_heads // (world * shard_of)
     num_pages = num_pages or cfg.num_pages
     reqs = W.config5_requests(B, 5, num_pages)
 
@@ -857,8 +858,10 @@ def run_decode70b(args):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     B = args.requests if args.requests != 64 else 256
+    if args.shard_of > 1 and world > 1:
+        raise SystemExit("--shard-of emulates one rank's shape on ONE GPU")
     r = decode70b_leg(world, rank, dev, args.steps, args.warmup, join=args.join, graph=args.graph, batch=B,
-                      num_pages=args.pages if args.pages != 32768 else None)
+                      num_pages=args.pages if args.pages != 32768 else None, shard_of=args.shard_of)
     peak, peak_kind = load_peaks()
     achieved = r["kern_bytes"] / (r["kern_ms"] * 1e-3) / 1e9
     if rank == 0:
@@ -868,9 +871,11 @@ def run_decode70b(args):
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": "llama3-70b-shaped decode layer with eviction: 64q/8kv heads, D128, bf16, page16, "
                                    f"{B} requests, lognormal ctx, 20% evicted+refilled every 32 steps",
-                       "parallelism": f"KV heads sharded x{world} ({r['hkv']} kv / {r['hq']} q heads per GPU), " + (
+                       "parallelism": (f"the shape one of {args.shard_of} ranks holds, alone on one GPU, no join; "
+                                       if args.shard_of > 1 else "") +
+                                      f"KV heads sharded x{world * args.shard_of} ({r['hkv']} kv / {r['hq']} q heads per GPU), " + (
                            "outputs stored to every GPU by the decode kernel (NVLink peer stores + flags)"
-                           if r["peer"] else "NCCL all-gather of attention outputs"),
+                           if r["peer"] else ("no join" if world == 1 else "NCCL all-gather of attention outputs")),
                        "pool_pages": r["num_pages"],
                        "l2": "inputs larger than L2; no flush", "launch": r["launch_mode"]},
             "clocks": r["clocks"], "gpu_launches": r["launches"],
@@ -1438,6 +1443,8 @@ def main():
     ap.add_argument("--graph", action="store_true",
                     help="decode70b: capture all timed steps in one CUDA graph (peer-store join or one GPU; the "
                          "NCCL join stays eager)")
+    ap.add_argument("--shard-of", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="decode70b on one GPU: the head counts one of this many ranks would hold (profiling)")
     ap.add_argument("--join", default="peer", choices=["peer", "nccl"],
                     help="decode70b on several GPUs: how the head-sharded outputs are joined")
     ap.add_argument("--pdl", type=int, default=3, choices=[0, 1, 2, 3],

@@ -80,8 +80,9 @@ constexpr int kMergeList = 1024;               // runs (or groups) one merge can
 
 struct DecodeParams {
   AttnArgs a;
-  float *part_o;    // [slot][PG][Hq][128]
-  float2 *part_ml;  // [slot][PG][Hq]  (running max in log2 domain, running sum)
+  float *part_o;    // [slot][subs][Hq][128]
+  float2 *part_ml;  // [slot][subs][Hq]  (running max in log2 domain, running sum)
+  int subs;         // partials per slot: 1, or the pages per stage when the warps of a stage cannot fold theirs on chip
   int *counters;    // the zero-state block
   int num_slots;    // scratch slots part_o / part_ml hold
   int steal;        // 0: every CTA keeps to its own chunks (results reproducible bit for bit)
@@ -326,7 +327,7 @@ __device__ __forceinline__ void merge_heads(const DecodeParams &p, const unsigne
 #pragma unroll
     for (int j = 0; j < PB; ++j) {
       const int pp = min(p0 + j, np - 1);  // (a slot read twice at the end of the list gets weight 0)
-      const size_t base = ((size_t)list[pp / subs] * PG + pp % subs) * a.hq;
+      const size_t base = ((size_t)list[pp / subs] * p.subs + pp % subs) * a.hq;
 #pragma unroll
       for (int u = 0; u < HW; ++u) {
         const int qh = min(q0 + u * kConsumerWarps, a.hq - 1);
@@ -363,7 +364,7 @@ __device__ __forceinline__ void merge_heads(const DecodeParams &p, const unsigne
     if (qh >= a.hq) continue;
     if (to_slot >= 0) {
       __syncwarp();  // every lane has read this head's partials before one of them is overwritten
-      const size_t idx = (size_t)to_slot * PG * a.hq + qh;
+      const size_t idx = (size_t)to_slot * p.subs * a.hq + qh;
       *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d4) = acc[u];
       if (lane == 0) p.part_ml[idx] = make_float2(M[u], L[u]);
       continue;
@@ -483,6 +484,9 @@ __global__ void __launch_bounds__(kThreads, 1)
   // chunk pieces per merge group of a long request: about what 16 CTAs own
   const int gsz = 16 * max(1, n_chunks / G);
   const int group = a.hq / HKV;
+  // several pages per stage and a GQA group that fits a warp's own tile: the warps of a stage fold their
+  // partials through shared memory when a run ends (p.subs == 1), instead of each writing its own to scratch
+  const bool fold_on_chip = PG > 1 && group <= 8;
 
   // Run headers need the rows contiguous and 16-byte aligned for bulk copies, and at most 32 query heads.
   bool use_hdr = a.hq * kDim * (int)sizeof(T) <= kHdrQBytes && a.q_sh == kDim &&
@@ -1213,7 +1217,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&empty_bar[s]);
+    // (with several pages per stage the run's last stage is kept a little longer: its tiles carry the warps'
+    // partial results to each other, below)
+    if (lane == 0 && !(fold_on_chip && (flags & kRunEnd))) mbar_arrive(&empty_bar[s]);
     ++it;
     if (flags & kRunEnd) break;
     {
@@ -1238,7 +1244,76 @@ __global__ void __launch_bounds__(kThreads, 1)
     ls0 += __shfl_xor_sync(0xffffffffu, ls0, 2);
     ls1 += __shfl_xor_sync(0xffffffffu, ls1, 1);
     ls1 += __shfl_xor_sync(0xffffffffu, ls1, 2);
-    if (PG == 1 && run_pieces == nseg) {
+    int slot = -1;  // the run's scratch slot, if it needs one
+    if (fold_on_chip) {
+      // ---- several pages per stage: the warps of a stage hold partials of the same heads.  Each writes its
+      // rows (unnormalised accumulator, maximum, sum) over its own K / V tile of the run's last stage, which
+      // nobody else reads; then all threads fold them, four consecutive d of one head at a time, into the
+      // request's output rows or into ONE partial of the run.
+      const bool whole = run_pieces == nseg;
+      uint8_t *page0 = stage0_ptr + s * kStageBytes;  // page slot ps at + ps * HKV * kTileBytes: K tiles, then V tiles
+      if (quad < group) {
+        float2 *orow = reinterpret_cast<float2 *>(page0 + pslot * (HKV * kTileBytes) + h * 4096 + quad * 512);
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt) orow[nt * 4 + qlane] = make_float2(o[nt][0], o[nt][1]);
+        if (qlane == 0)
+          reinterpret_cast<float2 *>(page0 + pslot * (HKV * kTileBytes) + HKV * 4096 + h * 4096)[quad] =
+              make_float2(m0, ls0);
+      }
+      if (tid == 0) sh_slot = my_slot;
+      consumer_bar_sync();
+      slot = sh_slot;
+      if (!whole && slot >= p.num_slots) {
+        if (tid == 0) report_error(a.err, PIEKV_ERR_PAGE_CAPACITY, KID_DECODE, c, slot);
+        if (tid == 0) atomicExch(&sh_abort, 1);
+        aborted = true;
+        break;
+      }
+      for (int e = tid * 4; e < a.hq * kDim; e += kConsumers * 4) {
+        const int qh = e >> 7, d = e & (kDim - 1);
+        const int hh = qh / group, row = qh - hh * group;
+        float2 ml[PG];
+        float M = -INFINITY;
+#pragma unroll
+        for (int ps = 0; ps < PG; ++ps) {
+          ml[ps] = reinterpret_cast<const float2 *>(page0 + ps * (HKV * kTileBytes) + HKV * 4096 + hh * 4096)[row];
+          if (ml[ps].y > 0.f) M = fmaxf(M, ml[ps].x);  // (a warp that saw no page contributes nothing)
+        }
+        float L = 0.f;
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int ps = 0; ps < PG; ++ps) {
+          if (ml[ps].y > 0.f) {
+            const float w = fast_exp2(ml[ps].x - M);
+            const float4 v =
+                *reinterpret_cast<const float4 *>(page0 + ps * (HKV * kTileBytes) + hh * 4096 + row * 512 + d * 4);
+            L = fmaf(ml[ps].y, w, L);
+            acc.x = fmaf(v.x, w, acc.x);
+            acc.y = fmaf(v.y, w, acc.y);
+            acc.z = fmaf(v.z, w, acc.z);
+            acc.w = fmaf(v.w, w, acc.w);
+          }
+        }
+        if (whole) {
+          const float lsum = add_sink(L, M, a.sinks, qh);
+          const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+          uint2 pk;
+          pk.x = pack2<T>(acc.x * inv, acc.y * inv);
+          pk.y = pack2<T>(acc.z * inv, acc.w * inv);
+          for (int dd = 0; dd < n_dst; ++dd) *reinterpret_cast<uint2 *>(dst_row(dd, b, qh) + d) = pk;
+          if (a.lse != nullptr && d == 0)
+            a.lse[(size_t)b * a.hq + qh] = lsum > 0.f ? (M + log2f(lsum)) * 0.6931471805599453f : -INFINITY;
+        } else {
+          const size_t idx = (size_t)slot * a.hq + qh;  // one partial per slot
+          *reinterpret_cast<float4 *>(p.part_o + idx * kDim + d) = acc;
+          if (d == 0) p.part_ml[idx] = make_float2(M, L);
+        }
+      }
+      fence_proxy_async_smem();  // these tiles are next written by bulk copies
+      consumer_bar_sync();
+      if (lane == 0) mbar_arrive(&empty_bar[s]);
+      if (whole) continue;
+    } else if (PG == 1 && run_pieces == nseg) {
       // the whole request lived in this run: normalise and store
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -1268,18 +1343,18 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       continue;
     }
-    // the run's scratch slot
-    if (tid == 0) sh_slot = my_slot;
-    consumer_bar_sync();
-    const int slot = sh_slot;
-    if (slot >= p.num_slots) {
-      if (tid == 0) report_error(a.err, PIEKV_ERR_PAGE_CAPACITY, KID_DECODE, c, slot);
-      if (tid == 0) atomicExch(&sh_abort, 1);
-      aborted = true;
-      break;
-    }
-    {
-      const size_t pidx = (size_t)slot * PG + pslot;
+    if (!fold_on_chip) {
+      // the run's scratch slot
+      if (tid == 0) sh_slot = my_slot;
+      consumer_bar_sync();
+      slot = sh_slot;
+      if (slot >= p.num_slots) {
+        if (tid == 0) report_error(a.err, PIEKV_ERR_PAGE_CAPACITY, KID_DECODE, c, slot);
+        if (tid == 0) atomicExch(&sh_abort, 1);
+        aborted = true;
+        break;
+      }
+      const size_t pidx = (size_t)slot * p.subs + pslot;
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int row = quad + half * 8;
@@ -1299,7 +1374,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       PIEKV_STAMP(5);
       const int n = collect(run_tab, c_first + b, nseg);
       PIEKV_STAMP(6);
-      merge_list(n, PG, b, -1);
+      merge_list(n, p.subs, b, -1);
       PIEKV_STAMP(7);
       continue;
     }
@@ -1314,7 +1389,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!arrive(&run_tab[tab_idx], slot, &grp_cnt[g_first + b], run_pieces, g_size)) continue;
     {
       const int n = collect(run_tab, g_first + b, g_size);
-      merge_list(n, PG, b, slot);  // into sub-slot 0 of this run's own slot
+      merge_list(n, p.subs, b, slot);  // into sub-slot 0 of this run's own slot
     }
     if (!arrive(&grp_tab[g_first + b], slot, &req_cnt[b], 1, n_groups)) continue;
     {
@@ -1389,10 +1464,14 @@ bool decode_tma_supported(const AttnArgs &a, int dtype) {
 // over other CTAs' chunks freely (every stolen interval is a run of its own).
 static int64_t min_slots(int batch) { return 2ll * sm_count() + batch + 64; }
 static int64_t full_slots(int batch) { return 6ll * sm_count() + 2ll * batch + 64; }
-static int64_t slot_bytes(int hq, int hkv) {
+// Partials per scratch slot.  With several pages per stage (fewer than 8 kv heads) the warps of a stage each
+// hold a partial of the same heads; they fold them through shared memory when a run ends (a GQA group of up to
+// 8 rows fits a warp's own tile), otherwise every warp writes its own.
+static int sub_slots(int hq, int hkv) {
   const int pg = (hkv == 1 || hkv == 2 || hkv == 4 || hkv == 8) ? 8 / hkv : 1;
-  return (int64_t)pg * hq * (kDim * 4 + 8);
+  return (pg > 1 && hq / hkv <= 8) ? 1 : pg;
 }
+static int64_t slot_bytes(int hq, int hkv) { return (int64_t)sub_slots(hq, hkv) * hq * (kDim * 4 + 8); }
 static int64_t window_meta_bytes(int batch) { return (((int64_t)batch + 1) * 12 + 255) / 256 * 256; }
 
 int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
@@ -1401,7 +1480,7 @@ int64_t decode_tma_workspace_bytes(int batch, int hq, int hkv) {
 
 static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t workspace_bytes, DecodeParams *p,
                    CUtensorMap *tm, cudaStream_t st) {
-  const int pg = 8 / a.hkv;
+  const int pg = sub_slots(a.hq, a.hkv);
   const int64_t need = decode_tma_workspace_bytes(a.batch, a.hq, a.hkv);
   PIEKV_REQUIRE(workspace != nullptr && workspace_bytes >= need, "decode: workspace too small (%lld < %lld bytes)",
                 (long long)workspace_bytes, (long long)need);
@@ -1416,6 +1495,7 @@ static int prepare(const AttnArgs &a, int dtype, void *workspace, int64_t worksp
   p->pdl = get_option(PIEKV_OPT_PDL);
   p->steal = get_option(PIEKV_OPT_WORK_STEALING) ? 1 : 0;
   p->num_slots = (int)slots;
+  p->subs = pg;
   uint8_t *ws = reinterpret_cast<uint8_t *>(workspace);
   p->counters = reinterpret_cast<int *>(ws);
   p->part_ml = reinterpret_cast<float2 *>(ws + kCounterBytes);
