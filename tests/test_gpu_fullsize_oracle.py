@@ -161,7 +161,9 @@ def test_long_context_chunk_vs_oracle():
     assert (lse.cpu() - ref_lse).abs().max().item() <= TOL_LSE
 
 
-@pytest.mark.parametrize("shard", [1, 8])  # all heads on one GPU / the per-GPU shape of an 8-way KV-head split
+# all heads on one GPU / the per-GPU shapes of a 2-, 4- and 8-way KV-head split (several pages per stage: the
+# warps of a stage fold their partials on chip)
+@pytest.mark.parametrize("shard", [1, 2, 4, 8])
 def test_config5_full_batch_vs_oracle(shard):
     cfg = W.CONFIG5
     D, B = cfg.head_dim, 256
