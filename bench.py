@@ -1230,13 +1230,13 @@ class CpuPath:
         return nreq
 
 
-def cpu_baseline(sample_steps: int = 0, budget_s: float = 20.0):
+def cpu_baseline(sample_steps: int = 0, sample_s: float = 20.0):
     path = CpuPath()
     path.step(0)
     t0 = time.perf_counter()
     path.step(1)
     one = time.perf_counter() - t0
-    n = sample_steps or max(1, min(64, int(budget_s / max(one, 1e-3))))
+    n = sample_steps or max(1, min(64, int(sample_s / max(one, 1e-3))))
     t0 = time.perf_counter()
     tokens = 0
     for i in range(n):
@@ -1261,10 +1261,10 @@ def run_reference(args):
     path.step(1)
     one = time.perf_counter() - t0
     # bound the whole run to about two minutes: each step processes a sample of the 64 requests
-    budget = 120.0
+    limit_s = 120.0
     nreq = 64
-    if one * (steps + warmup) > budget:
-        nreq = max(1, min(64, int(64 * budget / (one * (steps + warmup)))))
+    if one * (steps + warmup) > limit_s:
+        nreq = max(1, min(64, int(64 * limit_s / (one * (steps + warmup)))))
     for i in range(min(warmup, 3)):
         path.step(i, nreq)
     t0 = time.perf_counter()

@@ -50,7 +50,7 @@ constexpr int kConsumers = kConsumerWarps * 32;
 // per warp) plus the bookkeeping of the work partition do not fit the 168 registers a 384-thread CTA starts with.
 constexpr int kThreads = 384;
 constexpr int kRegsLaunch = 168, kRegsConsumer = 224, kRegsProducer = 56;
-static_assert(kConsumers * kRegsConsumer + 128 * kRegsProducer <= kThreads * kRegsLaunch, "register budget of the CTA");
+static_assert(kConsumers * kRegsConsumer + 128 * kRegsProducer <= kThreads * kRegsLaunch, "registers the CTA owns");
 static_assert(kRegsConsumer % 8 == 0 && kRegsProducer % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr int kStages = 3;
 constexpr int kTileBytes = 8192;               // one (page, head): K 4 KiB + V 4 KiB

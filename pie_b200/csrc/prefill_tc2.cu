@@ -59,7 +59,7 @@ constexpr int k2Threads = 384;
 constexpr int k2RegsLaunch = 168;  // what __launch_bounds__(384, 1) gives every thread at launch
 constexpr int k2RegsSoftmax = 200, k2RegsOther = 96;
 // setmaxnreg.inc waits until the registers exist: the CTA owns 384 * 168 and not one more
-static_assert(256 * k2RegsSoftmax + 128 * k2RegsOther <= k2Threads * k2RegsLaunch, "register budget of the CTA");
+static_assert(256 * k2RegsSoftmax + 128 * k2RegsOther <= k2Threads * k2RegsLaunch, "registers the CTA owns");
 static_assert(k2RegsSoftmax % 8 == 0 && k2RegsOther % 8 == 0, "setmaxnreg takes multiples of 8");
 constexpr int k2ColS = 0;    // + 128 * head
 constexpr int k2ColO = 256;  // + 128 * head
