@@ -381,6 +381,51 @@ def run_ours(args):
     barrier()
     e2e_ms = max_over_ranks(c0.elapsed_time(c1))
     e2e_value = n_gpus * B * e2e_steps / (e2e_ms * 1e-3)
+    e2e_eager_value, e2e_mode = e2e_value, "eager launches from Python"
+    # The same pipeline captured once as a CUDA graph (copy, kernel and copy nodes of 128 steps on three
+    # streams) and replayed: no Python or launch latency between the steps, and consecutive kernels are
+    # adjacent nodes again, so the promise behind the launch-overlap mode holds as in the headline (the kernel
+    # before a step wrote at most the requests' last pages; page tables and q / k / v arrive by copy nodes the
+    # kernel depends on in full).
+    try:
+        g_steps = min(e2e_steps, 128)
+        g_replays = max(1, -(-e2e_steps // g_steps))
+        ops.set_programmatic_dependent_launch(args.pdl)
+        torch.cuda.synchronize(dev)
+        issued[0] = 0
+        g_e2e = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_e2e, stream=s_comp):
+            fork = torch.cuda.Event()
+            fork.record(s_comp)
+            s_in.wait_event(fork)
+            s_out.wait_event(fork)
+            for i in range(g_steps):
+                step_e2e(warmup + i)
+            j_in, j_out = torch.cuda.Event(), torch.cuda.Event()
+            j_in.record(s_in)
+            j_out.record(s_out)
+            s_comp.wait_event(j_in)
+            s_comp.wait_event(j_out)
+        with torch.cuda.stream(s_comp):
+            g_e2e.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(s_comp):
+            g0.record(s_comp)
+            for _ in range(g_replays):
+                g_e2e.replay()
+            g1.record(s_comp)
+        barrier()
+        g_ms = max_over_ranks(g0.elapsed_time(g1))
+        g_value = n_gpus * B * g_steps * g_replays / (g_ms * 1e-3)
+        if ops.device_error(dev, clear=False) is None and g_value > e2e_value:
+            e2e_value, e2e_ms, e2e_steps = g_value, g_ms, g_steps * g_replays
+            e2e_mode = f"CUDA graph of {g_steps} pipelined steps replayed {g_replays}x"
+        del g_e2e
+    except Exception as e:  # the eager figure stands
+        e2e_mode = f"eager launches from Python (graph capture failed: {type(e).__name__})"
+        torch.cuda.synchronize(dev)
+    ops.set_programmatic_dependent_launch(0)
 
     # latency form: one buffer set, one stream, the host waits for the output before it issues the next step
     lat_steps = min(64, max(8, steps))
@@ -444,9 +489,11 @@ def run_ours(args):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps, "ms_per_step": e2e_ms / e2e_steps,
                     "latency_us_per_step": lat_us, "latency_steps": lat_steps,
+                    "launch": e2e_mode, "eager_value": e2e_eager_value,
                     "how": "pie_b200.ops wrappers; per step H2D of q/k/v + page tables from pinned memory and D2H of the "
                            "output. `value`: INDEPENDENT steps pipelined over upload / compute / download streams with "
-                           "3 buffer sets (throughput). `latency_us_per_step`: one buffer set, upload -> fused step -> "
+                           "3 buffer sets (throughput), as eager launches (`eager_value`) and as one captured CUDA graph of the "
+                           "same calls (`launch` says which the value is). `latency_us_per_step`: one buffer set, upload -> fused step -> "
                            "download, host synchronised after every step (what a dependent decode loop pays)"},
             "gpu_launches": timed_launches,
             "roofline": {"bound": "hbm",
