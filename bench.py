@@ -66,6 +66,15 @@ def load_peaks():
         return 6650.0, "fallback"
 
 
+def load_peaks_tensor():
+    """(sustained bf16 matmul TFLOP/s, where it came from)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops_sustained"]), "measured (sustained bf16 matmul)"
+    except Exception:
+        return 1400.0, "fallback"
+
+
 class ClockSampler:
     """Polls SM clock and throttle reasons through NVML while the timed region runs."""
 
@@ -1142,6 +1151,70 @@ def beam_leg():
         "device_error_word": ops.device_error(dev)}
 
 
+def run_qkv(args):
+    """`--workload qkv`: the QKV projection of the prefill mix (config 3's 20480 tokens, hidden 4096, 32q/8kv
+    heads) with RoPE + append, as the library GEMM followed by `rope_append_paged_kv_cache` and as the one fused
+    tcgen05 kernel (`qkv_rope_append_paged_kv_cache`); plus a decode-sized batch."""
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    cfg = W.CONFIG2
+    HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
+    hidden = 4096
+    peak_tf = load_peaks_tensor()[0]
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)
+    rows = []
+
+    def timed(fn, reps):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / reps
+
+    w = W.randn(((HQ + 2 * HKV) * D, hidden), 601, cfg.dtype, hidden ** -0.5, device=dev)
+    rope = ops.RopeConfig()
+    for label, meta, reps in (("prefill mix, 20480 tokens", W.config3_meta(num_pages=8192), 20),
+                              ("decode batch, 64 tokens", W.decode_steps(W.config2_requests(), 1)[0], 50)):
+        n = meta.nnz if hasattr(meta, "nnz") else meta.batch
+        pool = W.randn((32768 if n == 64 else 8192, 2, 16, HKV, D), 600, cfg.dtype, 0.5, device=dev)
+        x = W.randn((n, hidden), 602, cfg.dtype, 1.0, device=dev)
+        qo, indptr, indices, last, pos = t(meta.qo_indptr), t(meta.kv_indptr), t(meta.kv_indices), \
+            t(meta.kv_last_page_len), t(meta.pos_ids)
+        seq = ops.get_seq_lens(indptr, last, 16)
+        bi, kp = ops.get_batch_indices_positions(qo, seq, n)
+
+        def separate():
+            qkv = torch.nn.functional.linear(x, w)
+            q = qkv[:, : HQ * D].view(n, HQ, D)
+            k = qkv[:, HQ * D: (HQ + HKV) * D].view(n, HKV, D)
+            v = qkv[:, (HQ + HKV) * D:].view(n, HKV, D)
+            ops.rope_append_paged_kv_cache(q, k, v, pos, bi, kp, pool, indices, indptr, last, rope)
+
+        q_out = torch.empty((n, HQ, D), dtype=cfg.dtype, device=dev)
+
+        def fused():
+            ops.qkv_rope_append_paged_kv_cache(x, w, pos, bi, kp, pool, indices, indptr, HQ, HKV, rope=rope, q_out=q_out)
+
+        gemm_only = timed(lambda: torch.nn.functional.linear(x, w), reps)
+        sep = timed(separate, reps)
+        fus = timed(fused, reps)
+        flops = 2.0 * n * hidden * (HQ + 2 * HKV) * D
+        rows.append({"case": label, "tokens": n, "flop": flops,
+                     "library_gemm_ms": gemm_only, "library_gemm_plus_rope_append_ms": sep, "fused_ms": fus,
+                     "fused_tflops": flops / fus / 1e9, "library_gemm_tflops": flops / gemm_only / 1e9,
+                     "fused_frac_of_peak": flops / fus / 1e9 / peak_tf, "fused_vs_separate": sep / fus})
+        del pool, x
+    print(json.dumps({"workload": "QKV projection + RoPE + append, hidden 4096, 32q/8kv heads, D128, bf16, page16",
+                      "peak_TFLOPs": peak_tf, "rows": rows, "device_error_word": ops.device_error(dev)}), flush=True)
+
+
 def run_copy(args):
     """`--workload copy`: the page-copy kernel (copy-on-write of forked pages) and the RoPE + append kernel
     alone, with CUDA events: achieved bytes/s (read + written) against the measured HBM copy bandwidth."""
@@ -1483,7 +1556,7 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
     ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
     ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam", "copy"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam", "copy", "qkv"],
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
@@ -1519,6 +1592,8 @@ def main():
         run_beam(args)
     elif args.workload == "copy":
         run_copy(args)
+    elif args.workload == "qkv":
+        run_qkv(args)
     else:
         run_ours(args)
 

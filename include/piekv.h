@@ -152,6 +152,21 @@ int piekv_rope_append(void *q, void *k, const void *v, int64_t q_stride_n, int64
                       int32_t num_pages, int32_t dtype, const piekv_rope_params *rope,
                       int32_t rotate_k_in_place, int32_t *err, void *stream);
 
+/* The projection in front of the path, fused with it: qkv = x . w_qkv^T for `nnz` token rows
+ * (x [nnz, hidden], w_qkv [(Hq + 2 Hkv) * 128, hidden], both row-major 16-bit with row strides in elements),
+ * q heads rotated and written to q_out [nnz, Hq, 128] (contiguous), k heads rotated and v heads copied
+ * straight into each token's slot of the paged pool; the [nnz, (Hq + 2 Hkv) * 128] projection output never
+ * exists in memory, and the fp32 accumulator is rounded once, after the rotation.  head_dim 128, hidden a
+ * multiple of 64, pairs (i, i + 64) only.  Stands for the sequence linear -> split -> RoPE -> append of
+ * ForwardPass.attention (pie/src/pie_worker/model/llama3.py:627-685) when no adapter edits q / k / v in
+ * between. */
+int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const void *w_qkv, int64_t w_stride_n, void *q_out,
+                          const int32_t *pos_ids, const int32_t *batch_indices, const int32_t *positions,
+                          void *pool, const int32_t *kv_indices, const int32_t *kv_indptr, int32_t nnz,
+                          int32_t batch, int32_t hidden, int32_t num_qo_heads, int32_t num_kv_heads,
+                          int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype,
+                          const piekv_rope_params *rope, int32_t *err, void *stream);
+
 /* ---- attention ------------------------------------------------------------------- */
 
 /* Bytes of scratch piekv_decode_run needs at least for `batch` requests (split-KV partials and the

@@ -103,6 +103,11 @@ SIGNATURES = {
         [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _i64, _p, _p, _p, _p, _p, _p, _p,
          _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, C.POINTER(RopeParams), _i32, _p, _p],
     ),
+    "piekv_qkv_rope_append": (
+        C.c_int,
+        [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+         C.POINTER(RopeParams), _p, _p],
+    ),
     "piekv_decode_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
     "piekv_decode_counter_bytes": (_i64, [_i32]),
     "piekv_decode_run": (

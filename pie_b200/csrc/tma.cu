@@ -55,4 +55,19 @@ int make_q_tensor_map(CUtensorMap *tm, const void *q, int64_t nnz, int hq, int64
   return 0;
 }
 
+
+int make_matrix_tensor_map(CUtensorMap *tm, const void *ptr, int64_t rows, int64_t cols, int64_t row_stride, int dtype,
+                           int box_rows, int box_cols) {
+  EncodeTiledFn enc = get_encode_fn();
+  PIEKV_REQUIRE(enc != nullptr, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t gstr[1] = {(cuuint64_t)row_stride * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, tm_dtype(dtype), 2, const_cast<void *>(ptr), gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  PIEKV_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (matrix) failed with CUresult %d", (int)r);
+  return 0;
+}
+
 }  // namespace piekv

@@ -16,6 +16,18 @@ int make_page_tensor_map(CUtensorMap *tm, const void *pool, int num_pages, int h
 int make_q_tensor_map(CUtensorMap *tm, const void *q, int64_t nnz, int hq, int64_t q_sn, int64_t q_sh, int dtype,
                       int box_rows, int box_heads = 1);
 
+// Row-major matrix [rows, cols] of 16-bit elements (row stride in elements) seen as {cols, rows}; box
+// {box_cols (64: one 128-byte swizzled row), box_rows}: shared memory receives [box_rows][64], K-major.
+int make_matrix_tensor_map(CUtensorMap *tm, const void *ptr, int64_t rows, int64_t cols, int64_t row_stride, int dtype,
+                           int box_rows, int box_cols);
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, int c0, int c1, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(smem_u32(bar))
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap *tmap, int c0, int c1, int c2, int c3,
                                             int c4, uint64_t *bar) {
   asm volatile(

@@ -378,6 +378,53 @@ def rope_append_paged_kv_cache(q: Optional[torch.Tensor], k: torch.Tensor, v: to
             rope, rotate_k_in_place, "rope_append_paged_kv_cache")
 
 
+def qkv_rope_append_paged_kv_cache(x: torch.Tensor, w_qkv: torch.Tensor, pos_ids: torch.Tensor,
+                                   batch_indices: torch.Tensor, positions: torch.Tensor,
+                                   paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor, kv_indptr: torch.Tensor,
+                                   num_qo_heads: int, num_kv_heads: int, rope: Optional[RopeConfig] = None,
+                                   q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The QKV projection with RoPE and the append as its epilogue: `x` [n, hidden] times `w_qkv`
+    [(Hq + 2 Hkv) * 128, hidden] (the fused weight of pie/src/pie_worker/model/llama3.py:627-630, as
+    `torch.nn.functional.linear` takes it); rotated q comes back as [n, Hq, 128], rotated k and v go straight
+    into the paged cache.  The projection output itself is never written to memory, and the fp32 accumulator is
+    rounded once, after the rotation (the reference rounds the projection first).  One launch for
+    llama3.py:627-685 when no adapter edits q / k / v in between.  head_dim 128, 16-bit types, hidden a
+    multiple of 64."""
+    _require_cuda(x, "x")
+    _require_cuda(w_qkv, "w_qkv")
+    _require_i32(pos_ids, "pos_ids")
+    _require_i32(batch_indices, "batch_indices")
+    _require_i32(positions, "positions")
+    _require_i32(kv_indices, "kv_indices")
+    _require_i32(kv_indptr, "kv_indptr")
+    num_pages, page_size, hkv, d = _check_pool(paged_kv_cache)
+    if x.dim() != 2 or w_qkv.dim() != 2 or x.stride(1) != 1 or w_qkv.stride(1) != 1:
+        raise ValueError("x and w_qkv must be 2-D with contiguous rows")
+    n, hidden = x.shape
+    if hkv != num_kv_heads or d != 128:
+        raise ValueError(f"the cache holds {hkv} kv heads of dim {d}; expected {num_kv_heads} of dim 128")
+    if tuple(w_qkv.shape) != ((num_qo_heads + 2 * num_kv_heads) * d, hidden):
+        raise ValueError(f"w_qkv shape {tuple(w_qkv.shape)} differs from "
+                         f"({(num_qo_heads + 2 * num_kv_heads) * d}, {hidden})")
+    if not (x.dtype == w_qkv.dtype == paged_kv_cache.dtype):
+        raise ValueError("x, w_qkv and the cache must share one dtype")
+    if pos_ids.shape[0] < n or batch_indices.shape[0] < n or positions.shape[0] < n:
+        raise ValueError("pos_ids / batch_indices / positions shorter than the token count")
+    if q_out is None:
+        q_out = torch.empty((n, num_qo_heads, d), dtype=x.dtype, device=x.device)
+    elif tuple(q_out.shape) != (n, num_qo_heads, d) or q_out.dtype != x.dtype or not q_out.is_contiguous():
+        raise ValueError("q_out must be a contiguous [n, num_qo_heads, 128] tensor of x's dtype")
+    rp = (rope if rope is not None else RopeConfig()).to_c(d)
+    check(lib.piekv_qkv_rope_append(x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), q_out.data_ptr(),
+                                    pos_ids.data_ptr(), batch_indices.data_ptr(), positions.data_ptr(),
+                                    paged_kv_cache.data_ptr(), kv_indices.data_ptr(), kv_indptr.data_ptr(), n,
+                                    kv_indptr.shape[0] - 1, hidden, num_qo_heads, num_kv_heads, d, page_size,
+                                    num_pages, _dtype_code(x.dtype, "qkv_rope_append_paged_kv_cache"), rp,
+                                    _err_word(x.device).data_ptr(), _stream(x.device)),
+          "qkv_rope_append_paged_kv_cache")
+    return q_out
+
+
 def copy_kv_pages(kv_cache_at_layer: Sequence[torch.Tensor], src_pages: torch.Tensor, dst_pages: torch.Tensor,
                   valid_len: Optional[torch.Tensor] = None) -> None:
     """Copy the first `valid_len[j]` token rows (default: all) of page src[j] to page dst[j] in every
