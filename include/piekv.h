@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define PIEKV_VERSION 101
+#define PIEKV_VERSION 102
 
 /* element types */
 #define PIEKV_F32 0
@@ -166,6 +166,26 @@ int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const void *w_qkv, 
                           int32_t batch, int32_t hidden, int32_t num_qo_heads, int32_t num_kv_heads,
                           int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype,
                           const piekv_rope_params *rope, int32_t *err, void *stream);
+
+/* Optional terms between the projection and the rotation, as other model families have them: a bias on the
+ * whole projection (pie/src/pie_worker/model/qwen2.py:596-603) and a per-head RMSNorm of q and of k with a
+ * [128] weight each (qwen3.py:651-662: x * rsqrt(mean(x^2) + eps) * weight over the head's 128 elements), all
+ * evaluated on the fp32 accumulator.  NULL pointers switch a term off. */
+typedef struct piekv_qkv_options {
+  const void *bias;          /* [(Hq + 2 Hkv) * 128], storage type */
+  const void *q_norm_weight; /* [128], storage type */
+  const void *k_norm_weight; /* [128], storage type */
+  float rms_eps;
+  int32_t reserved;
+} piekv_qkv_options;
+
+int piekv_qkv_rope_append_opt(const void *x, int64_t x_stride_n, const void *w_qkv, int64_t w_stride_n, void *q_out,
+                              const int32_t *pos_ids, const int32_t *batch_indices, const int32_t *positions,
+                              void *pool, const int32_t *kv_indices, const int32_t *kv_indptr, int32_t nnz,
+                              int32_t batch, int32_t hidden, int32_t num_qo_heads, int32_t num_kv_heads,
+                              int32_t head_dim, int32_t page_size, int32_t num_pages, int32_t dtype,
+                              const piekv_rope_params *rope, int32_t *err, void *stream,
+                              const piekv_qkv_options *opt);
 
 /* ---- attention ------------------------------------------------------------------- */
 
@@ -443,8 +463,8 @@ int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_c
                             void *stream);
 
 /* sizeof of the structs that cross this boundary, for bindings to check their mirrors against:
- * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options, 3: piekv_wire_batch; anything
- * else: -1. */
+ * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options, 3: piekv_wire_batch,
+ * 4: piekv_qkv_options; anything else: -1. */
 int32_t piekv_abi_sizeof(int32_t which);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */

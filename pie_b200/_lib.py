@@ -62,6 +62,13 @@ class WireBatch(C.Structure):
                [(n, C.c_int32) for n in ("nnz", "batch", "total_pages", "num_runs")]
 
 
+class QkvOptions(C.Structure):
+    """Mirror of `piekv_qkv_options`."""
+
+    _fields_ = [("bias", C.c_void_p), ("q_norm_weight", C.c_void_p), ("k_norm_weight", C.c_void_p),
+                ("rms_eps", C.c_float), ("reserved", C.c_int32)]
+
+
 MAX_PEERS = 8
 PEER_HANDLE_BYTES = 64
 
@@ -107,6 +114,11 @@ SIGNATURES = {
         C.c_int,
         [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
          C.POINTER(RopeParams), _p, _p],
+    ),
+    "piekv_qkv_rope_append_opt": (
+        C.c_int,
+        [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+         C.POINTER(RopeParams), _p, _p, C.POINTER(QkvOptions)],
     ),
     "piekv_decode_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
     "piekv_decode_counter_bytes": (_i64, [_i32]),

@@ -14,8 +14,9 @@
 // Per tile: hidden / 64 k-blocks; a k-block is one TMA box of x (128 x 64, K-major, 128-byte swizzle) and one
 // of w (NH * 128 x 64), four tcgen05.mma (M128, N = NH * 128, K16) each.  Four stages of 32 or 48 KiB; two
 // accumulators (2 x NH * 128 TMEM columns) so that the epilogue of a tile runs under the MMAs of the next.
-// Roles: warps 0-3 epilogue (thread = token row = TMEM lane), warp 4 TMA producer, warp 5 MMA issuer and
-// TMEM owner.  Every wait is bounded (2 s); on expiry the error word is set and all roles leave.
+// Roles: warps 0-7 epilogue (thread = token row = TMEM lane; the two warps of a lane quarter take one head
+// each: the rotation's cos / sin are the epilogue's cost), warp 8 TMA producer, warp 9 MMA issuer and TMEM
+// owner.  Every wait is bounded (2 s); on expiry the error word is set and all roles leave.
 #include <type_traits>
 
 #include "rope.cuh"
@@ -30,8 +31,8 @@ constexpr int kQDim = 128;
 constexpr int kQBM = 128, kQBK = 64;
 constexpr int kQStages = 4;
 constexpr int kQTileBytes = kQBM * kQBK * 2;  // 128 rows x 64 16-bit elements
-constexpr int kQThreads = 192;
-constexpr int kQEpiWarps = 4, kQProducerWarp = 4, kQMmaWarp = 5;
+constexpr int kQEpiWarps = 8, kQProducerWarp = 8, kQMmaWarp = 9;
+constexpr int kQThreads = 32 * (kQEpiWarps + 2);
 
 struct QkvParams {
   int n, hidden, hq, hkv;
@@ -40,6 +41,10 @@ struct QkvParams {
   const int32_t *pos_ids, *batch_indices, *positions, *kv_indices, *kv_indptr;
   int batch, page_size, num_pages;
   int32_t *err;
+  const void *bias;     // nullable: [(Hq + 2 Hkv) * 128], added to the projection
+  const void *q_norm;   // nullable: [128] weight of a per-head RMSNorm of q, applied before the rotation
+  const void *k_norm;   // the same for k
+  float rms_eps;
 };
 
 template <typename T, int NH>
@@ -139,9 +144,10 @@ __global__ void __launch_bounds__(kQThreads, 1)
       }
     }
   } else {
-    // ================================================ epilogue: thread = token row
-    const int r = warp * 32 + lane;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    // ================================================ epilogue: thread = token row; warps w and w + 4 own the
+    // same 32 rows (TMEM lanes) and take one head of the tile each
+    const int r = (warp & 3) * 32 + lane;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     T *q_out = reinterpret_cast<T *>(p.q_out);
     T *pool = reinterpret_cast<T *>(p.pool);
     const size_t half_page = (size_t)p.page_size * p.hkv * kQDim;
@@ -155,7 +161,7 @@ __global__ void __launch_bounds__(kQThreads, 1)
       __syncwarp();
       tc::fence_after_sync();
 #pragma unroll 1
-      for (int hh = 0; hh < NH; ++hh) {
+      for (int hh = warp >> 2; hh < NH; hh += 2) {
       const int h = hg * NH + hh;
       // where the row goes, and whether it is rotated
       T *dst = nullptr;
@@ -193,6 +199,33 @@ __global__ void __launch_bounds__(kQThreads, 1)
         rot = false;  // the row is stored un-rotated, as the separate kernel does
       }
       const uint32_t acc = tmem + lane_base + (buf * NH + hh) * kQDim;
+      const T *bias = p.bias != nullptr ? reinterpret_cast<const T *>(p.bias) + (size_t)h * kQDim : nullptr;
+      const T *nw = is_q ? reinterpret_cast<const T *>(p.q_norm) : (is_k ? reinterpret_cast<const T *>(p.k_norm) : nullptr);
+      float inv_rms = 1.f;
+      if (nw != nullptr) {
+        // per-head RMSNorm of the row (over its 128 elements) ahead of the rotation: a pass of its own
+        // over the accumulator for the sum of squares
+        float ss = 0.f;
+#pragma unroll 1
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t v[32];
+          tc::tmem_ld32(acc + ch * 32, v);
+          tc::tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float x = __uint_as_float(v[i]) + (bias ? Elem<T>::to_f32(bias[ch * 32 + i]) : 0.f);
+            ss = fmaf(x, x, ss);
+          }
+        }
+        inv_rms = rsqrtf(ss * (1.f / kQDim) + p.rms_eps);
+      }
+      // element `col` of the row as the reference has it before the rotation
+      auto value = [&](uint32_t raw, int col) {
+        float x = __uint_as_float(raw);
+        if (bias) x += Elem<T>::to_f32(bias[col]);
+        if (nw) x = x * inv_rms * Elem<T>::to_f32(nw[col]);
+        return x;
+      };
       // pairs (i, i + 64): columns [32c, 32c + 32) with [64 + 32c, 64 + 32c + 32)
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {
@@ -204,8 +237,8 @@ __global__ void __launch_bounds__(kQThreads, 1)
           uint32_t olo[16], ohi[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float x0 = __uint_as_float(lo[i]), x1 = __uint_as_float(lo[i + 1]);
-            float y0 = __uint_as_float(hi[i]), y1 = __uint_as_float(hi[i + 1]);
+            float x0 = value(lo[i], c * 32 + i), x1 = value(lo[i + 1], c * 32 + i + 1);
+            float y0 = value(hi[i], 64 + c * 32 + i), y1 = value(hi[i + 1], 64 + c * 32 + i + 1);
             if (rot) {
               float c0, s0, c1, s1, a0, b0, a1, b1;
               rope_cos_sin1(rp, pos_id, c * 32 + i, 64, c0, s0);
@@ -259,13 +292,14 @@ int launch_qkv(const CUtensorMap &tx, const CUtensorMap &tw, const QkvParams &p,
 }  // namespace
 }  // namespace piekv
 
-extern "C" int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const void *w_qkv, int64_t w_stride_n,
-                                     void *q_out, const int32_t *pos_ids, const int32_t *batch_indices,
-                                     const int32_t *positions, void *pool, const int32_t *kv_indices,
-                                     const int32_t *kv_indptr, int32_t nnz, int32_t batch, int32_t hidden,
-                                     int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
-                                     int32_t num_pages, int32_t dtype, const piekv_rope_params *rope, int32_t *err,
-                                     void *stream) {
+extern "C" int piekv_qkv_rope_append_opt(const void *x, int64_t x_stride_n, const void *w_qkv, int64_t w_stride_n,
+                                         void *q_out, const int32_t *pos_ids, const int32_t *batch_indices,
+                                         const int32_t *positions, void *pool, const int32_t *kv_indices,
+                                         const int32_t *kv_indptr, int32_t nnz, int32_t batch, int32_t hidden,
+                                         int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim,
+                                         int32_t page_size, int32_t num_pages, int32_t dtype,
+                                         const piekv_rope_params *rope, int32_t *err, void *stream,
+                                         const piekv_qkv_options *opt) {
   using namespace piekv;
   PIEKV_REQUIRE(dtype == PIEKV_BF16 || dtype == PIEKV_F16, "qkv_rope_append: 16-bit types only (dtype %d)", dtype);
   PIEKV_REQUIRE(head_dim == kQDim, "qkv_rope_append: head_dim %d (only 128)", head_dim);
@@ -302,6 +336,11 @@ extern "C" int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const vo
   p.page_size = page_size;
   p.num_pages = num_pages;
   p.err = err;
+  p.bias = opt ? opt->bias : nullptr;
+  p.q_norm = opt ? opt->q_norm_weight : nullptr;
+  p.k_norm = opt ? opt->k_norm_weight : nullptr;
+  p.rms_eps = opt ? opt->rms_eps : 0.f;
+  PIEKV_REQUIRE(!opt || opt->rms_eps >= 0.f, "qkv_rope_append: negative rms_eps");
   CUtensorMap tx, tw;
   const int64_t rows_w = (int64_t)(num_qo_heads + 2 * num_kv_heads) * head_dim;
   if (int rc = make_matrix_tensor_map(&tx, x, nnz, hidden, x_stride_n, dtype, kQBM, kQBK)) return rc;
@@ -311,4 +350,16 @@ extern "C" int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const vo
   if (dtype == PIEKV_BF16)
     return nh == 2 ? launch_qkv<__nv_bfloat16, 2>(tx, tw, p, rp, st) : launch_qkv<__nv_bfloat16, 1>(tx, tw, p, rp, st);
   return nh == 2 ? launch_qkv<__half, 2>(tx, tw, p, rp, st) : launch_qkv<__half, 1>(tx, tw, p, rp, st);
+}
+
+extern "C" int piekv_qkv_rope_append(const void *x, int64_t x_stride_n, const void *w_qkv, int64_t w_stride_n,
+                                     void *q_out, const int32_t *pos_ids, const int32_t *batch_indices,
+                                     const int32_t *positions, void *pool, const int32_t *kv_indices,
+                                     const int32_t *kv_indptr, int32_t nnz, int32_t batch, int32_t hidden,
+                                     int32_t num_qo_heads, int32_t num_kv_heads, int32_t head_dim, int32_t page_size,
+                                     int32_t num_pages, int32_t dtype, const piekv_rope_params *rope, int32_t *err,
+                                     void *stream) {
+  return piekv_qkv_rope_append_opt(x, x_stride_n, w_qkv, w_stride_n, q_out, pos_ids, batch_indices, positions, pool,
+                                   kv_indices, kv_indptr, nnz, batch, hidden, num_qo_heads, num_kv_heads, head_dim,
+                                   page_size, num_pages, dtype, rope, err, stream, nullptr);
 }

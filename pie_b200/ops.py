@@ -382,14 +382,21 @@ def qkv_rope_append_paged_kv_cache(x: torch.Tensor, w_qkv: torch.Tensor, pos_ids
                                    batch_indices: torch.Tensor, positions: torch.Tensor,
                                    paged_kv_cache: torch.Tensor, kv_indices: torch.Tensor, kv_indptr: torch.Tensor,
                                    num_qo_heads: int, num_kv_heads: int, rope: Optional[RopeConfig] = None,
-                                   q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                                   q_out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                                   q_norm_weight: Optional[torch.Tensor] = None,
+                                   k_norm_weight: Optional[torch.Tensor] = None,
+                                   rms_norm_eps: float = 1e-6) -> torch.Tensor:
     """The QKV projection with RoPE and the append as its epilogue: `x` [n, hidden] times `w_qkv`
     [(Hq + 2 Hkv) * 128, hidden] (the fused weight of pie/src/pie_worker/model/llama3.py:627-630, as
     `torch.nn.functional.linear` takes it); rotated q comes back as [n, Hq, 128], rotated k and v go straight
     into the paged cache.  The projection output itself is never written to memory, and the fp32 accumulator is
     rounded once, after the rotation (the reference rounds the projection first).  One launch for
     llama3.py:627-685 when no adapter edits q / k / v in between.  head_dim 128, 16-bit types, hidden a
-    multiple of 64."""
+    multiple of 64.
+
+    `bias` [(Hq + 2 Hkv) * 128] is added to the projection (pie/src/pie_worker/model/qwen2.py:596-603);
+    `q_norm_weight` / `k_norm_weight` [128] apply the per-head RMSNorm of qwen3.py:651-662 to q / k before
+    the rotation (`rms_norm_eps` as there)."""
     _require_cuda(x, "x")
     _require_cuda(w_qkv, "w_qkv")
     _require_i32(pos_ids, "pos_ids")
@@ -415,12 +422,26 @@ def qkv_rope_append_paged_kv_cache(x: torch.Tensor, w_qkv: torch.Tensor, pos_ids
     elif tuple(q_out.shape) != (n, num_qo_heads, d) or q_out.dtype != x.dtype or not q_out.is_contiguous():
         raise ValueError("q_out must be a contiguous [n, num_qo_heads, 128] tensor of x's dtype")
     rp = (rope if rope is not None else RopeConfig()).to_c(d)
-    check(lib.piekv_qkv_rope_append(x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0), q_out.data_ptr(),
-                                    pos_ids.data_ptr(), batch_indices.data_ptr(), positions.data_ptr(),
-                                    paged_kv_cache.data_ptr(), kv_indices.data_ptr(), kv_indptr.data_ptr(), n,
-                                    kv_indptr.shape[0] - 1, hidden, num_qo_heads, num_kv_heads, d, page_size,
-                                    num_pages, _dtype_code(x.dtype, "qkv_rope_append_paged_kv_cache"), rp,
-                                    _err_word(x.device).data_ptr(), _stream(x.device)),
+    opt = None
+    if bias is not None or q_norm_weight is not None or k_norm_weight is not None:
+        opt = _lib.QkvOptions()
+        for name, t, numel in (("bias", bias, (num_qo_heads + 2 * num_kv_heads) * d),
+                               ("q_norm_weight", q_norm_weight, d), ("k_norm_weight", k_norm_weight, d)):
+            if t is not None:
+                _require_cuda(t, name)
+                if t.dtype != x.dtype or t.numel() != numel or not t.is_contiguous():
+                    raise ValueError(f"{name} must be a contiguous tensor of {numel} elements of x's dtype")
+            setattr(opt, name, t.data_ptr() if t is not None else None)
+        opt.rms_eps = float(rms_norm_eps)
+        opt.reserved = 0
+    check(lib.piekv_qkv_rope_append_opt(x.data_ptr(), x.stride(0), w_qkv.data_ptr(), w_qkv.stride(0),
+                                        q_out.data_ptr(), pos_ids.data_ptr(), batch_indices.data_ptr(),
+                                        positions.data_ptr(), paged_kv_cache.data_ptr(), kv_indices.data_ptr(),
+                                        kv_indptr.data_ptr(), n, kv_indptr.shape[0] - 1, hidden, num_qo_heads,
+                                        num_kv_heads, d, page_size, num_pages,
+                                        _dtype_code(x.dtype, "qkv_rope_append_paged_kv_cache"), rp,
+                                        _err_word(x.device).data_ptr(), _stream(x.device),
+                                        C.byref(opt) if opt is not None else None),
           "qkv_rope_append_paged_kv_cache")
     return q_out
 

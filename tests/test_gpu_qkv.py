@@ -57,16 +57,28 @@ def _case(n_req, hq, hkv, hidden, seed, dtype=torch.bfloat16, num_pages=256):
                 pos=np.array(pos, np.int32), bi=bi, kp=kp)
 
 
-def _oracle(c, table, round_projection):
+def _oracle(c, table, round_projection, bias=None, q_norm=None, k_norm=None, eps=1e-6):
     """(q rows, pool) of the reference sequence on the CPU; `round_projection` rounds the projection to the
-    storage type before the rotation, as the reference does."""
+    storage type before the rotation, as the reference does.  `bias`: qwen2.py:596-603; `q_norm` / `k_norm`:
+    the per-head RMSNorm of qwen3.py:651-662."""
     n, hq, hkv, d = c["n"], c["hq"], c["hkv"], c["d"]
     qkv = c["x"].float() @ c["w"].float().t()
+    if bias is not None:
+        qkv = qkv + bias.float()
     if round_projection:
         qkv = qkv.to(c["x"].dtype).float()
     q = qkv[:, : hq * d].reshape(n, hq, d)
     k = qkv[:, hq * d: (hq + hkv) * d].reshape(n, hkv, d)
     v = qkv[:, (hq + hkv) * d:].reshape(n, hkv, d)
+
+    def rms(t, w):
+        t = t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+        return t.to(c["x"].dtype).float() if round_projection else t
+
+    if q_norm is not None:
+        q = rms(q, q_norm)
+    if k_norm is not None:
+        k = rms(k, k_norm)
     cs, sn = table[c["pos"], :64], table[c["pos"], 64:]
     q = R.apply_rope(q, cs, sn).to(c["x"].dtype)   # float32 in: one rounding at the end
     k = R.apply_rope(k, cs, sn).to(c["x"].dtype)
@@ -100,6 +112,30 @@ def test_qkv_rope_append_against_the_oracle(n_req, hq, hkv, hidden):
         page = int(c["idx"][c["ptr"][b] + pos // 16])
         untouched[page, :, pos % 16] = False
     assert torch.equal(pool_gpu.cpu()[untouched].view(torch.int16), c["pool"][untouched].view(torch.int16))
+
+
+@pytest.mark.parametrize("family", ["qwen2 (bias)", "qwen3 (q / k norm)", "both"])
+def test_qkv_rope_append_with_bias_and_per_head_norm(family):
+    c = _case(4, 16, 4, 512, seed=21)
+    inv = R.rope_inv_freq(128, 1000000.0, "plain", 1.0)
+    table = R.make_cos_sin_table(256, inv)
+    bias = W.randn(((16 + 8) * 128,), 31, torch.bfloat16, 0.5) if family != "qwen3 (q / k norm)" else None
+    qn = (1.0 + W.randn((128,), 32, torch.bfloat16, 0.2)) if family != "qwen2 (bias)" else None
+    kn = (1.0 + W.randn((128,), 33, torch.bfloat16, 0.2)) if family != "qwen2 (bias)" else None
+    pool_gpu = c["pool"].cuda()
+    rope = ops.RopeConfig(mode="table", cos_sin_table=dev(table))
+    q = ops.qkv_rope_append_paged_kv_cache(
+        c["x"].cuda(), c["w"].cuda(), dev(c["pos"]), dev(c["bi"]), dev(c["kp"]), pool_gpu, dev(c["idx"]),
+        dev(c["ptr"]), 16, 4, rope=rope, bias=None if bias is None else bias.cuda(),
+        q_norm_weight=None if qn is None else qn.cuda(), k_norm_weight=None if kn is None else kn.cuda(),
+        rms_norm_eps=1e-6)
+    torch.cuda.synchronize()
+    assert ops.device_error("cuda") is None
+    q1, pool1 = _oracle(c, table, False, bias, qn, kn)
+    q2, pool2 = _oracle(c, table, True, bias, qn, kn)
+    assert within(q.cpu(), q1, 1) and within(pool_gpu.cpu(), pool1, 1)
+    assert within(q.cpu(), q2, 3, OPERAND) and within(pool_gpu.cpu(), pool2, 3, OPERAND)
+    assert not within(q.cpu(), _oracle(c, table, False)[0], 1)  # the options do something
 
 
 def test_qkv_rope_append_equals_the_separate_kernels_on_a_rounded_projection():
