@@ -486,3 +486,38 @@ def _two_level(hq, hkv, ctx, deterministic):
     else:
         assert (out.float() - out2.float()).abs().max().item() <= 4e-3
     assert int(ws[: ops.COUNTER_BYTES].view(torch.int32).abs().sum().item()) == 0
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (6, 2)])  # two heads per work item / one head per CTA
+def test_prefill_work_items_with_nothing_to_attend_to(hq, hkv):
+    """A request whose mask hides every key (all of its query tiles have no kv tile to visit) and a request
+    without query tokens, between ordinary ones: zeros and -inf for the first, nothing for the second, the
+    ordinary requests as the oracle has them.  (The persistent kernel passes such items through all its roles
+    without loads or MMAs.)"""
+    reqs = [(40, 150), (300, 200), (0, 0), (70, 140)]
+    sc = make_scenario(hq, hkv, 128, torch.bfloat16, reqs, seed=77, scale=0.5)
+    m = sc.meta
+    rng = np.random.default_rng(9)
+    parts = []
+    for b in range(m.batch):
+        qo, kv = int(m.qo_indptr[b + 1] - m.qo_indptr[b]), int(m.seq_lens[b])
+        blk = rng.random((qo, kv)) < 0.5
+        if qo:
+            blk[:, 0] = True
+        if b == 1:
+            blk[:] = False  # nothing is visible to any query of this request
+        parts.append(blk.reshape(-1))
+    mask = np.concatenate(parts)
+    ref, ref_lse = R.prefill_attention(sc.q, sc.pool, m.qo_indptr, m.kv_indptr, m.kv_indices, m.kv_last_page_len,
+                                       custom_mask=mask, return_lse=True)
+    w = ops.BatchPrefillWithPagedKVCacheWrapper(_workspace(), "NHD")
+    w.plan(qo_indptr=dev(m.qo_indptr), paged_kv_indptr=dev(m.kv_indptr), paged_kv_indices=dev(m.kv_indices),
+           paged_kv_last_page_len=dev(m.kv_last_page_len), num_qo_heads=hq, num_kv_heads=hkv, head_dim_qk=128,
+           page_size=16, custom_mask=dev(mask), q_data_type=torch.bfloat16)
+    out, lse = w.run(sc.q.cuda(), sc.pool.cuda(), return_lse=True)
+    assert ops.device_error("cuda") is None
+    s, e = int(m.qo_indptr[1]), int(m.qo_indptr[2])
+    assert torch.count_nonzero(out[s:e]).item() == 0 and torch.isinf(lse[s:e]).all() and (lse[s:e] < 0).all()
+    keep = np.r_[0:s, e:int(m.qo_indptr[-1])]
+    assert (out.cpu().float()[keep] - ref.float()[keep]).abs().max().item() <= 2e-2
+    assert (lse.cpu()[keep] - ref_lse[keep]).abs().max().item() <= 2e-2
