@@ -306,7 +306,7 @@ __device__ __noinline__ int collect_slots(unsigned short *tab, int first, int co
 // to L2 - which, while the other SMs are still streaming, takes microseconds.  The result is the request's
 // output row (normalised) or again a partial (maximum, sum, unnormalised accumulator) written to sub-slot 0
 // of `to_slot`.
-template <typename T, int PG, int HW>
+template <typename T, int HW>
 __device__ __forceinline__ void merge_heads(const DecodeParams &p, const unsigned short *list, int np, int subs, int b,
                                             int to_slot, int peer_step, int q0) {
   constexpr int PB = 16 / HW;  // partials per batch
@@ -387,7 +387,7 @@ __device__ __forceinline__ void merge_heads(const DecodeParams &p, const unsigne
 
 // All consumer threads: warp w folds heads w, w + 8, ... (up to four at a time; with few heads per warp more
 // partials are in flight per batch instead).
-template <typename T, int PG>
+template <typename T>
 __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned short *list, int n, int subs, int b,
                                          int to_slot, int peer_step) {
   const int warp = threadIdx.x >> 5;
@@ -396,11 +396,11 @@ __device__ __noinline__ void merge_slots(const DecodeParams &p, const unsigned s
   for (int q0 = warp; q0 < hq; q0 += 4 * kConsumerWarps) {
     const int left = (hq - q0 + kConsumerWarps - 1) / kConsumerWarps;  // heads of this warp from q0 on
     if (left >= 3)
-      merge_heads<T, PG, 4>(p, list, np, subs, b, to_slot, peer_step, q0);
+      merge_heads<T, 4>(p, list, np, subs, b, to_slot, peer_step, q0);
     else if (left == 2)
-      merge_heads<T, PG, 2>(p, list, np, subs, b, to_slot, peer_step, q0);
+      merge_heads<T, 2>(p, list, np, subs, b, to_slot, peer_step, q0);
     else
-      merge_heads<T, PG, 1>(p, list, np, subs, b, to_slot, peer_step, q0);
+      merge_heads<T, 1>(p, list, np, subs, b, to_slot, peer_step, q0);
   }
 }
 
@@ -917,7 +917,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     return collect_slots(tab, first, count, sh_list, &sh_nlist, sh_wsum);
   };
   auto merge_list = [&](int n, int subs, int b_, int to_slot) {
-    merge_slots<T, PG>(p, sh_list, n, subs, b_, to_slot, peer_step);
+    merge_slots<T>(p, sh_list, n, subs, b_, to_slot, peer_step);
   };
 
   int b = 0, req_begin = 0, req_end = 0, last_len = kPage, rope_pos = 0, win_first = 0;
