@@ -472,7 +472,8 @@ def run_ours(args):
         except Exception as e:  # a sub-record must never cost the headline its line
             sub["head_sharded"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
         if world == 1:
-            for name, fn in (("prefill", lambda: prefill_subrecord(dev)), ("beam", lambda: beam_subrecord(dev))):
+            for name, fn in (("prefill", lambda: prefill_subrecord(dev)), ("beam", lambda: beam_subrecord(dev)),
+                             ("qkv", lambda: qkv_subrecord(dev))):
                 try:
                     sub[name] = fn()
                 except Exception as e:
@@ -1151,19 +1152,17 @@ def beam_leg():
         "device_error_word": ops.device_error(dev)}
 
 
-def run_qkv(args):
-    """`--workload qkv`: the QKV projection of the prefill mix (config 3's 20480 tokens, hidden 4096, 32q/8kv
-    heads) with RoPE + append, as the library GEMM followed by `rope_append_paged_kv_cache` and as the one fused
-    tcgen05 kernel (`qkv_rope_append_paged_kv_cache`); plus a decode-sized batch."""
+def qkv_rows(dev, prefill_only=False):
+    """The QKV projection of the prefill mix (config 3's 20480 tokens, hidden 4096, 32q/8kv heads) with RoPE +
+    append, as the library GEMM followed by `rope_append_paged_kv_cache` and as the one fused tcgen05 kernel
+    (`qkv_rope_append_paged_kv_cache`); plus (unless `prefill_only`) a decode-sized batch."""
     from pie_b200 import ops
     from pie_b200 import workloads as W
 
-    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
-    torch.cuda.set_device(dev)
     cfg = W.CONFIG2
     HQ, HKV, D = cfg.num_qo_heads, cfg.num_kv_heads, cfg.head_dim
     hidden = 4096
-    peak_tf = load_peaks_tensor()[0]
+    peak_tf, peak_kind = load_peaks_tensor()
     t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(dev)
     rows = []
 
@@ -1180,8 +1179,10 @@ def run_qkv(args):
 
     w = W.randn(((HQ + 2 * HKV) * D, hidden), 601, cfg.dtype, hidden ** -0.5, device=dev)
     rope = ops.RopeConfig()
-    for label, meta, reps in (("prefill mix, 20480 tokens", W.config3_meta(num_pages=8192), 20),
-                              ("decode batch, 64 tokens", W.decode_steps(W.config2_requests(), 1)[0], 50)):
+    cases = [("prefill mix, 20480 tokens", W.config3_meta(num_pages=8192), 20)]
+    if not prefill_only:
+        cases.append(("decode batch, 64 tokens", W.decode_steps(W.config2_requests(), 1)[0], 50))
+    for label, meta, reps in cases:
         n = meta.nnz if hasattr(meta, "nnz") else meta.batch
         pool = W.randn((32768 if n == 64 else 8192, 2, 16, HKV, D), 600, cfg.dtype, 0.5, device=dev)
         x = W.randn((n, hidden), 602, cfg.dtype, 1.0, device=dev)
@@ -1209,8 +1210,38 @@ def run_qkv(args):
         rows.append({"case": label, "tokens": n, "flop": flops,
                      "library_gemm_ms": gemm_only, "library_gemm_plus_rope_append_ms": sep, "fused_ms": fus,
                      "fused_tflops": flops / fus / 1e9, "library_gemm_tflops": flops / gemm_only / 1e9,
-                     "fused_frac_of_peak": flops / fus / 1e9 / peak_tf, "fused_vs_separate": sep / fus})
-        del pool, x
+                     "fused_frac_of_peak": flops / fus / 1e9 / peak_tf, "fused_vs_separate": sep / fus,
+                     "peak_source": peak_kind})
+        del pool, x, q_out
+    del w
+    torch.cuda.empty_cache()
+    return rows, peak_tf
+
+
+def qkv_subrecord(dev):
+    """The `qkv` sub-record of the headline line: the fused projection + RoPE + append kernel on the prefill
+    mix, next to the library GEMM followed by the separate kernel."""
+    from pie_b200 import ops
+
+    rows, peak_tf = qkv_rows(dev, prefill_only=True)
+    r = rows[0]
+    return {"workload": "QKV projection + RoPE + append of the prefill mix: 20480 tokens, hidden 4096, 32q/8kv heads, "
+                        "D128, bf16, page16",
+            "kernel": "qkv_rope_append_kernel (tcgen05 GEMM, RoPE + append in the epilogue)",
+            "ms_per_launch": r["fused_ms"], "library_gemm_ms": r["library_gemm_ms"],
+            "library_gemm_plus_rope_append_ms": r["library_gemm_plus_rope_append_ms"],
+            "roofline": {"bound": "tensor", "achieved": r["fused_tflops"], "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": r["fused_frac_of_peak"], "peak_source": r["peak_source"]},
+            "device_error_word": ops.device_error(dev)}
+
+
+def run_qkv(args):
+    """`--workload qkv`: see `qkv_rows`."""
+    from pie_b200 import ops
+
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(dev)
+    rows, peak_tf = qkv_rows(dev)
     print(json.dumps({"workload": "QKV projection + RoPE + append, hidden 4096, 32q/8kv heads, D128, bf16, page16",
                       "peak_TFLOPs": peak_tf, "rows": rows, "device_error_word": ops.device_error(dev)}), flush=True)
 
