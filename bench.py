@@ -1300,7 +1300,7 @@ def run_copy(args):
                  "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak})
     us = timed(lambda: ops.append_paged_kv_cache(k, v, bi, kp, pool[:8192], indices, indptr, last), 30)
     nbytes = n * (2 * 2 * HKV * D * 2)
-    rows.append({"kernel": "rope_append_tokens_kernel (append only)", "tokens": n, "bytes": nbytes, "us": us,
+    rows.append({"kernel": "append_tokens_warp_kernel (append only)", "tokens": n, "bytes": nbytes, "us": us,
                  "GBps": nbytes / us / 1e3, "frac_of_peak": nbytes / us / 1e3 / peak})
     print(json.dumps({"workload": "page copy and RoPE + append kernels alone, 32q/8kv heads, D128, bf16, page16",
                       "peak_GBps": peak, "peak_source": peak_kind, "rows": rows,

@@ -400,6 +400,60 @@ __global__ void __launch_bounds__(256) rope_append_tokens_kernel(AppendArgs a, R
   }
 }
 
+// Append without a rotation (ops.append_paged_kv_cache): a warp per token, no block-wide step.  Every lane
+// resolves the token's page itself (the three loads are the same addresses for the whole warp), then the
+// lanes move the k row and the v row in 16-byte pieces with all of a lane's loads issued before its stores.
+template <typename T>
+__global__ void __launch_bounds__(256) append_tokens_warp_kernel(AppendArgs a) {
+  constexpr int VEC = 16 / sizeof(T);
+  const int tok = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= a.nnz) return;
+  const int b = a.batch_indices[tok];
+  const int pos = a.positions[tok];
+  if (b < 0 || b >= a.batch) {
+    if (lane == 0) report_error(a.err, PIEKV_ERR_BATCH_INDEX, KID_APPEND, tok, b);
+    return;
+  }
+  const int p0 = a.kv_indptr[b], p1 = a.kv_indptr[b + 1];
+  const int slot = pos >= 0 ? pos / a.page_size : -1;
+  if (slot < 0 || p0 + slot >= p1) {
+    if (lane == 0) report_error(a.err, PIEKV_ERR_PAGE_SLOT, KID_APPEND, tok, pos);
+    return;
+  }
+  const int page = a.kv_indices[p0 + slot];
+  if (page < 0 || page >= a.num_pages) {
+    if (lane == 0) report_error(a.err, PIEKV_ERR_PAGE_ID, KID_APPEND, tok, page);
+    return;
+  }
+  const int D = a.dim;
+  const size_t half_page = (size_t)a.page_size * a.hkv * D;
+  T *kdst = reinterpret_cast<T *>(a.pool) + (size_t)page * 2 * half_page + (size_t)(pos % a.page_size) * a.hkv * D;
+  const int chunks = D / VEC;            // 16-byte pieces per head row
+  const int items = a.hkv * chunks;      // per tensor
+  constexpr int kU = 4;
+  for (int x0 = lane; x0 < items; x0 += 32 * kU) {
+    Vec<T, VEC> kv[kU], vv[kU];
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int x = x0 + u * 32;
+      if (x < items) {
+        const int h = x / chunks, ch = x - h * chunks;
+        kv[u] = load_vec<T, VEC>(reinterpret_cast<const T *>(a.k) + (size_t)tok * a.k_sn + (size_t)h * a.k_sh + ch * VEC);
+        vv[u] = load_vec<T, VEC>(reinterpret_cast<const T *>(a.v) + (size_t)tok * a.v_sn + (size_t)h * a.v_sh + ch * VEC);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const int x = x0 + u * 32;
+      if (x < items) {
+        store_vec<T, VEC>(kdst + (size_t)x * VEC, kv[u]);
+        store_vec<T, VEC>(kdst + half_page + (size_t)x * VEC, vv[u]);
+      }
+    }
+  }
+}
+
 // Per-pair frequencies in double, rounded once to fp32.  Formula of
 // pie/src/flashinfer_metal/kernels/metal_rope.metal:66-89 with the low/high/old_context
 // parameters the reference passes at pie/src/pie_worker/model/llama3.py:660-669.
@@ -446,7 +500,9 @@ static int launch_rope_append_t(const AppendArgs &a, const RopeDev &rp, cudaStre
   if (a.v) vec_ok = vec_ok && aligned16(a.v) && stride_ok(a.v_sn) && stride_ok(a.v_sh);
   if (a.pool) vec_ok = vec_ok && aligned16(a.pool);
   if (a.nnz == 0) return 0;
-  if (vec_ok && !rp.interleave && a.dim <= 2 * kMaxHalfDim && (a.k != nullptr || a.pool == nullptr)) {
+  if (vec_ok && rp.mode == PIEKV_ROPE_NONE && a.q == nullptr && a.k != nullptr && a.v != nullptr && a.pool != nullptr) {
+    append_tokens_warp_kernel<T><<<(a.nnz + 7) / 8, 256, 0, st>>>(a);
+  } else if (vec_ok && !rp.interleave && a.dim <= 2 * kMaxHalfDim && (a.k != nullptr || a.pool == nullptr)) {
     rope_append_tokens_kernel<T><<<(a.nnz + kTokPerBlock - 1) / kTokPerBlock, 256, 0, st>>>(a, rp);
   } else if (vec_ok) {
     int tx = a.dim / VEC;  // chunks across a full row (V copy); rope uses half of them
