@@ -471,6 +471,10 @@ def run_ours(args):
             sub["head_sharded"] = measure_head_sharded(world, rank, dev, steps=48, warmup=4)
         except Exception as e:  # a sub-record must never cost the headline its line
             sub["head_sharded"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+        try:
+            sub["oproj"] = measure_oproj(world, rank, dev, steps=24, warmup=4)
+        except Exception as e:
+            sub["oproj"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
         if world == 1:
             for name, fn in (("prefill", lambda: prefill_subrecord(dev)), ("beam", lambda: beam_subrecord(dev)),
                              ("qkv", lambda: qkv_subrecord(dev))):
@@ -1246,6 +1250,124 @@ def run_qkv(args):
                       "peak_TFLOPs": peak_tf, "rows": rows, "device_error_word": ops.device_error(dev)}), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------
+# secondary workload: output projection with the sum over the ranks in its epilogue
+# ---------------------------------------------------------------------------------------------
+def measure_oproj(world, rank, dev, steps=40, warmup=5, cases=None, shard_of=1):
+    """The `oproj` sub-record: the row-parallel output projection of a 70B-shaped layer (hidden 8192, 64 query
+    heads x 128 split over the ranks) with the all-reduce and the residual add in the kernel's epilogue
+    (`piekv_oproj_allreduce`), next to what the reference does with library calls: matmul, NCCL all-reduce,
+    residual add.  Eight layers' weight shards are used in turn so that a launch does not find its weights in
+    L2.  Times are CUDA events around `steps` launches, max over ranks."""
+    import torch.distributed as dist
+
+    from pie_b200 import ops
+    from pie_b200 import workloads as W
+    from pie_b200.parallel import PeerReduce
+
+    hidden, k_full, layers = 8192, 8192, 8
+    kl = k_full // (world * shard_of)   # shard_of > 1: the shape one of that many ranks holds, no exchange
+    dt = torch.bfloat16
+    ws = [W.randn((hidden, kl), 900 + l, dt, 0.02, device=dev) for l in range(layers)]
+    peak_tf, peak_tf_kind = load_peaks_tensor()
+    peak_bw, peak_bw_kind = load_peaks()
+    cases = cases or (("decode", 256), ("prefill", 8192))
+    n_max = max(n for _, n in cases)
+    pr = PeerReduce(n_max, hidden, dt, dev)
+
+    def over_ranks(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed(fn):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        return over_ranks(e0.elapsed_time(e1) / steps)
+
+    rows = []
+    for name, n in cases:
+        a = W.randn((n, kl), 910, dt, 0.5, device=dev)
+        res = W.randn((n, hidden), 911, dt, 1.0, device=dev)
+
+        def fused(i):
+            return pr.oproj(a, ws[i % layers], res)
+
+        def library(i):
+            y = torch.matmul(a, ws[i % layers].t())
+            if world > 1:
+                dist.all_reduce(y)
+            return res + y
+
+        def library_matmul(i):
+            return torch.matmul(a, ws[i % layers].t())
+
+        got = fused(0).clone()
+        want = library(0)
+        torch.cuda.synchronize(dev)
+        diff = (got.float() - want.float()).abs().max().item()
+        ms_f = timed(fused)
+        ms_l = timed(library)
+        ms_g = timed(library_matmul)
+        flops = 2.0 * n * hidden * kl
+        w_bytes = hidden * kl * 2 + n * kl * 2 + 2 * n * hidden * 2
+        row = {"case": name, "rows": n, "k_local": kl, "fused_ms": ms_f, "library_ms": ms_l,
+               "library_matmul_alone_ms": ms_g, "fused_vs_library": ms_l / ms_f,
+               "fused_tflops_per_gpu": flops / ms_f / 1e9, "max_abs_diff_to_library": diff}
+        if n <= 1024:
+            ach = w_bytes / (ms_f * 1e-3) / 1e9
+            row["roofline"] = {"bound": "hbm", "achieved": ach, "peak": peak_bw, "unit": "GB/s", "frac": ach / peak_bw,
+                               "peak_source": peak_bw_kind, "bytes_per_launch": w_bytes,
+                               "note": "weight shard + rows in + residual in + rows out; the exchange is not counted"}
+        else:
+            ach = flops / ms_f / 1e9
+            row["roofline"] = {"bound": "tensor", "achieved": ach, "peak": peak_tf, "unit": "TFLOP/s",
+                               "frac": ach / peak_tf, "peak_source": peak_tf_kind}
+        if world > 1:
+            # fp32 partial sums to the owners + rounded rows to every rank, per rank and launch
+            row["nvlink_bytes_out_per_gpu"] = int(n * hidden * 4 * (world - 1) / world + n * hidden * 2 * (world - 1) / world)
+        rows.append(row)
+    err = ops.device_error(dev)
+    pr.close()
+    if rank != 0:
+        return None
+    return {"workload": f"o_proj of a llama3-70b-shaped layer: hidden {hidden}, {k_full // 128} query heads x 128 over "
+                        f"{world} rank(s), bf16; residual added; 8 layers' weights in turn",
+            "kernel": "oproj_reduce_kernel (tcgen05 GEMM; fp32 partial sums over NVLink peer stores, summed in rank "
+                      "order by the tile's owner, one rounding, rows stored to every rank)",
+            "library": "torch.matmul + NCCL all_reduce + residual add" if world > 1 else "torch.matmul + residual add",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "rows": rows, "device_error_word": err}
+
+
+def run_oproj(args):
+    """`--workload oproj`: see `measure_oproj`; one rank per GPU under torchrun."""
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rec = measure_oproj(world, rank, dev, steps=args.steps, warmup=args.warmup, shard_of=args.shard_of)
+    if rank == 0:
+        print(json.dumps(rec), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_copy(args):
     """`--workload copy`: the page-copy kernel (copy-on-write of forked pages) and the RoPE + append kernel
     alone, with CUDA events: achieved bytes/s (read + written) against the measured HBM copy bandwidth."""
@@ -1587,7 +1709,7 @@ def main():
     ap.add_argument("--requests", type=int, default=64, help="requests per GPU (default: the workload's 64)")
     ap.add_argument("--pages", type=int, default=32768, help="pool pages (default: the workload's 32768)")
     ap.add_argument("--kernel-reps", type=int, default=100, help="launches timed for the roofline figure")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam", "copy", "qkv"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "decode70b", "beam", "copy", "qkv", "oproj"],
                     help="decode: the headline decode layer; prefill: the chunked-prefill mix (tensor-core bound)")
     ap.add_argument("--prefill-scale", type=float, default=1.0, help="fraction of the 8+8 requests of the prefill mix")
     ap.add_argument("--prefill-mask", action="store_true", help="prefill: pass the reference-form boolean mask")
@@ -1625,6 +1747,8 @@ def main():
         run_copy(args)
     elif args.workload == "qkv":
         run_qkv(args)
+    elif args.workload == "oproj":
+        run_oproj(args)
     else:
         run_ours(args)
 

@@ -33,7 +33,7 @@
 extern "C" {
 #endif
 
-#define PIEKV_VERSION 102
+#define PIEKV_VERSION 103
 
 /* element types */
 #define PIEKV_F32 0
@@ -462,9 +462,50 @@ int piekv_peer_wait(const int32_t *flags, int32_t world, int32_t step, int32_t *
 int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_counter, int32_t *err,
                             void *stream);
 
+/* ---- output projection with the sum over the ranks in its epilogue ---------------------------------
+ *
+ * Replaces, for a head-sharded (tensor-parallel) layer, the three steps after the attention in
+ * pie/src/pie_worker/model/llama3.py:693-709: the row-parallel o_proj on the local shard
+ * (fun.linear(attn_output, proj_o)), dist.all_reduce of the partial result, and residual + attn_proj.
+ * One launch per rank and step; the partial sums travel as fp32 over NVLink (plain peer stores) and
+ * the result is rounded once.  Every rank gets the same bits.
+ *
+ * Buffers of all ranks are mapped into every process (piekv_peer_alloc / piekv_peer_open):
+ *   out[r]     the result rows [n, hidden] (row stride `hidden`) on rank r.  Alternate between two
+ *              buffers from step to step: a rank may run one step ahead of a rank that still reads.
+ *   stage[r]   staging for the partial sums of the tiles rank r owns; stage_bytes each
+ *   arrive[r]  int32[arrive_words], done[r] int32[done_words] flag words on rank r, zero at the start
+ * Sizes for n <= n_max from piekv_oproj_allreduce_sizes: sizes[0] staging bytes, [1] arrival words,
+ * [2] completion words.  `step` must grow by one from call to call (start at 1) and be the same on
+ * every rank, as must n, k_local and hidden.  world == 1 needs only out[0].
+ * A rank that waits 2 s for another gives up with PIEKV_ERR_WAIT_TIMEOUT in the error word. */
+typedef struct piekv_peer_reduce {
+  void *out[PIEKV_MAX_PEERS];
+  void *stage[PIEKV_MAX_PEERS];
+  int32_t *arrive[PIEKV_MAX_PEERS];
+  int32_t *done[PIEKV_MAX_PEERS];
+  int64_t stage_bytes, arrive_words, done_words;
+  int32_t world, rank;
+  int32_t step;
+  int32_t reserved;
+} piekv_peer_reduce;
+
+int piekv_oproj_allreduce_sizes(int32_t n_max, int32_t hidden, int32_t world, int64_t *sizes);
+
+/* out[r][i, :] = residual[i, :] + sum over ranks of a[i, :k_local] . w_o[:, :k_local]^T for every r.
+ * a: [n, k_local] this rank's attention rows (k_local = local heads x head_dim, a multiple of 64);
+ * w_o: [hidden, k_local] this rank's columns of the projection weight (rows = output features, as
+ * torch.nn.functional.linear takes it); residual: NULL or [n, hidden], the same values on every rank;
+ * hidden a multiple of 64; 16-bit types; strides in elements.  n == 0 launches nothing: do not consume a
+ * step number for it. */
+int piekv_oproj_allreduce(const void *a, int64_t a_stride_n, const void *w_o, int64_t w_stride_n,
+                          const void *residual, int64_t residual_stride_n, int32_t n, int32_t k_local,
+                          int32_t hidden, int32_t dtype, const piekv_peer_reduce *peers, int32_t *err,
+                          void *stream);
+
 /* sizeof of the structs that cross this boundary, for bindings to check their mirrors against:
  * which = 0: piekv_rope_params, 1: piekv_peer_outputs, 2: piekv_attn_options, 3: piekv_wire_batch,
- * 4: piekv_qkv_options; anything else: -1. */
+ * 4: piekv_qkv_options, 5: piekv_peer_reduce; anything else: -1. */
 int32_t piekv_abi_sizeof(int32_t which);
 
 /* ---- page copy (fork with copy-on-write of a partial page) ----------------------- */

@@ -88,6 +88,24 @@ class PeerOutputsC(C.Structure):
     ]
 
 
+class PeerReduceC(C.Structure):
+    """Mirror of `piekv_peer_reduce`."""
+
+    _fields_ = [
+        ("out", C.c_void_p * MAX_PEERS),
+        ("stage", C.c_void_p * MAX_PEERS),
+        ("arrive", C.c_void_p * MAX_PEERS),
+        ("done", C.c_void_p * MAX_PEERS),
+        ("stage_bytes", C.c_int64),
+        ("arrive_words", C.c_int64),
+        ("done_words", C.c_int64),
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("step", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
 _p = C.c_void_p
 _i32 = C.c_int32
 _i64 = C.c_int64
@@ -119,6 +137,11 @@ SIGNATURES = {
         C.c_int,
         [_p, _i64, _p, _i64, _p, _p, _p, _p, _p, _p, _p, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
          C.POINTER(RopeParams), _p, _p, C.POINTER(QkvOptions)],
+    ),
+    "piekv_oproj_allreduce_sizes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_int64)]),
+    "piekv_oproj_allreduce": (
+        C.c_int,
+        [_p, _i64, _p, _i64, _p, _i64, _i32, _i32, _i32, _i32, C.POINTER(PeerReduceC), _p, _p],
     ),
     "piekv_decode_workspace_bytes": (_i64, [_i32, _i32, _i32, _i32]),
     "piekv_decode_counter_bytes": (_i64, [_i32]),

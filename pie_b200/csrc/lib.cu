@@ -61,6 +61,7 @@ extern "C" int32_t piekv_abi_sizeof(int32_t which) {
   if (which == 2) return (int32_t)sizeof(piekv_attn_options);
   if (which == 3) return (int32_t)sizeof(piekv_wire_batch);
   if (which == 4) return (int32_t)sizeof(piekv_qkv_options);
+  if (which == 5) return (int32_t)sizeof(piekv_peer_reduce);
   return -1;
 }
 

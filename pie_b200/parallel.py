@@ -13,6 +13,8 @@ Two schemes, both taken from the reference:
 `allgather_heads` uses NCCL's collective (gloo on CPU for the tests).  `PeerOutputs` is the other way
 to join head-sharded ranks: output buffers mapped into every process of the node, which the decode
 kernel itself fills on all GPUs with plain peer stores, so no collective follows the attention.
+`PeerReduce` is the same idea one step further down the layer: the row-parallel o_proj whose epilogue
+sums the ranks' partial results over NVLink, in place of the reference's linear + all_reduce + residual.
 """
 from __future__ import annotations
 
@@ -176,5 +178,151 @@ class PeerOutputs:
                     self._lib.lib.piekv_peer_close(b)
             self._local = None
             dist.barrier(group=self.group)  # everyone has unmapped before the owners free
+            self._lib.lib.piekv_peer_free(self._own)
+        self._base = None
+
+
+def reduce_layout(n_max: int, hidden: int, world: int, elem_size: int) -> dict:
+    """Offsets inside a rank's shared allocation for `PeerReduce`: arrival flags, completion flags,
+    staging, two output buffers; sizes from the library (`piekv_oproj_allreduce_sizes`)."""
+    from . import _lib
+    sizes = (C.c_int64 * 3)()
+    _lib.check(_lib.lib.piekv_oproj_allreduce_sizes(n_max, hidden, world, sizes), "oproj_allreduce_sizes")
+    stage_bytes, arrive_words, done_words = int(sizes[0]), int(sizes[1]), int(sizes[2])
+    up = lambda x: (x + 255) // 256 * 256
+    lay = {"stage_bytes": stage_bytes, "arrive_words": arrive_words, "done_words": done_words}
+    lay["arrive"] = 0
+    lay["done"] = up(4 * arrive_words)
+    lay["stage"] = lay["done"] + up(4 * done_words)
+    lay["out0"] = lay["stage"] + up(stage_bytes)
+    out_bytes = up(n_max * hidden * elem_size)
+    lay["out1"] = lay["out0"] + out_bytes
+    lay["nbytes"] = lay["out1"] + out_bytes
+    return lay
+
+
+class PeerReduce:
+    """Row-parallel output projection without a collective: `oproj(a, w_o, residual)` launches one kernel
+    per rank that computes this rank's partial product, sends it as fp32 to the rank that owns each tile,
+    sums the ranks there in rank order, adds the residual, rounds once and stores the rows into EVERY
+    rank's output buffer (pie/src/pie_worker/model/llama3.py:693-709: linear, all_reduce, residual add).
+    The returned [n, hidden] tensor is complete on this rank when the kernel ends, and holds the same
+    bits on every rank.  Two output buffers alternate from step to step: a result stays valid until the
+    call after the next.  Consume it on the stream the next call is queued on.
+
+    One process per GPU on one node; every rank makes the same calls with the same sizes.  Collective
+    constructor and `close()`."""
+
+    def __init__(self, n_max: int, hidden: int, dtype: torch.dtype, device,
+                 group: Optional[dist.ProcessGroup] = None) -> None:
+        from . import _lib
+        self._lib = _lib
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if self.world > _lib.MAX_PEERS:
+            raise ValueError(f"{self.world} ranks: at most {_lib.MAX_PEERS} GPUs of one node")
+        self.device = torch.device(device)
+        self.n_max, self.hidden, self.dtype = int(n_max), int(hidden), dtype
+        es = torch.empty((), dtype=dtype).element_size()
+        self._lay = reduce_layout(self.n_max, self.hidden, self.world, es)
+        self.nbytes = self._lay["nbytes"]
+        ptr = C.c_void_p()
+        handle = C.create_string_buffer(_lib.PEER_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib.piekv_peer_alloc(self.nbytes, C.byref(ptr), handle), "peer_alloc")
+            self._own = int(ptr.value)
+            self._base: Optional[List[int]] = [self._own] * self.world
+            if self.world > 1:
+                handles: List[Optional[bytes]] = [None] * self.world
+                dist.all_gather_object(handles, handle.raw, group=group)
+                for r in range(self.world):
+                    if r == self.rank:
+                        continue
+                    q = C.c_void_p()
+                    _lib.check(_lib.lib.piekv_peer_open(handles[r], C.byref(q)), f"peer_open(rank {r})")
+                    self._base[r] = int(q.value)
+        self._local = torch.as_tensor(_RawCuda(self._own, self.nbytes), device=self.device)
+        self.step = 0
+        self._desc = None
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=group)  # every rank has mapped every buffer before anyone stores
+
+    def _descriptor(self):
+        """The library's description of this step: one prebuilt struct per output buffer, the step number set."""
+        if self._desc is None:
+            lay = self._lay
+            self._desc = []
+            for off in (lay["out1"], lay["out0"]):   # index = step & 1
+                d = self._lib.PeerReduceC()
+                for r in range(self.world):
+                    d.out[r] = self._base[r] + off
+                    d.stage[r] = self._base[r] + lay["stage"]
+                    d.arrive[r] = self._base[r] + lay["arrive"]
+                    d.done[r] = self._base[r] + lay["done"]
+                d.stage_bytes, d.arrive_words, d.done_words = lay["stage_bytes"], lay["arrive_words"], lay["done_words"]
+                d.world, d.rank, d.reserved = self.world, self.rank, 0
+                self._desc.append(d)
+        d = self._desc[self.step & 1]
+        d.step = self.step
+        return d
+
+    def oproj(self, a: torch.Tensor, w_o: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """a: [n, k_local] (or [n, local heads, head_dim]) this rank's attention rows; w_o: [hidden, k_local]
+        this rank's columns of the projection weight; residual: None or [n, hidden] (the same on every rank).
+        Returns residual + sum over ranks of a @ w_o.T as [n, hidden], a view of this step's buffer."""
+        from .ops import _dtype_code, _err_word, _require_cuda, _stream
+        _require_cuda(a, "a")
+        _require_cuda(w_o, "w_o")
+        if a.dim() == 3:
+            a = a.reshape(a.shape[0], -1)
+        if a.dim() != 2 or w_o.dim() != 2 or a.stride(1) != 1 or w_o.stride(1) != 1:
+            raise ValueError("a and w_o must be 2-D with contiguous rows")
+        n, k = a.shape
+        if tuple(w_o.shape) != (self.hidden, k):
+            raise ValueError(f"w_o shape {tuple(w_o.shape)} differs from ({self.hidden}, {k})")
+        if n > self.n_max:
+            raise ValueError(f"{n} rows: the buffers were sized for {self.n_max}")
+        if a.dtype != self.dtype or w_o.dtype != self.dtype:
+            raise ValueError("a and w_o must have the dtype the buffers were made for")
+        if residual is not None:
+            _require_cuda(residual, "residual")
+            if tuple(residual.shape) != (n, self.hidden) or residual.dtype != self.dtype or residual.stride(1) != 1:
+                raise ValueError("residual must be [n, hidden] with contiguous rows, of the same dtype")
+        if n == 0:
+            return torch.empty((0, self.hidden), dtype=self.dtype, device=self.device)
+        self.step += 1
+        d = self._descriptor()
+        try:
+            self._lib.check(self._lib.lib.piekv_oproj_allreduce(
+                a.data_ptr(), a.stride(0), w_o.data_ptr(), w_o.stride(0),
+                residual.data_ptr() if residual is not None else None,
+                residual.stride(0) if residual is not None else 0, n, k, self.hidden,
+                _dtype_code(self.dtype, "oproj_allreduce"), C.byref(d), _err_word(self.device).data_ptr(),
+                _stream(self.device)), "oproj_allreduce")
+        except Exception:
+            self.step -= 1   # nothing was launched: the step number is not used up
+            raise
+        return self.result(n)
+
+    def result(self, n: int) -> torch.Tensor:
+        """[n, hidden] rows of the latest step on this rank."""
+        off = self._lay["out0"] if (self.step & 1) else self._lay["out1"]
+        return self._local[off:].view(self.dtype)[: n * self.hidden].view(n, self.hidden)
+
+    def close(self) -> None:
+        if self._base is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # nobody is still storing into a buffer about to go away
+        with torch.cuda.device(self.device):
+            for r, b in enumerate(self._base):
+                if r != self.rank:
+                    self._lib.lib.piekv_peer_close(b)
+            self._local = None
+            if self.world > 1:
+                dist.barrier(group=self.group)  # everyone has unmapped before the owners free
             self._lib.lib.piekv_peer_free(self._own)
         self._base = None

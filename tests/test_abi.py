@@ -28,7 +28,7 @@ def test_header_and_bindings_agree():
 
 
 def test_version_and_error_text():
-    assert _lib.lib.piekv_version() == 102
+    assert _lib.lib.piekv_version() == 103
     rc = _lib.lib.piekv_get_seq_lens(None, None, 4, 16, None, None)
     assert rc > 0
     assert b"null" in _lib.lib.piekv_last_error_string()
@@ -87,6 +87,7 @@ def test_struct_mirrors_have_the_size_the_library_reports():
     assert _lib.lib.piekv_abi_sizeof(2) == C.sizeof(_lib.AttnOptions)
     assert _lib.lib.piekv_abi_sizeof(3) == C.sizeof(_lib.WireBatch)
     assert _lib.lib.piekv_abi_sizeof(4) == C.sizeof(_lib.QkvOptions)
+    assert _lib.lib.piekv_abi_sizeof(5) == C.sizeof(_lib.PeerReduceC)
     assert _lib.lib.piekv_abi_sizeof(99) == -1
 
 
