@@ -1274,6 +1274,7 @@ def measure_oproj(world, rank, dev, steps=40, warmup=5, cases=None, shard_of=1):
     cases = cases or (("decode", 256), ("prefill", 8192))
     n_max = max(n for _, n in cases)
     pr = PeerReduce(n_max, hidden, dt, dev)
+    pr16 = PeerReduce(n_max, hidden, dt, dev, partial_sums="storage") if world > 1 else None
 
     def over_ranks(x):
         if world == 1:
@@ -1303,6 +1304,9 @@ def measure_oproj(world, rank, dev, steps=40, warmup=5, cases=None, shard_of=1):
 
         def fused(i):
             return pr.oproj(a, ws[i % layers], res)
+
+        def fused16(i):
+            return pr16.oproj(a, ws[i % layers], res)
 
         def library(i):
             y = torch.matmul(a, ws[i % layers].t())
@@ -1337,9 +1341,17 @@ def measure_oproj(world, rank, dev, steps=40, warmup=5, cases=None, shard_of=1):
         if world > 1:
             # fp32 partial sums to the owners + rounded rows to every rank, per rank and launch
             row["nvlink_bytes_out_per_gpu"] = int(n * hidden * 4 * (world - 1) / world + n * hidden * 2 * (world - 1) / world)
+            # the same kernel with the partial sums rounded to bf16 on their way (an all-reduce's bytes)
+            got16 = fused16(0).clone()
+            torch.cuda.synchronize(dev)
+            row["partials_16bit_max_abs_diff_to_library"] = (got16.float() - want.float()).abs().max().item()
+            row["partials_16bit_fused_ms"] = timed(fused16)
+            row["partials_16bit_fused_vs_library"] = ms_l / row["partials_16bit_fused_ms"]
         rows.append(row)
     err = ops.device_error(dev)
     pr.close()
+    if pr16 is not None:
+        pr16.close()
     if rank != 0:
         return None
     return {"workload": f"o_proj of a llama3-70b-shaped layer: hidden {hidden}, {k_full // 128} query heads x 128 over "

@@ -479,6 +479,9 @@ int piekv_peer_wait_counted(const int32_t *flags, int32_t world, int32_t *step_c
  * [2] completion words.  `step` must grow by one from call to call (start at 1) and be the same on
  * every rank, as must n, k_local and hidden.  world == 1 needs only out[0].
  * A rank that waits 2 s for another gives up with PIEKV_ERR_WAIT_TIMEOUT in the error word. */
+/* flags: the partial sums cross NVLink rounded to the 16-bit storage type (what an all-reduce of 16-bit
+ * tensors does) instead of fp32: half the bytes, for large n where the link is the limit. */
+#define PIEKV_REDUCE_PARTIALS_16BIT 1
 typedef struct piekv_peer_reduce {
   void *out[PIEKV_MAX_PEERS];
   void *stage[PIEKV_MAX_PEERS];
@@ -487,7 +490,7 @@ typedef struct piekv_peer_reduce {
   int64_t stage_bytes, arrive_words, done_words;
   int32_t world, rank;
   int32_t step;
-  int32_t reserved;
+  int32_t flags; /* PIEKV_REDUCE_* bits; the same on every rank */
 } piekv_peer_reduce;
 
 int piekv_oproj_allreduce_sizes(int32_t n_max, int32_t hidden, int32_t world, int64_t *sizes);

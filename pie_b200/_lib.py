@@ -102,9 +102,11 @@ class PeerReduceC(C.Structure):
         ("world", C.c_int32),
         ("rank", C.c_int32),
         ("step", C.c_int32),
-        ("reserved", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
+
+REDUCE_PARTIALS_16BIT = 1
 
 _p = C.c_void_p
 _i32 = C.c_int32

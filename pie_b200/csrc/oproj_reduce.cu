@@ -50,7 +50,8 @@ struct OprojParams {
   int n, k, hidden;
   int world, rank, step;
   int slots;  // tiles an owner may hold: ceil(tiles / world)
-  float *stage[PIEKV_MAX_PEERS];     // stage[r]: [world][slots][NT / 4][128][4] fp32 on rank r
+  int stage16;  // partial sums travel rounded to the 16-bit storage type instead of fp32
+  uint8_t *stage[PIEKV_MAX_PEERS];   // stage[r]: [world][slots][NT / 4][128][4] fp32 (or [NT / 8][128][8] 16-bit) on rank r
   int32_t *arrive[PIEKV_MAX_PEERS];  // arrive[r]: [slots][world][8] on rank r
   int32_t *done[PIEKV_MAX_PEERS];    // done[r]: [tiles][8] on rank r
   void *out[PIEKV_MAX_PEERS];        // out[r]: [n, hidden] on rank r
@@ -204,13 +205,18 @@ __global__ void __launch_bounds__(kOThreads, 1)
     const int r = (warp & 3) * 32 + lane;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const int c_half = (warp >> 2) * kHalf;
-    constexpr size_t kTileFloats = (size_t)kOBM * NT;
+    const size_t tile_bytes = (size_t)kOBM * NT * (p.stage16 ? 2 : 4);
     // the warp's tile for the rows it is about to store: 32 rows x kRowBytes, 16-byte pieces swizzled by row
     uint8_t *wtile = smem_raw + (base - smem_u32(smem_raw)) + STAGES * kStageBytes + warp * (32 * kRowBytes);
     auto swz = [](int row, int piece) { return kPieces == 8 ? (piece ^ (row & 7)) : (piece ^ ((row >> 1) & 3)); };
     const int32_t *arrive_own = p.arrive[p.rank];
     const int32_t *done_own = p.done[p.rank];
-    const float *stage_own = p.stage[p.rank];
+    const uint8_t *stage_own = p.stage[p.rank];
+    // Tile t belongs to rank t mod world.  With an even grid a CTA therefore keeps one role for all its tiles
+    // (they are a grid apart): the senders run ahead of the owners of the same tiles on the other ranks, so
+    // that an owner seldom waits for a partial.  Measured and not kept: roles that alternate from tile to tile
+    // (every owned tile then waits for its sender in lockstep, 8 % slower on 8192 rows), and completion flags
+    // raised one tile late (the wait moves from the fence into the stores: the link is the limit).
     int nt = 0;
     bool alive = true;
     OTRACE_DECL
@@ -230,18 +236,29 @@ __global__ void __launch_bounds__(kOThreads, 1)
       const uint32_t acc = tmem + lane_base + buf * NT + c_half;
       if (owner != p.rank) {
         // ---- the partial goes to the owner
-        float4 *dst = reinterpret_cast<float4 *>(p.stage[owner] + ((size_t)p.rank * p.slots + slot) * kTileFloats) +
-                      (size_t)(c_half / 4) * kOBM + r;
+        uint8_t *tile = p.stage[owner] + ((size_t)p.rank * p.slots + slot) * tile_bytes;
 #pragma unroll 1
         for (int ch = 0; ch < kHalf / 32; ++ch) {
           uint32_t v[32];
           tc::tmem_ld32(acc + ch * 32, v);
           tc::tmem_wait_ld();
           if (row_ok) {
+            if (p.stage16) {
+              uint4 *dst = reinterpret_cast<uint4 *>(tile) + (size_t)((c_half + ch * 32) / 8) * kOBM + r;
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              dst[(size_t)(ch * 8 + q) * kOBM] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                                            __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+              for (int q = 0; q < 4; ++q)
+                dst[(size_t)q * kOBM] =
+                    make_uint4(pack2<T>(__uint_as_float(v[8 * q]), __uint_as_float(v[8 * q + 1])),
+                               pack2<T>(__uint_as_float(v[8 * q + 2]), __uint_as_float(v[8 * q + 3])),
+                               pack2<T>(__uint_as_float(v[8 * q + 4]), __uint_as_float(v[8 * q + 5])),
+                               pack2<T>(__uint_as_float(v[8 * q + 6]), __uint_as_float(v[8 * q + 7])));
+            } else {
+              float4 *dst = reinterpret_cast<float4 *>(tile) + (size_t)((c_half + ch * 32) / 4) * kOBM + r;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                dst[(size_t)q * kOBM] = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
+                                                    __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+            }
           }
         }
         OTRACE(1)
@@ -288,10 +305,25 @@ __global__ void __launch_bounds__(kOThreads, 1)
                 if (src == p.rank) {
 #pragma unroll
                   for (int i = 0; i < 32; ++i) s[i] += __uint_as_float(v[i]);
+                } else if (p.stage16) {
+                  const uint4 *sp = reinterpret_cast<const uint4 *>(stage_own + ((size_t)src * p.slots + slot) * tile_bytes) +
+                                    (size_t)((c_half + ch * 32) / 8) * kOBM + r;
+                  uint4 x[4];
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) x[q] = __ldcg(sp + (size_t)q * kOBM);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) {
+                    const uint32_t w4[4] = {x[q].x, x[q].y, x[q].z, x[q].w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 f = unpack2<T>(w4[e]);
+                      s[8 * q + 2 * e] += f.x;
+                      s[8 * q + 2 * e + 1] += f.y;
+                    }
+                  }
                 } else {
-                  const float4 *sp =
-                      reinterpret_cast<const float4 *>(stage_own + ((size_t)src * p.slots + slot) * kTileFloats) +
-                      (size_t)(c_half / 4 + ch * 8) * kOBM + r;
+                  const float4 *sp = reinterpret_cast<const float4 *>(stage_own + ((size_t)src * p.slots + slot) * tile_bytes) +
+                                     (size_t)((c_half + ch * 32) / 4) * kOBM + r;
                   float4 x[8];
 #pragma unroll
                   for (int q = 0; q < 8; ++q) x[q] = __ldcg(sp + (size_t)q * kOBM);
@@ -477,6 +509,7 @@ extern "C" int piekv_oproj_allreduce(const void *a, int64_t a_stride_n, const vo
   p.rank = peers->rank;
   p.step = peers->step;
   p.slots = (int)slots;
+  p.stage16 = (peers->flags & PIEKV_REDUCE_PARTIALS_16BIT) ? 1 : 0;
   p.residual = residual;
   p.residual_stride = residual_stride_n;
   p.err = err;
@@ -491,13 +524,13 @@ extern "C" int piekv_oproj_allreduce(const void *a, int64_t a_stride_n, const vo
       PIEKV_REQUIRE(peers->stage[r] != nullptr && peers->arrive[r] != nullptr && peers->done[r] != nullptr &&
                         (reinterpret_cast<uintptr_t>(peers->stage[r]) & 15) == 0,
                     "oproj_allreduce: staging or flags of rank %d missing", r);
-      p.stage[r] = reinterpret_cast<float *>(peers->stage[r]);
+      p.stage[r] = reinterpret_cast<uint8_t *>(peers->stage[r]);
       p.arrive[r] = peers->arrive[r];
       p.done[r] = peers->done[r];
     }
   }
   if (peers->world > 1) {
-    PIEKV_REQUIRE(peers->stage_bytes >= slots * peers->world * (int64_t)kOBM * nt * 4 &&
+    PIEKV_REQUIRE(peers->stage_bytes >= slots * peers->world * (int64_t)kOBM * nt * (p.stage16 ? 2 : 4) &&
                       peers->arrive_words >= slots * peers->world * kOFlagsPerTile &&
                       peers->done_words >= tiles * kOFlagsPerTile,
                   "oproj_allreduce: staging or flag arrays too small for %d rows (see piekv_oproj_allreduce_sizes)", n);

@@ -209,15 +209,21 @@ class PeerReduce:
     The returned [n, hidden] tensor is complete on this rank when the kernel ends, and holds the same
     bits on every rank.  Two output buffers alternate from step to step: a result stays valid until the
     call after the next.  Consume it on the stream the next call is queued on.
+    `partial_sums="storage"` sends the partial sums rounded to the 16-bit dtype, as an all-reduce of 16-bit
+    tensors does (half the NVLink bytes; for prefill-sized batches on four or more ranks, where the link is
+    the limit); the default sends fp32 and rounds once.
 
     One process per GPU on one node; every rank makes the same calls with the same sizes.  Collective
     constructor and `close()`."""
 
     def __init__(self, n_max: int, hidden: int, dtype: torch.dtype, device,
-                 group: Optional[dist.ProcessGroup] = None) -> None:
+                 group: Optional[dist.ProcessGroup] = None, partial_sums: str = "fp32") -> None:
         from . import _lib
         self._lib = _lib
         self.group = group
+        if partial_sums not in ("fp32", "storage"):
+            raise ValueError("partial_sums: 'fp32', or 'storage' to send them rounded to the 16-bit dtype")
+        self.partial_sums = partial_sums
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if self.world > _lib.MAX_PEERS:
@@ -262,7 +268,8 @@ class PeerReduce:
                     d.arrive[r] = self._base[r] + lay["arrive"]
                     d.done[r] = self._base[r] + lay["done"]
                 d.stage_bytes, d.arrive_words, d.done_words = lay["stage_bytes"], lay["arrive_words"], lay["done_words"]
-                d.world, d.rank, d.reserved = self.world, self.rank, 0
+                d.world, d.rank = self.world, self.rank
+                d.flags = self._lib.REDUCE_PARTIALS_16BIT if self.partial_sums == "storage" else 0
                 self._desc.append(d)
         d = self._desc[self.step & 1]
         d.step = self.step

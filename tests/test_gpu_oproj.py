@@ -126,7 +126,7 @@ def test_a_rank_that_never_comes_times_out():
     torch.cuda.synchronize()
     err = ops.device_error(dev)
     assert err is not None and err["code"] == _lib.PIEKV_ERR_WAIT_TIMEOUT, err
-    # what rank 0 owed to rank 1 did arrive: the partial of tile 1 (rank 1 owns odd tiles) and its flags
+    # what rank 0 owed to rank 1 did arrive: the partial of tile 1 (rank 1 owns it) and its flags
     r1 = mem[lay["nbytes"]:]
     flags = r1[lay["arrive"]: lay["arrive"] + 4 * 16].view(torch.int32)   # slot 0: [2 senders][8 warps]
     assert flags[:8].tolist() == [1] * 8 and flags[8:16].tolist() == [0] * 8
