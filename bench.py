@@ -875,16 +875,10 @@ def measure_head_sharded(world, rank, dev, steps=48, warmup=4):
                        "lognormal ctx (median 2048), 20% evicted + refilled every 32 steps", "steps": steps,
            "warmup": warmup, "scaling": "strong"}
     if world == 1:
-        # eager launches and one graph of all steps: a busy host (the GPUs' machines are shared) can hold the
-        # eager loop back, the graph paces itself
         r = decode70b_leg(1, 0, dev, steps, warmup)
-        rg = decode70b_leg(1, 0, dev, steps, warmup, graph=True)
-        best = r if r["ms"] <= rg["ms"] else rg
-        rec.update({"n_gpus": 1, "join": "none (all heads on one GPU)", "tokens_per_s": best["B"] * steps / (best["ms"] * 1e-3),
-                    "ms_per_step": best["ms"] / steps, "eager_ms_per_step": r["ms"] / steps,
-                    "graph_ms_per_step": rg["ms"] / steps, "per_gpu_kernel_us": best["kern_ms"] * 1e3,
-                    "roofline": roof(best), "strong_scaling_vs_1gpu": 1.0, "launch": best["launch_mode"],
-                    "device_error_word": r["err"] or rg["err"]})
+        rec.update({"n_gpus": 1, "join": "none (all heads on one GPU)", "tokens_per_s": r["B"] * steps / (r["ms"] * 1e-3),
+                    "ms_per_step": r["ms"] / steps, "per_gpu_kernel_us": r["kern_ms"] * 1e3, "roofline": roof(r),
+                    "strong_scaling_vs_1gpu": 1.0, "launch": r["launch_mode"], "device_error_word": r["err"]})
         return rec
     peer = decode70b_leg(world, rank, dev, steps, warmup, join="peer")
     peer_graph = decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=True)
@@ -892,7 +886,7 @@ def measure_head_sharded(world, rank, dev, steps=48, warmup=4):
     # the unsharded step on rank 0 alone (the other ranks wait at the barrier with an idle GPU)
     one = None
     if rank == 0:
-        one = decode70b_leg(1, 0, dev, steps, warmup, graph=True)   # a graph: not held back by a busy host
+        one = decode70b_leg(1, 0, dev, steps, warmup)
     torch.cuda.synchronize(dev)
     dist.barrier()
     if rank != 0:
