@@ -30,6 +30,7 @@ on the host cores; `--impl flashinfer` times the reference's CUDA dependency as 
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import math
 import os
@@ -194,7 +195,8 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a collective that a failed rank never joins gives up after five minutes, not the default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     n_gpus = world
@@ -915,7 +917,8 @@ def run_decode70b(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        # a collective that a failed rank never joins gives up after five minutes, not the default ten
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=300))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     B = args.requests if args.requests != 64 else 256
@@ -1372,7 +1375,7 @@ def run_oproj(args):
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=300))
     rec = measure_oproj(world, rank, dev, steps=args.steps, warmup=args.warmup, shard_of=args.shard_of)
     if rank == 0:
         print(json.dumps(rec), flush=True)
