@@ -92,16 +92,6 @@ def test_argument_checks():
         pr.close()
 
 
-def test_sizes():
-    lay = reduce_layout(128, 4096, 2, 2)
-    # 64 narrow tiles: 32 per owner, one staged copy per sender
-    assert lay["stage_bytes"] == 2 * 32 * 128 * 64 * 4
-    assert lay["arrive_words"] == 32 * 2 * 8 and lay["done_words"] == 64 * 8
-    assert reduce_layout(128, 4096, 1, 2)["stage_bytes"] == 0
-    wide = reduce_layout(20480, 4096, 8, 2)
-    assert wide["stage_bytes"] >= 20480 * 4096 * 4
-
-
 def test_a_rank_that_never_comes_times_out():
     """Two ranks described, one launched: the launched rank's wait for the other's partial sums runs out
     after two seconds, the error word says so, and the context stays usable."""

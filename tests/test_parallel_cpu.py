@@ -86,3 +86,24 @@ def test_peer_layout_is_aligned_and_disjoint():
         assert off0 >= 8 * 4                      # the flag words of up to 8 ranks come first
         assert off0 % 256 == 0 and off1 % 256 == 0 and total % 256 == 0
         assert off1 - off0 >= need and total - off1 >= need
+
+
+def test_oproj_reduce_layout_sizes():
+    """Staging and flag sizes of the o_proj exchange (host arithmetic of the library, no GPU)."""
+    from pie_b200.parallel import reduce_layout
+    lay = reduce_layout(128, 4096, 2, 2)
+    # 64 narrow tiles: 32 per owner, one staged copy per sender
+    assert lay["stage_bytes"] == 2 * 32 * 128 * 64 * 4
+    assert lay["arrive_words"] == 32 * 2 * 8 and lay["done_words"] == 64 * 8
+    assert reduce_layout(128, 4096, 1, 2)["stage_bytes"] == 0
+    wide = reduce_layout(20480, 4096, 8, 2)
+    assert wide["stage_bytes"] >= 20480 * 4096 * 4
+    # regions do not overlap and are 256-byte aligned
+    order = ["arrive", "done", "stage", "out0", "out1", "nbytes"]
+    offs = [lay[k] for k in order]
+    assert offs == sorted(offs) and all(o % 256 == 0 for o in offs)
+    assert lay["done"] - lay["arrive"] >= 4 * lay["arrive_words"]
+    assert lay["stage"] - lay["done"] >= 4 * lay["done_words"]
+    assert lay["out0"] - lay["stage"] >= lay["stage_bytes"]
+    assert lay["out1"] - lay["out0"] >= 128 * 4096 * 2
+
