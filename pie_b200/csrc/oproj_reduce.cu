@@ -21,7 +21,10 @@
 // The staging layout is private: within a tile, 16-byte pieces (4 fp32 columns) of the 128 rows are
 // contiguous, so that the 32 rows of a warp store and load 512 contiguous bytes per instruction.  Warp w
 // of the owner reads exactly the rows and columns that warp w of the sender wrote, so the flags are per
-// warp and the epilogue warps never meet at a block-wide barrier.
+// warp and the epilogue warps never meet at a block-wide barrier.  On request the partials travel rounded to
+// the 16-bit storage type (8 columns per piece): an all-reduce's bytes and numerics.  The owner's result rows
+// go through a swizzled shared-memory tile of the warp and leave as 128-byte row pieces: a thread-per-row
+// store would put 16-byte fragments, a row apart, on the link.
 //
 // All ranks must launch with the same sizes (and so the same grid): a CTA takes its tiles in increasing
 // order on every rank, which is what keeps the waits free of cycles.  Flags carry the step number, which
