@@ -494,6 +494,10 @@ typedef struct piekv_peer_reduce {
 } piekv_peer_reduce;
 
 int piekv_oproj_allreduce_sizes(int32_t n_max, int32_t hidden, int32_t world, int64_t *sizes);
+/* Hidden columns per tile (256, 128 or 64) that piekv_oproj_allreduce uses for n rows; 0 for sizes it
+ * rejects.  Tiles are 128 rows high, numbered row tile * (hidden / cols) + column tile; tile t belongs to
+ * rank t % world and is staged in slot t / world of its owner.  For tools that inspect the staging. */
+int32_t piekv_oproj_tile_cols(int32_t n, int32_t hidden);
 
 /* out[r][i, :] = residual[i, :] + sum over ranks of a[i, :k_local] . w_o[:, :k_local]^T for every r.
  * a: [n, k_local] this rank's attention rows (k_local = local heads x head_dim, a multiple of 64);

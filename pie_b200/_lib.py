@@ -141,6 +141,7 @@ SIGNATURES = {
          C.POINTER(RopeParams), _p, _p, C.POINTER(QkvOptions)],
     ),
     "piekv_oproj_allreduce_sizes": (C.c_int, [_i32, _i32, _i32, C.POINTER(C.c_int64)]),
+    "piekv_oproj_tile_cols": (_i32, [_i32, _i32]),
     "piekv_oproj_allreduce": (
         C.c_int,
         [_p, _i64, _p, _i64, _p, _i64, _i32, _i32, _i32, _i32, C.POINTER(PeerReduceC), _p, _p],

@@ -458,6 +458,11 @@ extern "C" void *piekv_oproj_trace(void) {
 }
 #endif
 
+extern "C" int32_t piekv_oproj_tile_cols(int32_t n, int32_t hidden) {
+  if (n <= 0 || hidden <= 0 || hidden % 64 != 0) return 0;
+  return piekv::oproj_tile_cols(n, hidden);
+}
+
 extern "C" int piekv_oproj_allreduce_sizes(int32_t n_max, int32_t hidden, int32_t world, int64_t *sizes) {
   using namespace piekv;
   PIEKV_REQUIRE(n_max > 0 && hidden > 0 && hidden % 64 == 0 && world >= 1 && world <= PIEKV_MAX_PEERS && sizes != nullptr,

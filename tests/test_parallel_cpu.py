@@ -107,3 +107,33 @@ def test_oproj_reduce_layout_sizes():
     assert lay["out0"] - lay["stage"] >= lay["stage_bytes"]
     assert lay["out1"] - lay["out0"] >= 128 * 4096 * 2
 
+
+def test_oproj_staging_holds_every_tiling():
+    """The index arithmetic of the o_proj exchange, redone on the host: for every shape the tile width the
+    launcher picks, each tile's (owner, slot) is unique, and the staging and flag arrays that
+    `piekv_oproj_allreduce_sizes` asks for hold every tile of every row count up to the maximum."""
+    from pie_b200 import _lib
+    from pie_b200.parallel import reduce_layout
+    for hidden in (64, 1024, 4096, 8192):
+        for world in (1, 2, 4, 8):
+            for n_max in (1, 128, 300, 5000):
+                lay = reduce_layout(n_max, hidden, world, 2)
+                for n in sorted({1, n_max // 2 + 1, n_max}):
+                    nt = _lib.lib.piekv_oproj_tile_cols(n, hidden)
+                    assert nt in (64, 128, 256) and hidden % nt == 0
+                    tiles = -(-n // 128) * (hidden // nt)
+                    slots = -(-tiles // world)
+                    seen = set()
+                    for t in range(tiles):
+                        key = (t % world, t // world)
+                        assert key not in seen and key[1] < slots
+                        seen.add(key)
+                    if world > 1:
+                        assert lay["stage_bytes"] >= world * slots * 128 * nt * 4
+                    assert lay["arrive_words"] >= slots * world * 8
+                    assert lay["done_words"] >= tiles * 8
+    assert _lib.lib.piekv_oproj_tile_cols(8192, 8192) == 256      # enough wide tiles for every SM
+    assert _lib.lib.piekv_oproj_tile_cols(256, 8192) == 128       # a decode step: 128 tiles
+    assert _lib.lib.piekv_oproj_tile_cols(64, 4096) == 64
+    assert _lib.lib.piekv_oproj_tile_cols(64, 96) == 0
+
