@@ -23,8 +23,10 @@ bytes / CUDA-event time against the measured HBM copy bandwidth; the attention-o
 `cpu_baseline` = the CPU oracle on a bounded sample.  The same line carries sub-records of the secondary
 workloads, measured after the headline's timed region: `head_sharded` (70B-shaped decode, KV heads split
 over the N ranks and joined by the decode kernel's peer stores, with the NCCL all-gather and the one-GPU
-step beside it) at every N, and `prefill` (chunked-prefill mix, tensor-core roofline) and `beam` (beam
-search with shared pages) at N = 1.  `--impl reference` times the CPU restatement of the reference path
+step beside it) and `oproj` (the o_proj of that layer with the sum over the ranks and the residual in the
+kernel's epilogue, matmul + NCCL all-reduce + add beside it) at every N, and `prefill` (chunked-prefill mix,
+tensor-core roofline), `beam` (beam search with shared pages) and `qkv` (QKV projection with RoPE + append as
+its epilogue) at N = 1.  `--impl reference` times the CPU restatement of the reference path
 on the host cores; `--impl flashinfer` times the reference's CUDA dependency as a black box.
 """
 from __future__ import annotations
@@ -1740,7 +1742,7 @@ def main():
     ap.add_argument("--min-timed-ms", type=float, default=250.0,
                     help="decode: replay the captured graph of --steps steps until the timed region lasts this long")
     ap.add_argument("--no-sub", action="store_true",
-                    help="decode: skip the secondary workloads' sub-records (head_sharded, prefill, beam)")
+                    help="decode: skip the secondary workloads' sub-records (head_sharded, oproj, prefill, beam, qkv)")
     ap.add_argument("--prefill-brle", action="store_true",
                     help="prefill: pass the mask as BRLE runs (wire form), expanded to bits on the device")
     args = ap.parse_args()
