@@ -271,6 +271,7 @@ def run_ours(args):
     # The graph holds the driver's K steps.  It is replayed R times back to back inside ONE event pair so
     # that the timed region lasts about a quarter of a second whatever K is (clock samples, power state);
     # steps / ms_per_step stay per step, `timed_replays` = R.
+    torch.cuda.synchronize(dev)  # the inputs were made on the default stream; `stream` is not ordered behind it
     with torch.cuda.stream(stream):
         for i in range(warmup):
             step_device(i, stream.cuda_stream)
@@ -383,6 +384,7 @@ def run_ours(args):
             ev_out[b].record(s_out)
 
     ops.set_programmatic_dependent_launch(0)
+    torch.cuda.synchronize(dev)  # buffers and the wrapper above were made on the default stream
     for i in range(3):
         step_e2e(i)
     barrier()
@@ -785,6 +787,10 @@ def decode70b_leg(world, rank, dev, steps, warmup, join="peer", graph=False, bat
 
     g = None
     launch_mode = "eager, one fused kernel per step"
+    # The pool, the inputs and the zeroed workspace were made on the default stream, and `side` is not ordered
+    # behind it: without this, a first step on `side` can read a workspace that is not zero yet (recycled
+    # allocator memory holds whatever the previous leg left there).
+    torch.cuda.synchronize(dev)
     side = torch.cuda.Stream(device=dev)
     use_graph = graph and (peers is not None or world == 1)  # the NCCL join stays eager
     if use_graph:
@@ -1110,6 +1116,7 @@ def beam_leg():
                 ops.copy_kv_pages(pool, src, dst, val)
                 launches[0] += 3
 
+    torch.cuda.synchronize(dev)  # tables and buffers above were made on the default stream
     side = torch.cuda.Stream(device=dev)
     with torch.cuda.stream(side):
         device_run()  # eager once: warm-up
