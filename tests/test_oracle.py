@@ -190,3 +190,30 @@ def test_oracle_window_and_sinks_against_a_dense_float64_softmax():
         s = (k[lo:, 0].double() @ sc.q[j, 1].double()) * (1.0 / math.sqrt(64))  # the all-true mask does not bound above
         want = torch.softmax(s, 0) @ v[lo:, 0].double()
         assert (out[j, 1].double() - want).abs().max().item() < 1e-5
+
+
+def test_oproj_allreduce_residual_chain():
+    """The oracle's o_proj + all-reduce + residual (llama3.py:693-709): sharding the contraction changes
+    nothing but roundings, and the reference's three roundings stay within three storage-type steps of
+    the exact sum."""
+    import torch
+    from oracle import paged_kv_ref as R
+    g = torch.Generator().manual_seed(5)
+    n, k, hidden = 19, 256, 96
+    a = (torch.randn((n, k), generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn((hidden, k), generator=g) * 0.5).to(torch.bfloat16)
+    res = torch.randn((n, hidden), generator=g).to(torch.bfloat16)
+    exact1 = R.oproj_allreduce_residual([a], [w], res, exact=True)
+    for world in (1, 2, 4):
+        kl = k // world
+        ash = [a[:, r * kl:(r + 1) * kl] for r in range(world)]
+        wsh = [w[:, r * kl:(r + 1) * kl] for r in range(world)]
+        exact = R.oproj_allreduce_residual(ash, wsh, res, exact=True)
+        assert torch.allclose(exact, exact1, rtol=0, atol=1e-9)
+        got = R.oproj_allreduce_residual(ash, wsh, res)
+        assert got.dtype == torch.bfloat16 and got.shape == (n, hidden)
+        parts = sum((x.double() @ y.double().t()).abs() for x, y in zip(ash, wsh))
+        bound = 2.0 ** -8 * (parts + 2 * exact.abs() + res.double().abs()) + 1e-6
+        assert bool(((got.double() - exact).abs() <= bound).all())
+    assert R.oproj_allreduce_residual([a], [w], None).shape == (n, hidden)
+
